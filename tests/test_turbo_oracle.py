@@ -1,0 +1,146 @@
+"""Pins the TurboQuant codec restatement (oracle/turbo_oracle.c) against the reference's own
+C++ (tests/test_turbo_quant.cpp of the SwiftLM tree) compiled into oracle/_ref/."""
+import ctypes as C
+import subprocess
+import os
+
+import numpy as np
+import pytest
+
+from oracle import c_oracle as CO
+
+REF = CO.load_ref()
+pytestmark = pytest.mark.skipif(REF is None, reason="oracle/_ref not built (run make -C oracle)")
+
+
+def fptr(a):
+    return a.ctypes.data_as(C.c_void_p)
+
+
+def ref_gauss(n, seed=20260330):
+    REF.turbo_ref_seed(C.c_uint64(seed))
+    return np.array([REF.turbo_ref_rn() for _ in range(n)], np.float32)
+
+
+def test_reference_test_program_passes():
+    exe = os.path.join(os.path.dirname(CO.__file__), "_ref", "test_turbo_quant")
+    out = subprocess.run([exe], capture_output=True, text=True)
+    assert out.returncode == 0 and "9/9 tests passed" in out.stdout
+
+
+def test_transforms_bit_exact():
+    lib = CO.load()
+    x = ref_gauss(128 * 8).reshape(8, 128)
+    for mine, ref in (("turbo_rot_fwd", "turbo_ref_rfwd"), ("turbo_rot_inv", "turbo_ref_rinv"),
+                      ("turbo_qjl_rot", "turbo_ref_qrot")):
+        for row in x:
+            a, b = row.copy(), row.copy()
+            getattr(lib, mine)(fptr(a))
+            getattr(REF, ref)(fptr(b))
+            np.testing.assert_array_equal(a, b)
+    a, b = x[0].copy(), x[0].copy()
+    lib.turbo_fwht128(fptr(a))
+    REF.turbo_ref_fwht(fptr(b), 128)
+    np.testing.assert_array_equal(a, b)
+
+
+def test_index_pack_fp16_bit_exact():
+    lib = CO.load()
+    lib.turbo_from_f16.restype = C.c_float
+    lib.turbo_to_f16.restype = C.c_uint16
+    lib.turbo_to_f16.argtypes = [C.c_float]
+    bounds = [REF.turbo_ref_boundaries()[i] for i in range(7)]
+    probes = list(np.linspace(-0.3, 0.3, 601, dtype=np.float32)) + bounds + \
+        [np.nextafter(np.float32(b), np.float32(1)) for b in bounds] + \
+        [np.nextafter(np.float32(b), np.float32(-1)) for b in bounds]
+    for v in probes:
+        assert lib.turbo_nearest3(C.c_float(v)) == REF.turbo_ref_nc3(C.c_float(v))
+    rng = np.random.default_rng(1)
+    for _ in range(20):
+        idx = rng.integers(0, 8, 128).astype(np.uint8)
+        a, b = np.zeros(48, np.uint8), np.zeros(48, np.uint8)
+        lib.turbo_pack3(fptr(idx), fptr(a))
+        REF.turbo_ref_p3(fptr(idx), fptr(b), 128)
+        np.testing.assert_array_equal(a, b)
+        u, w = np.zeros(128, np.uint8), np.zeros(128, np.uint8)
+        lib.turbo_unpack3(fptr(a), fptr(u))
+        REF.turbo_ref_u3(fptr(a), fptr(w), 128)
+        np.testing.assert_array_equal(u, idx)
+        np.testing.assert_array_equal(w, idx)
+    vals = np.concatenate([rng.standard_normal(2000) * 10.0 ** rng.integers(-9, 6, 2000),
+                           [0.0, -0.0, 1e-8, 65504.0, 1e6, -1e6, 6.1e-5, 5.9e-5]]).astype(np.float32)
+    for v in vals:
+        h = lib.turbo_to_f16(C.c_float(v))
+        assert h == REF.turbo_ref_tf16(C.c_float(v))
+        assert lib.turbo_from_f16(C.c_uint16(h)) == REF.turbo_ref_ff16(C.c_uint16(h))
+
+
+def _ref_encode_v(src):
+    """The V flow of the reference test, tests/test_turbo_quant.cpp:69-75, from its primitives."""
+    buf = src.copy()
+    gn = np.sqrt(np.float32(sum(np.float32(x) * np.float32(x) for x in buf), dtype=np.float32))
+    return buf, gn
+
+
+def test_v_codec_matches_reference_flow_and_snr():
+    src = ref_gauss(128 * 200).reshape(200, 128)
+    packed, norm = CO.turbo_encode_v(src)
+    dec = CO.turbo_decode_v(packed, norm)
+    # reference flow, vector by vector, with the reference's primitives
+    cents = np.array([REF.turbo_ref_centroids()[i] for i in range(8)], np.float32)
+    tm = te = 0.0
+    for t in range(200):
+        buf = src[t].copy()
+        ns = np.float32(0)
+        for x in buf:
+            ns = np.float32(ns + x * x)
+        gn = np.float32(np.sqrt(ns))
+        inv = np.float32(1) / gn
+        buf = (buf * inv).astype(np.float32)
+        REF.turbo_ref_rfwd(fptr(buf))
+        idx = np.array([REF.turbo_ref_nc3(C.c_float(x)) for x in buf], np.uint8)
+        rs = np.float32(0)
+        for i in idx:
+            rs = np.float32(rs + cents[i] * cents[i])
+        cor = np.float32(gn / np.float32(np.sqrt(rs)))
+        pk = np.zeros(48, np.uint8)
+        REF.turbo_ref_p3(fptr(idx), fptr(pk), 128)
+        np.testing.assert_array_equal(pk, packed[t])
+        assert REF.turbo_ref_tf16(C.c_float(cor)) == norm[t]
+        d = cents[idx].copy()
+        REF.turbo_ref_rinv(fptr(d))
+        d = (d * np.float32(REF.turbo_ref_ff16(C.c_uint16(int(norm[t]))))).astype(np.float32)
+        np.testing.assert_array_equal(d, dec[t])
+        tm += float(((d - src[t]) ** 2).mean())
+        te += float((src[t] ** 2).mean())
+    rel = tm / te
+    assert abs(rel - 0.0343) < 5e-4          # the figure the reference test prints (T7)
+    assert -10 * np.log10(rel) > 9.0
+
+
+def test_k_codec_inner_product_snr_matches_reference():
+
+    lib = CO.load()
+    # T8 draws after T3-T7 consumed numbers; reproduce the statistic on our own draw instead
+    rng = np.random.default_rng(8)
+    ki = rng.standard_normal((100, 128)).astype(np.float32)
+    kq = rng.standard_normal((100, 128)).astype(np.float32)
+    packed, signs, norm, rnorm = CO.turbo_encode_k(ki)
+    dec = CO.turbo_decode_k(packed, signs, norm, rnorm)
+    ipt = (ki * kq).sum(-1)
+    ipa = (dec * kq).sum(-1)
+    rel = float(((ipa - ipt) ** 2).sum() / (ipt ** 2).sum())
+    assert rel < 0.15 and -10 * np.log10(rel) > 9.0
+    # decode flow from reference primitives (tests/test_turbo_quant.cpp:96-98) on vector 0
+    cents = np.array([REF.turbo_ref_centroids()[i] for i in range(8)], np.float32)
+    idx = np.zeros(128, np.uint8)
+    REF.turbo_ref_u3(fptr(packed[0]), fptr(idx), 128)
+    d = cents[idx].copy()
+    REF.turbo_ref_rinv(fptr(d))
+    sf = np.array([1.0 if signs[0][i // 8] & (1 << (i % 8)) else -1.0 for i in range(128)], np.float32)
+    REF.turbo_ref_qrot(fptr(sf))
+    qs = np.float32(np.float32(REF.turbo_ref_qjl_c()) / np.float32(128.0)
+                    * np.float32(REF.turbo_ref_ff16(C.c_uint16(int(rnorm[0])))))
+    sc = np.float32(REF.turbo_ref_ff16(C.c_uint16(int(norm[0]))))
+    want = ((d + sf * qs) * sc).astype(np.float32)
+    np.testing.assert_array_equal(want, dec[0])
