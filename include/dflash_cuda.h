@@ -1,0 +1,145 @@
+/* dflash_cuda.h — C ABI of the B200 (sm_100a) implementation of SwiftLM's DFlash
+ * speculative-verify kernels.
+ *
+ * These entry points are what the Swift functions in Sources/DFlash/DFlashKernels.swift of the
+ * SwiftLM tree bind to once their Metal bodies are replaced (a SwiftPM C target exposes this
+ * header through a module map).  Conventions, all functions:
+ *   - every pointer is a DEVICE pointer on the current CUDA device unless its name says "host";
+ *   - tensors are dense, row-major, last axis contiguous, exactly the reference's layouts;
+ *   - `stream` is a cudaStream_t passed as void* (NULL = the default stream); work is
+ *     stream-ordered and the call returns without synchronising;
+ *   - the caller owns every buffer; the library keeps no reference after the call returns;
+ *   - the return value is a dflash_status (0 = ok, negative = error); nothing aborts, nothing
+ *     falls back to a CPU path.  dflash_last_error_string() describes the last failure of the
+ *     calling thread.
+ *   - base pointers must be 16-byte aligned (cudaMalloc gives 256).
+ */
+#ifndef DFLASH_CUDA_H
+#define DFLASH_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum {
+  DFLASH_OK = 0,
+  DFLASH_ERR_INVALID_ARG = -1,   /* null pointer, non-positive size, misaligned base pointer */
+  DFLASH_ERR_UNSUPPORTED = -2,   /* shape or dtype outside the supported set (the reference returns nil / falls back) */
+  DFLASH_ERR_CUDA = -3,          /* a CUDA runtime or driver call failed; see dflash_last_error_string() */
+  DFLASH_ERR_WORKSPACE = -4,     /* workspace missing or smaller than *_workspace_bytes() */
+  DFLASH_ERR_DEVICE_TIMEOUT = -5 /* a bounded device-side wait gave up (reported by dflash_device_status) */
+} dflash_status;
+
+typedef enum { DFLASH_F32 = 0, DFLASH_BF16 = 1, DFLASH_F16 = 2, DFLASH_U8 = 3 } dflash_dtype;
+
+/* KV storage formats of dflash_verify_sdpa. */
+typedef enum { DFLASH_KV_DENSE = 0, DFLASH_KV_TURBO3 = 1 } dflash_kv_format;
+
+/* ---------------------------------------------------------------------------------------------
+ * Gated-delta forward that records the innovation tape; with n_per_seq it is the replay of a
+ * recorded (q,k,v,beta,g) block from the last committed state to the accepted length.
+ * Replaces DFlashKernels.gatedDeltaKernelWithTape, Sources/DFlash/DFlashKernels.swift:316-367
+ * (kernel body :122-199, CPU statement :409-466).
+ *
+ *   q,k      [B,T,Hk,Dk]  in_dtype          v    [B,T,Hv,Dv]  in_dtype
+ *   g        [B,T,Hv] or, if g_is_vector, [B,T,Hv,Dk]  in_dtype   (the decay itself, in (0,1))
+ *   beta     [B,T,Hv]     in_dtype          state_in / state_out  [B,Hv,Dv,Dk]  fp32
+ *   mask     [B,T] mask_dtype or NULL: step t of sequence b runs iff mask > 0.5        (:36,:115)
+ *   n_per_seq int32[B] or NULL: step t runs iff t < n_per_seq[b] (accepted length)
+ *   y        [B,T,Hv,Dv]  in_dtype          tape [B,T,Hv,Dv] fp32, may be NULL
+ * Per running step, per (b, hv), hk = hv / (Hv/Hk):  S *= g;  kv = S k;  delta = (v - kv) beta;
+ * S += delta (x) k;  y = S q.  A step that does not run leaves S untouched and writes y = 0,
+ * tape = 0.  fp32 arithmetic, no per-step rounding of the state.  state_out may alias state_in.
+ * Supported: Dk % 32 == 0, Dk <= 512, Hv % Hk == 0, T <= 64; in_dtype f32 / bf16 / f16.
+ */
+int32_t dflash_gated_delta_tape(const void* q, const void* k, const void* v, const void* g,
+                                const void* beta, const float* state_in, const void* mask,
+                                const int32_t* n_per_seq, void* y, float* state_out, float* tape,
+                                int32_t B, int32_t T, int32_t Hk, int32_t Hv, int32_t Dk, int32_t Dv,
+                                int32_t g_is_vector, int32_t in_dtype, int32_t mask_dtype,
+                                void* stream);
+
+/* Tape replay:  S <- S * g_t + delta_t (x) k_t  for the running steps.
+ * Replaces DFlashKernels.tapeReplayKernel, Sources/DFlash/DFlashKernels.swift:252-301 (kernel
+ * body :43-81, CPU statement :371-407).  The caller in the reference slices the first
+ * nAccepted+1 steps before the call (Sources/DFlash/RecurrentRollbackCache.swift:115-125);
+ * here the same is expressed without copies by n_per_seq[b] = nAccepted_b + 1.
+ *   tape [B,T,Hv,Dv] fp32;  k [B,T,Hk,Dk], g [B,T,Hv(,Dk)] in kg_dtype;  state fp32.
+ * mask / n_per_seq / aliasing / supported shapes as above.
+ */
+int32_t dflash_tape_replay(const float* tape, const void* k, const void* g, const float* state_in,
+                           const void* mask, const int32_t* n_per_seq, float* state_out, int32_t B,
+                           int32_t T, int32_t Hk, int32_t Hv, int32_t Dk, int32_t Dv,
+                           int32_t g_is_vector, int32_t kg_dtype, int32_t mask_dtype, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Batched block-verify attention:  out = softmax(scale * Q K^T [+ mask]) V  with the reference's
+ * visibility rule: key n is visible to query row r iff n <= N_b - 16 + r, where N_b counts the
+ * 16 block keys (Sources/DFlash/DFlashKernels.swift:614).
+ * Replaces DFlashKernels.batchedSDPA2Pass, :737-815 (partials kernel :563-649, reduce :661-720).
+ *
+ *   q, out  [B,Hq,16,D]  dtype (bf16 or f16)
+ *   dense KV, page_table == NULL:   k,v [B,Hkv,N,D]
+ *   paged KV, page_table != NULL:   k,v [num_pages,Hkv,page_tokens,D]; page_table int32
+ *           [B,max_pages]; logical token n of sequence b lives in page page_table[b][n/page_tokens]
+ *           at row n % page_tokens (page_tokens a multiple of 128; not part of the reference)
+ *   kv_len_per_seq int32[B] or NULL (every sequence has N keys); 16 <= N_b <= N
+ *   mask    additive [B,Hq,16,N] dtype or NULL; a value < the most negative finite value of
+ *           dtype hides the key (:551), otherwise it is added to the score (:553)
+ *   workspace: dflash_verify_sdpa_workspace_bytes() bytes of device scratch (split-KV partials)
+ * Supported, as the reference (:755-758): T == 16, dtype bf16/f16, D in {128,256},
+ * Hq % Hkv == 0; otherwise DFLASH_ERR_UNSUPPORTED (the reference returns nil).
+ */
+int32_t dflash_verify_sdpa(const void* q, const void* k, const void* v, const int32_t* page_table,
+                           const int32_t* kv_len_per_seq, const void* mask, void* out,
+                           void* workspace, size_t workspace_bytes, int32_t B, int32_t Hq,
+                           int32_t Hkv, int32_t T, int32_t D, int32_t N, int32_t page_tokens,
+                           int32_t max_pages, float scale, int32_t dtype, int32_t kv_format,
+                           void* stream);
+
+size_t dflash_verify_sdpa_workspace_bytes(int32_t B, int32_t Hq, int32_t Hkv, int32_t D, int32_t N);
+
+/* ---------------------------------------------------------------------------------------------
+ * Acceptance bookkeeping on the device (no host round trip of the accepted length).
+ * dflash_greedy_tokens replaces DFlashRuntime.greedyTokensWithMask,
+ * Sources/DFlash/DFlashRuntime.swift:118-128: argmax over the vocabulary with suppressed ids
+ * forced to -1e9, ties to the lowest index.  logits [rows,V] logits_dtype; suppress uint8[V] or
+ * NULL; posterior uint32[rows].
+ * dflash_accept_lengths replaces DFlashRuntime.matchAcceptanceLength, :133-142, and the
+ * commit arithmetic :523-547: verify_ids int32[B,T] (staged token, then T-1 drafted);
+ * accept[b] = number of leading i < T-1 with verify_ids[b,i+1] == posterior[b,i];
+ * next_token[b] = posterior[b, accept[b]]; replay_len[b] = accept[b] + 1, the n_per_seq of the
+ * replay (Sources/DFlash/RecurrentRollbackCache.swift:115).  next_token / replay_len may be NULL.
+ */
+int32_t dflash_greedy_tokens(const void* logits, const uint8_t* suppress, uint32_t* posterior,
+                             int32_t rows, int32_t V, int32_t logits_dtype, void* stream);
+int32_t dflash_accept_lengths(const uint32_t* posterior, const int32_t* verify_ids, int32_t* accept,
+                              int32_t* next_token, int32_t* replay_len, int32_t B, int32_t T,
+                              void* stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Host-side helpers.
+ */
+/* Splits `units` independent work units (sequences for replay, (sequence, KV head) pairs for
+ * attention) over n_gpus ranks in contiguous ranges, sizes differing by at most one.
+ * begin_end_host: int32[2*n_gpus] receives [begin_0,end_0,begin_1,end_1,...].  Not in the
+ * reference (it is single-device). */
+int32_t dflash_partition_plan(int32_t units, int32_t n_gpus, int32_t* begin_end_host);
+
+/* Reads (and clears) the device-side status word of the current device after synchronising
+ * `stream`: 0, or DFLASH_ERR_DEVICE_TIMEOUT if a kernel's bounded wait gave up. */
+int32_t dflash_device_status(void* stream);
+
+int32_t dflash_device_count(void);
+const char* dflash_last_error_string(void);
+/* Number of kernel launches issued by this library in the calling process so far. */
+uint64_t dflash_launch_count(void);
+const char* dflash_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DFLASH_CUDA_H */

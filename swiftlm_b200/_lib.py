@@ -1,0 +1,71 @@
+"""ctypes binding of libdflash_cuda.so (the C ABI declared in include/dflash_cuda.h).
+
+There is no fallback: if the library is missing or a call fails, an exception is raised.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+_PKG = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_PKG, "lib", "libdflash_cuda.so")
+
+F32, BF16, F16, U8 = 0, 1, 2, 3
+KV_DENSE, KV_TURBO3 = 0, 1
+OK, ERR_INVALID_ARG, ERR_UNSUPPORTED, ERR_CUDA, ERR_WORKSPACE, ERR_DEVICE_TIMEOUT = 0, -1, -2, -3, -4, -5
+
+_vp, _i32, _u64, _sz, _f32 = C.c_void_p, C.c_int32, C.c_uint64, C.c_size_t, C.c_float
+
+# name -> (restype, argtypes); must list every symbol include/dflash_cuda.h declares
+SIGNATURES = {
+    "dflash_gated_delta_tape": (_i32, [_vp] * 11 + [_i32] * 9 + [_vp]),
+    "dflash_tape_replay": (_i32, [_vp] * 7 + [_i32] * 9 + [_vp]),
+    "dflash_verify_sdpa": (_i32, [_vp] * 8 + [_sz] + [_i32] * 8 + [_f32, _i32, _i32, _vp]),
+    "dflash_verify_sdpa_workspace_bytes": (_sz, [_i32] * 5),
+    "dflash_greedy_tokens": (_i32, [_vp, _vp, _vp, _i32, _i32, _i32, _vp]),
+    "dflash_accept_lengths": (_i32, [_vp] * 5 + [_i32, _i32, _vp]),
+    "dflash_partition_plan": (_i32, [_i32, _i32, C.POINTER(_i32)]),
+    "dflash_device_status": (_i32, [_vp]),
+    "dflash_device_count": (_i32, []),
+    "dflash_last_error_string": (C.c_char_p, []),
+    "dflash_launch_count": (_u64, []),
+    "dflash_version": (C.c_char_p, []),
+}
+
+
+class DFlashError(RuntimeError):
+    def __init__(self, status: int, message: str):
+        super().__init__(f"dflash status {status}: {message}")
+        self.status = status
+
+
+class DFlashUnsupported(DFlashError):
+    """Shape or dtype outside the supported set (the reference returns nil or falls back)."""
+
+
+_lib = None
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(
+                f"{LIB_PATH} is missing: build it with `python -m swiftlm_b200.build` "
+                "(there is no CPU fallback)")
+        handle = C.CDLL(LIB_PATH)
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(handle, name)
+            fn.restype = res
+            fn.argtypes = args
+        _lib = handle
+    return _lib
+
+
+def check(status: int) -> None:
+    if status == OK:
+        return
+    msg = lib().dflash_last_error_string().decode()
+    if status == ERR_UNSUPPORTED:
+        raise DFlashUnsupported(status, msg)
+    raise DFlashError(status, msg)

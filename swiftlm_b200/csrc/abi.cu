@@ -1,0 +1,214 @@
+// extern "C" entry points of libdflash_cuda: argument validation, dispatch, error reporting.
+// Declarations and the reference interface each one replaces: include/dflash_cuda.h.
+#include <atomic>
+#include <cstdarg>
+#include <cstdio>
+#include <mutex>
+
+#include "common.cuh"
+
+namespace dflash {
+
+namespace {
+thread_local char g_error[512] = "";
+std::atomic<uint64_t> g_launches{0};
+__device__ int g_status_word = 0;
+
+constexpr int kMaxDevices = 64;
+std::mutex g_dev_mutex;
+int* g_status_ptr[kMaxDevices] = {};
+int g_sm_count[kMaxDevices] = {};
+}  // namespace
+
+void set_error(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_error, sizeof g_error, fmt, ap);
+  va_end(ap);
+}
+
+void count_launch(int n) { g_launches.fetch_add((uint64_t)n, std::memory_order_relaxed); }
+
+int* device_status_word() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
+  std::lock_guard<std::mutex> lock(g_dev_mutex);
+  if (!g_status_ptr[dev]) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_status_word) != cudaSuccess) return nullptr;
+    g_status_ptr[dev] = reinterpret_cast<int*>(p);
+  }
+  return g_status_ptr[dev];
+}
+
+int sm_count() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return 148;
+  std::lock_guard<std::mutex> lock(g_dev_mutex);
+  if (!g_sm_count[dev]) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    g_sm_count[dev] = n;
+  }
+  return g_sm_count[dev];
+}
+
+namespace {
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+int32_t bad(const char* what) {
+  set_error("invalid argument: %s", what);
+  return DFLASH_ERR_INVALID_ARG;
+}
+
+int32_t check_gdn_shape(int B, int T, int Hk, int Hv, int Dk, int Dv, int dtype, int mask_dtype,
+                        const void* mask) {
+  if (B <= 0 || T <= 0 || Hk <= 0 || Hv <= 0 || Dk <= 0 || Dv <= 0) return bad("non-positive dimension");
+  if (dtype != DFLASH_F32 && dtype != DFLASH_BF16 && dtype != DFLASH_F16) {
+    set_error("unsupported input dtype %d", dtype);
+    return DFLASH_ERR_UNSUPPORTED;
+  }
+  if (mask && (mask_dtype < DFLASH_F32 || mask_dtype > DFLASH_U8)) return bad("mask_dtype");
+  if (Dk % 32 != 0 || Dk > 512) {
+    set_error("unsupported Dk=%d (need a multiple of 32, at most 512)", Dk);
+    return DFLASH_ERR_UNSUPPORTED;
+  }
+  if (Hv % Hk != 0) {
+    set_error("unsupported heads: Hv=%d is not a multiple of Hk=%d", Hv, Hk);
+    return DFLASH_ERR_UNSUPPORTED;
+  }
+  if (T > 64) {
+    set_error("unsupported T=%d (at most 64 steps per call)", T);
+    return DFLASH_ERR_UNSUPPORTED;
+  }
+  return DFLASH_OK;
+}
+
+}  // namespace
+}  // namespace dflash
+
+using namespace dflash;
+
+extern "C" {
+
+int32_t dflash_gated_delta_tape(const void* q, const void* k, const void* v, const void* g,
+                                const void* beta, const float* state_in, const void* mask,
+                                const int32_t* n_per_seq, void* y, float* state_out, float* tape,
+                                int32_t B, int32_t T, int32_t Hk, int32_t Hv, int32_t Dk, int32_t Dv,
+                                int32_t g_is_vector, int32_t in_dtype, int32_t mask_dtype, void* stream) {
+  if (!q || !k || !v || !g || !beta || !state_in || !y || !state_out) return bad("null tensor pointer");
+  if (int32_t st = check_gdn_shape(B, T, Hk, Hv, Dk, Dv, in_dtype, mask_dtype, mask)) return st;
+  if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(state_in) || !aligned16(state_out) ||
+      !aligned16(y) || (tape && !aligned16(tape)))
+    return bad("tensor base pointers must be 16-byte aligned");
+  GdnArgs a{q, k, v, g, beta, state_in, mask, n_per_seq, y, state_out, tape,
+            B, T, Hk, Hv, Dk, Dv, g_is_vector ? 1 : 0, in_dtype, mask_dtype, false};
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (gdn_fast_supported(a)) return launch_gdn_fast(a, s);
+  return launch_gdn_generic(a, s);
+}
+
+int32_t dflash_tape_replay(const float* tape, const void* k, const void* g, const float* state_in,
+                           const void* mask, const int32_t* n_per_seq, float* state_out, int32_t B,
+                           int32_t T, int32_t Hk, int32_t Hv, int32_t Dk, int32_t Dv,
+                           int32_t g_is_vector, int32_t kg_dtype, int32_t mask_dtype, void* stream) {
+  if (!tape || !k || !g || !state_in || !state_out) return bad("null tensor pointer");
+  if (int32_t st = check_gdn_shape(B, T, Hk, Hv, Dk, Dv, kg_dtype, mask_dtype, mask)) return st;
+  if (!aligned16(tape) || !aligned16(k) || !aligned16(state_in) || !aligned16(state_out))
+    return bad("tensor base pointers must be 16-byte aligned");
+  GdnArgs a{nullptr, k, nullptr, g, nullptr, state_in, mask, n_per_seq, nullptr, state_out,
+            const_cast<float*>(tape), B, T, Hk, Hv, Dk, Dv, g_is_vector ? 1 : 0, kg_dtype, mask_dtype, true};
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (gdn_fast_supported(a)) return launch_gdn_fast(a, s);
+  return launch_gdn_generic(a, s);
+}
+
+int32_t dflash_verify_sdpa(const void* q, const void* k, const void* v, const int32_t* page_table,
+                           const int32_t* kv_len_per_seq, const void* mask, void* out, void* workspace,
+                           size_t workspace_bytes, int32_t B, int32_t Hq, int32_t Hkv, int32_t T,
+                           int32_t D, int32_t N, int32_t page_tokens, int32_t max_pages, float scale,
+                           int32_t dtype, int32_t kv_format, void* stream) {
+  if (!q || !k || !v || !out) return bad("null tensor pointer");
+  if (B <= 0 || Hq <= 0 || Hkv <= 0 || N <= 0) return bad("non-positive dimension");
+  // eligibility of the reference's kernel, Sources/DFlash/DFlashKernels.swift:755-758
+  if (T != 16) { set_error("unsupported query length %d (the verify block has 16 rows)", T); return DFLASH_ERR_UNSUPPORTED; }
+  if (dtype != DFLASH_BF16 && dtype != DFLASH_F16) { set_error("unsupported dtype %d (bf16 or f16)", dtype); return DFLASH_ERR_UNSUPPORTED; }
+  if (D != 128 && D != 256) { set_error("unsupported head_dim %d (128 or 256)", D); return DFLASH_ERR_UNSUPPORTED; }
+  if (Hq % Hkv != 0) { set_error("unsupported heads: Hq=%d not a multiple of Hkv=%d", Hq, Hkv); return DFLASH_ERR_UNSUPPORTED; }
+  if (N < 16) { set_error("unsupported N=%d: the 16 block keys are part of the KV", N); return DFLASH_ERR_UNSUPPORTED; }
+  if (kv_format != DFLASH_KV_DENSE) { set_error("unsupported kv_format %d in dflash_verify_sdpa", kv_format); return DFLASH_ERR_UNSUPPORTED; }
+  if (page_table && (page_tokens <= 0 || page_tokens % 128 != 0 || max_pages <= 0 ||
+                     (long long)max_pages * page_tokens < N))
+    return bad("paged KV needs page_tokens % 128 == 0 and max_pages * page_tokens >= N");
+  if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(out) || (workspace && !aligned16(workspace)))
+    return bad("tensor base pointers must be 16-byte aligned");
+  SdpaArgs a{q, k, v, page_table, kv_len_per_seq, mask, out, workspace, workspace_bytes,
+             B, Hq, Hkv, D, N, page_tokens, max_pages, scale, dtype};
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (sdpa_tc_supported(a)) return launch_sdpa_tc(a, s);
+  return launch_sdpa_simple(a, s);
+}
+
+size_t dflash_verify_sdpa_workspace_bytes(int32_t B, int32_t Hq, int32_t Hkv, int32_t D, int32_t N) {
+  if (B <= 0 || Hq <= 0 || Hkv <= 0 || D <= 0 || N <= 0) return 0;
+  return sdpa_workspace_bytes(B, Hq, Hkv, D, N);
+}
+
+int32_t dflash_greedy_tokens(const void* logits, const uint8_t* suppress, uint32_t* posterior,
+                             int32_t rows, int32_t V, int32_t logits_dtype, void* stream) {
+  if (!logits || !posterior) return bad("null tensor pointer");
+  if (rows <= 0 || V <= 0) return bad("non-positive dimension");
+  return launch_greedy_tokens(logits, suppress, posterior, rows, V, logits_dtype,
+                              reinterpret_cast<cudaStream_t>(stream));
+}
+
+int32_t dflash_accept_lengths(const uint32_t* posterior, const int32_t* verify_ids, int32_t* accept,
+                              int32_t* next_token, int32_t* replay_len, int32_t B, int32_t T,
+                              void* stream) {
+  if (!posterior || !verify_ids || !accept) return bad("null tensor pointer");
+  if (B <= 0 || T <= 0) return bad("non-positive dimension");
+  return launch_accept_lengths(posterior, verify_ids, accept, next_token, replay_len, B, T,
+                               reinterpret_cast<cudaStream_t>(stream));
+}
+
+int32_t dflash_partition_plan(int32_t units, int32_t n_gpus, int32_t* begin_end_host) {
+  if (units < 0 || n_gpus <= 0 || !begin_end_host) return bad("partition_plan arguments");
+  const int base = units / n_gpus, extra = units % n_gpus;
+  int pos = 0;
+  for (int r = 0; r < n_gpus; ++r) {
+    const int len = base + (r < extra ? 1 : 0);
+    begin_end_host[2 * r] = pos;
+    begin_end_host[2 * r + 1] = pos + len;
+    pos += len;
+  }
+  return DFLASH_OK;
+}
+
+int32_t dflash_device_status(void* stream) {
+  int* word = device_status_word();
+  if (!word) { set_error("no CUDA device"); return DFLASH_ERR_CUDA; }
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  int host = 0;
+  DFLASH_CUDA_CHECK(cudaMemcpyAsync(&host, word, sizeof(int), cudaMemcpyDeviceToHost, s));
+  DFLASH_CUDA_CHECK(cudaStreamSynchronize(s));
+  if (host != 0) {
+    DFLASH_CUDA_CHECK(cudaMemsetAsync(word, 0, sizeof(int), s));
+    DFLASH_CUDA_CHECK(cudaStreamSynchronize(s));
+    set_error("a device-side bounded wait gave up (code %d)", host);
+    return DFLASH_ERR_DEVICE_TIMEOUT;
+  }
+  return DFLASH_OK;
+}
+
+int32_t dflash_device_count(void) {
+  int n = 0;
+  if (cudaGetDeviceCount(&n) != cudaSuccess) { cudaGetLastError(); return 0; }
+  return n;
+}
+
+const char* dflash_last_error_string(void) { return g_error; }
+uint64_t dflash_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+const char* dflash_version(void) { return "dflash-cuda 0.1 (sm_100a)"; }
+
+}  // extern "C"

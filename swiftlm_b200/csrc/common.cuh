@@ -1,0 +1,121 @@
+// Shared declarations of the DFlash CUDA library (sm_100a).
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/dflash_cuda.h"
+
+namespace dflash {
+
+// ---- error plumbing (abi.cu owns the storage) --------------------------------------------
+void set_error(const char* fmt, ...);
+void count_launch(int n = 1);
+// Address of the per-device status word (a __device__ int); nullptr on failure.
+int* device_status_word();
+int sm_count();
+
+#define DFLASH_CUDA_CHECK(expr)                                                          \
+  do {                                                                                   \
+    cudaError_t _e = (expr);                                                             \
+    if (_e != cudaSuccess) {                                                             \
+      ::dflash::set_error("%s failed: %s (%s:%d)", #expr, cudaGetErrorString(_e), __FILE__, __LINE__); \
+      return DFLASH_ERR_CUDA;                                                            \
+    }                                                                                    \
+  } while (0)
+
+#define DFLASH_LAUNCH_CHECK()                                                            \
+  do {                                                                                   \
+    cudaError_t _e = cudaGetLastError();                                                 \
+    if (_e != cudaSuccess) {                                                             \
+      ::dflash::set_error("kernel launch failed: %s (%s:%d)", cudaGetErrorString(_e), __FILE__, __LINE__); \
+      return DFLASH_ERR_CUDA;                                                            \
+    }                                                                                    \
+  } while (0)
+
+// ---- element access ----------------------------------------------------------------------
+__device__ __forceinline__ float to_f32(float x) { return x; }
+__device__ __forceinline__ float to_f32(__nv_bfloat16 x) { return __bfloat162float(x); }
+__device__ __forceinline__ float to_f32(__half x) { return __half2float(x); }
+__device__ __forceinline__ float to_f32(uint8_t x) { return (float)x; }
+
+template <typename T> __device__ __forceinline__ T from_f32(float x);
+template <> __device__ __forceinline__ float from_f32<float>(float x) { return x; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float x) { return __float2bfloat16_rn(x); }
+template <> __device__ __forceinline__ __half from_f32<__half>(float x) { return __float2half_rn(x); }
+
+// mask[b*T+t] > 0.5 for a mask of runtime dtype
+__device__ __forceinline__ bool mask_on(const void* mask, int mask_dtype, int idx) {
+  switch (mask_dtype) {
+    case DFLASH_F32: return reinterpret_cast<const float*>(mask)[idx] > 0.5f;
+    case DFLASH_BF16: return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(mask)[idx]) > 0.5f;
+    case DFLASH_F16: return __half2float(reinterpret_cast<const __half*>(mask)[idx]) > 0.5f;
+    default: return reinterpret_cast<const uint8_t*>(mask)[idx] != 0;
+  }
+}
+
+// Bit t set <=> step t of sequence b runs.  T <= 64.
+__device__ __forceinline__ unsigned long long step_bits(const void* mask, int mask_dtype,
+                                                        const int32_t* n_per_seq, int b, int T) {
+  unsigned long long bits = T >= 64 ? ~0ull : ((1ull << T) - 1ull);
+  if (n_per_seq) {
+    int n = n_per_seq[b];
+    n = n < 0 ? 0 : (n > T ? T : n);
+    bits &= n >= 64 ? ~0ull : ((1ull << n) - 1ull);
+  }
+  if (mask) {
+    unsigned long long m = 0;
+    for (int t = 0; t < T; ++t) m |= (unsigned long long)mask_on(mask, mask_dtype, b * T + t) << t;
+    bits &= m;
+  }
+  return bits;
+}
+
+inline size_t dtype_size(int dt) { return dt == DFLASH_F32 ? 4 : (dt == DFLASH_U8 ? 1 : 2); }
+
+// ---- kernel families (defined in their own translation units) -----------------------------
+struct GdnArgs {
+  const void *q, *k, *v, *g, *beta;
+  const float* state_in;
+  const void* mask;
+  const int32_t* n_per_seq;
+  void* y;
+  float* state_out;
+  float* tape;        // forward: output (may be null); replay: input
+  int B, T, Hk, Hv, Dk, Dv;
+  int g_is_vector, in_dtype, mask_dtype;
+  bool replay;        // true: S <- S g + tape (x) k ; false: full forward
+};
+
+int32_t launch_gdn_generic(const GdnArgs& a, cudaStream_t stream);
+// Dk == Dv == 128, scalar gate, T <= 16: TMA-pipelined persistent kernel.
+bool gdn_fast_supported(const GdnArgs& a);
+int32_t launch_gdn_fast(const GdnArgs& a, cudaStream_t stream);
+
+struct SdpaArgs {
+  const void *q, *k, *v;
+  const int32_t* page_table;
+  const int32_t* kv_len;
+  const void* mask;
+  void* out;
+  void* workspace;
+  size_t workspace_bytes;
+  int B, Hq, Hkv, D, N, page_tokens, max_pages;
+  float scale;
+  int dtype;
+};
+
+size_t sdpa_workspace_bytes(int B, int Hq, int Hkv, int D, int N);
+int32_t launch_sdpa_simple(const SdpaArgs& a, cudaStream_t stream);
+bool sdpa_tc_supported(const SdpaArgs& a);
+int32_t launch_sdpa_tc(const SdpaArgs& a, cudaStream_t stream);
+
+int32_t launch_greedy_tokens(const void* logits, const uint8_t* suppress, uint32_t* posterior,
+                             int rows, int V, int logits_dtype, cudaStream_t stream);
+int32_t launch_accept_lengths(const uint32_t* posterior, const int32_t* verify_ids, int32_t* accept,
+                              int32_t* next_token, int32_t* replay_len, int B, int T,
+                              cudaStream_t stream);
+
+}  // namespace dflash

@@ -1,0 +1,211 @@
+"""Host-side mirror of the reference's kernel entry points (`public enum DFlashKernels`,
+Sources/DFlash/DFlashKernels.swift of the SwiftLM tree) on top of the C ABI.
+
+Same names (snake_case), argument meaning, layouts and error behaviour as the Swift API:
+inputs are never mutated, outputs are fresh tensors, `batched_sdpa_2pass` returns None for
+shapes outside the supported set exactly where the reference returns nil.  torch is used only
+for device memory and streams; every computation happens in libdflash_cuda.so.  There is no
+CPU path: tensors must live on a CUDA device.
+"""
+from __future__ import annotations
+
+from typing import Optional, Tuple
+
+import torch
+
+from . import _lib
+
+_DT = {torch.float32: _lib.F32, torch.bfloat16: _lib.BF16, torch.float16: _lib.F16,
+       torch.uint8: _lib.U8, torch.bool: _lib.U8}
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return None if t is None else t.data_ptr()
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _need_cuda(*ts):
+    for t in ts:
+        if t is not None and not t.is_cuda:
+            raise RuntimeError("DFlash kernels run on a CUDA device only (no CPU fallback)")
+
+
+def _mask_arg(mask: Optional[torch.Tensor]):
+    if mask is None:
+        return None, 0
+    if mask.dtype not in _DT:
+        mask = mask.to(torch.float32)
+    return mask.contiguous(), _DT[mask.dtype]
+
+
+def _n_arg(n_per_seq, B, device):
+    if n_per_seq is None:
+        return None
+    n = torch.as_tensor(n_per_seq, device=device).to(torch.int32).contiguous()
+    if n.numel() != B:
+        raise ValueError("n_per_seq must have one entry per sequence")
+    return n
+
+
+def gated_delta_kernel_with_tape(q, k, v, g, beta, state, mask=None, n_per_seq=None,
+                                 want_tape: bool = True) -> Tuple[torch.Tensor, torch.Tensor, Optional[torch.Tensor]]:
+    """DFlashKernels.gatedDeltaKernelWithTape (Sources/DFlash/DFlashKernels.swift:316-324).
+
+    q,k [B,T,Hk,Dk]; v [B,T,Hv,Dv]; g [B,T,Hv] or [B,T,Hv,Dk]; beta [B,T,Hv];
+    state [B,Hv,Dv,Dk] (kept in fp32); mask [B,T] optional.  Returns (y [B,T,Hv,Dv] in q's
+    dtype, new state fp32, innovation tape fp32 [B,T,Hv,Dv]).
+    n_per_seq (int32 [B], not in the reference signature) runs only the first n steps of each
+    sequence: this is the replay of a recorded block to its accepted length.
+    """
+    _need_cuda(q, k, v, g, beta, state)
+    B, T, Hk, Dk = q.shape
+    Hv, Dv = v.shape[2], v.shape[3]
+    dt = q.dtype
+    if dt not in (torch.float32, torch.bfloat16, torch.float16):
+        raise _lib.DFlashUnsupported(_lib.ERR_UNSUPPORTED, f"input dtype {dt}")
+    q, k, v, g, beta = (x.to(dt).contiguous() for x in (q, k, v, g, beta))
+    state = state.to(torch.float32).contiguous()
+    mask, mdt = _mask_arg(mask)
+    n = _n_arg(n_per_seq, B, q.device)
+    y = torch.empty((B, T, Hv, Dv), dtype=dt, device=q.device)
+    state_out = torch.empty_like(state)
+    tape = torch.empty((B, T, Hv, Dv), dtype=torch.float32, device=q.device) if want_tape else None
+    _lib.check(_lib.lib().dflash_gated_delta_tape(
+        _ptr(q), _ptr(k), _ptr(v), _ptr(g), _ptr(beta), _ptr(state), _ptr(mask), _ptr(n),
+        _ptr(y), _ptr(state_out), _ptr(tape), B, T, Hk, Hv, Dk, Dv, int(g.dim() == 4), _DT[dt], mdt,
+        _stream()))
+    return y, state_out, tape
+
+
+def tape_replay_kernel(tape, k, g, state, mask=None, n_per_seq=None) -> torch.Tensor:
+    """DFlashKernels.tapeReplayKernel (Sources/DFlash/DFlashKernels.swift:252-258).
+
+    tape [B,T,Hv,Dv] (fp32), k [B,T,Hk,Dk], g [B,T,Hv] or [B,T,Hv,Dk], state [B,Hv,Dv,Dk].
+    Returns the replayed state.  n_per_seq replays only the first n steps per sequence (what
+    the reference's caller does by slicing, Sources/DFlash/RecurrentRollbackCache.swift:115-118).
+    """
+    _need_cuda(tape, k, g, state)
+    B, T, Hv, Dv = tape.shape
+    Hk, Dk = k.shape[2], k.shape[3]
+    dt = k.dtype
+    if dt not in (torch.float32, torch.bfloat16, torch.float16):
+        raise _lib.DFlashUnsupported(_lib.ERR_UNSUPPORTED, f"input dtype {dt}")
+    tape = tape.to(torch.float32).contiguous()
+    k = k.contiguous()
+    g = g.to(dt).contiguous()
+    state = state.to(torch.float32).contiguous()
+    mask, mdt = _mask_arg(mask)
+    n = _n_arg(n_per_seq, B, k.device)
+    out = torch.empty_like(state)
+    _lib.check(_lib.lib().dflash_tape_replay(
+        _ptr(tape), _ptr(k), _ptr(g), _ptr(state), _ptr(mask), _ptr(n), _ptr(out),
+        B, T, Hk, Hv, Dk, Dv, int(g.dim() == 4), _DT[dt], mdt, _stream()))
+    return out
+
+
+_workspaces = {}
+
+
+def _workspace(device, nbytes: int) -> Optional[torch.Tensor]:
+    if nbytes == 0:
+        return None
+    key = (device.index, torch.cuda.current_stream().cuda_stream)
+    ws = _workspaces.get(key)
+    if ws is None or ws.numel() < nbytes:
+        ws = torch.empty(nbytes, dtype=torch.uint8, device=device)
+        _workspaces[key] = ws
+    return ws
+
+
+def batched_sdpa_2pass(queries, keys, values, scale: float, mask=None, kv_len=None,
+                       page_table=None, out=None, n_max=None) -> Optional[torch.Tensor]:
+    """DFlashKernels.batchedSDPA2Pass (Sources/DFlash/DFlashKernels.swift:737-743).
+
+    queries [B,Hq,16,D]; keys/values [B,Hkv,N,D] (or, with page_table int32 [B,max_pages],
+    page pools [num_pages,Hkv,page_tokens,D]); optional additive mask [B,Hq,16,N].
+    Returns [B,Hq,16,D] in the input dtype, or None where the reference returns nil
+    (query length != 16, dtype not bf16/f16, head_dim not in {128,256}, Hq % Hkv != 0).
+    """
+    _need_cuda(queries, keys, values)
+    if queries.dim() != 4 or keys.dim() != 4 or values.dim() != 4:
+        return None
+    B, Hq, T, D = queries.shape
+    dt = queries.dtype
+    if T != 16 or dt not in (torch.bfloat16, torch.float16):
+        return None
+    if D not in (128, 256) or values.shape[3] != D:
+        return None
+    Hkv = keys.shape[1]
+    if Hkv <= 0 or Hq % Hkv != 0:
+        return None
+    q = queries.contiguous()
+    k = keys.to(dt).contiguous()
+    v = values.to(dt).contiguous()
+    if kv_len is not None:
+        kv_len = torch.as_tensor(kv_len, device=q.device).to(torch.int32).contiguous()
+    if page_table is None:
+        N, page_tokens, max_pages = keys.shape[2], 0, 0
+    else:
+        if kv_len is None:
+            raise ValueError("paged KV needs kv_len")
+        page_table = page_table.to(torch.int32).contiguous()
+        page_tokens, max_pages = keys.shape[2], page_table.shape[1]
+        # n_max avoids a host read of kv_len on the hot path
+        N = int(n_max) if n_max is not None else int(kv_len.max())
+    if mask is not None:
+        mask = mask.to(dt).expand(B, Hq, 16, N).contiguous()
+    if out is None:
+        out = torch.empty_like(q)
+    L = _lib.lib()
+    ws = _workspace(q.device, L.dflash_verify_sdpa_workspace_bytes(B, Hq, Hkv, D, N))
+    try:
+        _lib.check(L.dflash_verify_sdpa(
+            _ptr(q), _ptr(k), _ptr(v), _ptr(page_table), _ptr(kv_len), _ptr(mask), _ptr(out),
+            _ptr(ws), 0 if ws is None else ws.numel(), B, Hq, Hkv, T, D, N, page_tokens, max_pages,
+            float(scale), _DT[dt], _lib.KV_DENSE, _stream()))
+    except _lib.DFlashUnsupported:
+        return None
+    return out
+
+
+def greedy_tokens_with_mask(logits: torch.Tensor, suppress_token_mask: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """DFlashRuntime.greedyTokensWithMask (Sources/DFlash/DFlashRuntime.swift:118-128).
+    logits [..., V]; returns token ids (uint32 values held in an int64-free int32 view)."""
+    _need_cuda(logits)
+    V = logits.shape[-1]
+    flat = logits.contiguous().view(-1, V)
+    sup = None
+    if suppress_token_mask is not None:
+        sup = suppress_token_mask.to(device=logits.device, dtype=torch.uint8).contiguous()
+    post = torch.empty(flat.shape[0], dtype=torch.int32, device=logits.device)
+    _lib.check(_lib.lib().dflash_greedy_tokens(_ptr(flat), _ptr(sup), _ptr(post), flat.shape[0], V,
+                                              _DT[logits.dtype], _stream()))
+    return post.view(logits.shape[:-1])
+
+
+def accept_lengths(posterior: torch.Tensor, verify_ids: torch.Tensor):
+    """DFlashRuntime.matchAcceptanceLength + the commit arithmetic
+    (Sources/DFlash/DFlashRuntime.swift:133-142, :523-547), batched over sequences.
+    posterior, verify_ids int32 [B,T].  Returns (accept [B], next_token [B], replay_len [B])."""
+    _need_cuda(posterior, verify_ids)
+    B, T = verify_ids.shape
+    posterior = posterior.to(torch.int32).contiguous()
+    verify_ids = verify_ids.to(torch.int32).contiguous()
+    acc = torch.empty(B, dtype=torch.int32, device=posterior.device)
+    nxt = torch.empty_like(acc)
+    rep = torch.empty_like(acc)
+    _lib.check(_lib.lib().dflash_accept_lengths(_ptr(posterior), _ptr(verify_ids), _ptr(acc), _ptr(nxt),
+                                               _ptr(rep), B, T, _stream()))
+    return acc, nxt, rep
+
+
+def device_status() -> None:
+    """Raises if a kernel's bounded device-side wait gave up since the last check."""
+    _lib.check(_lib.lib().dflash_device_status(_stream()))
+
+
+def launch_count() -> int:
+    return int(_lib.lib().dflash_launch_count())

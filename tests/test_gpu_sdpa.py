@@ -1,0 +1,155 @@
+"""GPU parity of the block-verify attention against the CPU oracle, through the C ABI.
+Tolerance: 2e-2 absolute (bf16/f16 inputs, fp32 accumulation, output rounded to the input dtype)."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import c_oracle as CO
+from oracle import dflash_oracle as O
+from tests.golden import gen_golden as G
+
+pytestmark = pytest.mark.gpu
+GOLD = os.path.join(os.path.dirname(__file__), "golden")
+TORCH_DT = {"bf16": torch.bfloat16, "fp16": torch.float16}
+ATOL = 2e-2
+
+
+def K():
+    from swiftlm_b200 import kernels
+    return kernels
+
+
+def dev(x, dt=None):
+    t = torch.from_numpy(np.ascontiguousarray(x)).cuda()
+    return t if dt is None else t.to(dt)
+
+
+def run(x, dtype, **kw):
+    dt = TORCH_DT[dtype]
+    out = K().batched_sdpa_2pass(dev(x["q"], dt), dev(x["k"], dt), dev(x["v"], dt), float(x["scale"]), **kw)
+    torch.cuda.synchronize()
+    K().device_status()
+    return out
+
+
+@pytest.mark.parametrize("name", sorted(G.SDPA_CASES))
+def test_golden_vectors(name):
+    x, dtype = G.sdpa_case(name)
+    gold = np.load(os.path.join(GOLD, name + ".npz"))
+    out = run(x, dtype).float().cpu().numpy()
+    assert np.abs(out - gold["out"]).max() < ATOL
+
+
+CASES = [
+    # B, Hq, Hkv, N (incl. the 16 block keys), D, dtype
+    (2, 16, 2, 16 + 1000, 256, "bf16"),       # GQA 8, D 256: the production shape, short
+    (1, 16, 2, 16, 256, "bf16"),              # only the block itself
+    (3, 8, 2, 16 + 77, 128, "bf16"),          # ragged tile edge, D 128, GQA 4
+    (1, 32, 8, 16 + 512, 128, "fp16"),        # the reference bench shape (Hq 32, Hk 8, D 128)
+    (2, 4, 4, 16 + 300, 256, "bf16"),         # no grouping (GQA 1)
+    (1, 16, 1, 16 + 2100, 256, "bf16"),       # GQA 16: two 128-row query tiles per KV head
+    (8, 16, 2, 16 + 4096, 256, "bf16"),       # a slice of the benchmark configuration
+]
+
+
+@pytest.mark.parametrize("case", CASES, ids=lambda c: "x".join(map(str, c)))
+def test_matches_oracle(case):
+    B, Hq, Hkv, N, D, dtype = case
+    x = O.make_sdpa_inputs(B, Hq, Hkv, N, D, 1000 + sum(case[:5]), dtype)
+    out = run(x, dtype)
+    assert out is not None and out.dtype == TORCH_DT[dtype]
+    want = CO.verify_sdpa(x["q"], x["k"], x["v"], float(x["scale"]))
+    assert np.abs(out.float().cpu().numpy() - want).max() < ATOL
+
+
+def test_block_causal_rule_is_exact():
+    """Row r must not depend on block keys r+1..15: perturb them, outputs of rows <= r stay
+    bit-identical (an index error shows up as a changed bit, not as a tolerance miss)."""
+    x = O.make_sdpa_inputs(2, 16, 2, 16 + 333, 256, 1100, "bf16")
+    base = run(x, "bf16").clone()
+    N = x["k"].shape[2]
+    for r in (0, 7, 14):
+        y = {k_: v_.copy() if hasattr(v_, "copy") else v_ for k_, v_ in x.items()}
+        y["k"][:, :, N - 16 + r + 1:] = O.round_bf16(y["k"][:, :, N - 16 + r + 1:] * 1.5 + 1.0)
+        y["v"][:, :, N - 16 + r + 1:] = O.round_bf16(y["v"][:, :, N - 16 + r + 1:] - 2.0)
+        out = run(y, "bf16")
+        assert torch.equal(out[:, :, :r + 1], base[:, :, :r + 1])
+        assert not torch.equal(out[:, :, r + 1:], base[:, :, r + 1:])
+
+
+def test_ragged_lengths_match_per_sequence_runs():
+    x = O.make_sdpa_inputs(3, 16, 2, 16 + 700, 256, 1101, "bf16")
+    lens = np.array([716, 16, 345], np.int32)
+    out = run(x, "bf16", kv_len=lens).float().cpu().numpy()
+    want = CO.verify_sdpa(x["q"], x["k"], x["v"], float(x["scale"]), kv_len=lens)
+    assert np.abs(out - want).max() < ATOL
+
+
+def test_paged_kv_equals_contiguous():
+    B, Hq, Hkv, D, pt = 2, 16, 2, 256, 256
+    lens = np.array([16 + 1000, 16 + 257], np.int32)
+    N = int(lens.max())
+    x = O.make_sdpa_inputs(B, Hq, Hkv, N, D, 1102, "bf16")
+    dense = run(x, "bf16", kv_len=lens)
+    max_pages = (N + pt - 1) // pt
+    rng = np.random.default_rng(7)
+    perm = rng.permutation(B * max_pages + 3)[:B * max_pages].reshape(B, max_pages).astype(np.int32)
+    kp = np.zeros((B * max_pages + 3, Hkv, pt, D), np.float32)
+    vp = np.zeros_like(kp)
+    for b in range(B):
+        for pg in range(max_pages):
+            lo, hi = pg * pt, min(N, (pg + 1) * pt)
+            kp[perm[b, pg], :, :hi - lo] = x["k"][b, :, lo:hi]
+            vp[perm[b, pg], :, :hi - lo] = x["v"][b, :, lo:hi]
+    dt = torch.bfloat16
+    paged = K().batched_sdpa_2pass(dev(x["q"], dt), dev(kp, dt), dev(vp, dt), float(x["scale"]), kv_len=lens,
+                                   page_table=dev(perm))
+    torch.cuda.synchronize()
+    assert torch.equal(paged, dense)
+
+
+def test_additive_mask():
+    x = O.make_sdpa_inputs(1, 8, 2, 16 + 90, 128, 1103, "bf16")
+    N = x["k"].shape[2]
+    mask = np.zeros((1, 8, 16, N), np.float32)
+    mask[..., 5] = -np.inf
+    mask[..., 11] = 0.75
+    out = run(x, "bf16", mask=dev(mask)).float().cpu().numpy()
+    want = O.verify_sdpa(x["q"], x["k"], x["v"], x["scale"], mask=mask)
+    assert np.abs(out - want).max() < ATOL
+
+
+def test_out_of_contract_shapes_return_none():
+    q = torch.zeros(1, 16, 8, 256, dtype=torch.bfloat16, device="cuda")
+    k = torch.zeros(1, 2, 64, 256, dtype=torch.bfloat16, device="cuda")
+    assert K().batched_sdpa_2pass(q, k, k, 0.1) is None                         # query length 8
+    q = torch.zeros(1, 16, 16, 64, dtype=torch.bfloat16, device="cuda")
+    k = torch.zeros(1, 2, 64, 64, dtype=torch.bfloat16, device="cuda")
+    assert K().batched_sdpa_2pass(q, k, k, 0.1) is None                         # head_dim 64
+    q = torch.zeros(1, 16, 16, 256, dtype=torch.float32, device="cuda")
+    k = torch.zeros(1, 2, 64, 256, dtype=torch.float32, device="cuda")
+    assert K().batched_sdpa_2pass(q, k, k, 0.1) is None                         # fp32
+    q = torch.zeros(1, 15, 16, 256, dtype=torch.bfloat16, device="cuda")
+    k = torch.zeros(1, 2, 64, 256, dtype=torch.bfloat16, device="cuda")
+    assert K().batched_sdpa_2pass(q, k, k, 0.1) is None                         # Hq % Hkv != 0
+
+
+def test_full_size_properties_benchmark_config():
+    """Configuration of the headline metric (B=32, Hq=16, Hkv=2, D=256, N=4096+16): results do
+    not depend on how sequences are batched, and constant V gives constant output."""
+    B, Hq, Hkv, N, D = 32, 16, 2, 4096 + 16, 256
+    g = torch.Generator(device="cuda").manual_seed(20260332)
+    q = torch.randn(B, Hq, 16, D, device="cuda", generator=g).bfloat16()
+    k = torch.randn(B, Hkv, N, D, device="cuda", generator=g).bfloat16()
+    v = torch.randn(B, Hkv, N, D, device="cuda", generator=g).bfloat16()
+    out = K().batched_sdpa_2pass(q, k, v, 1.0 / 16)
+    sub = K().batched_sdpa_2pass(q[5:9], k[5:9], v[5:9], 1.0 / 16)
+    torch.cuda.synchronize()
+    assert float((out[5:9].float() - sub.float()).abs().max()) < ATOL
+    ones = torch.ones_like(v) * 0.5
+    c = K().batched_sdpa_2pass(q, k, ones, 1.0 / 16)
+    assert float((c.float() - 0.5).abs().max()) < 1e-2
+    want = CO.verify_sdpa(q[:1].float().cpu().numpy(), k[:1].float().cpu().numpy(), v[:1].float().cpu().numpy(), 1.0 / 16)
+    assert np.abs(out[:1].float().cpu().numpy() - want).max() < ATOL
