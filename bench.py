@@ -1,0 +1,393 @@
+#!/usr/bin/env python
+"""Benchmark of the DFlash speculative-verify hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+One "step" is one pass of the hot path over one batch of seeded synthetic input: the
+gated-delta tape replay of BASELINE configs[1] (64 sequences x 36 linear-attention layers x 32
+v-heads, Dk = Dv = 128, T = 16, bf16 per-token inputs, fp32 state, per-sequence accepted length
+n ~ U{0..16}).  The headline `value` is replayed head-states per second with all inputs
+resident in HBM; `e2e` is the same metric through the package's host-buffer API (pinned host
+memory in, pinned host memory out, copies inside the timed region).  The verify attention of
+configs[2] is timed in the same run and reported under "sdpa".  With N > 1 (torchrun) every
+rank replays its own 64 sequences (sequence-sharded, no collective on the data path); the line
+reports the whole-job aggregate and the max-over-ranks time.
+
+`--impl reference` times the CPU statement of the same path (the oracle port of the
+reference's ops path, OpenMP over all host cores) on a bounded sample of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+SEED = 20260330
+CFG1 = dict(B_seq=64, L=36, T=16, Hk=16, Hv=32, D=128)
+CFG2 = dict(B=32, Hq=16, Hkv=2, T=16, D=256, N=4096 + 16)
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return dict(hbm_gbs=p["hbm_gbs"], bf16_tflops=p["bf16_tflops"],
+                    bf16_tflops_sustained=p.get("bf16_tflops_sustained", p["bf16_tflops"]), source="measured")
+    return dict(hbm_gbs=6650.0, bf16_tflops=1590.0, bf16_tflops_sustained=1400.0, source="fallback")
+
+
+def profiled_traffic():
+    """DRAM bytes per unit from the committed ncu summaries (profiles/traffic.json), or {}."""
+    path = os.path.join(ROOT, "profiles", "traffic.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return json.load(f)
+    return {}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.FIELDS, "--format=csv,noheader,nounits",
+                 "-lms", "20"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        mhz, mx, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                mhz.append(float(parts[0]))
+                mx = float(parts[1])
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[2:6]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(mhz) if mhz else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
+                "samples": len(mhz)}
+
+
+# ------------------------------------------------------------------------------------------------
+# workloads
+# ------------------------------------------------------------------------------------------------
+
+
+def make_replay_inputs(torch, device, seed, cfg=CFG1, pinned_host=False):
+    """configs[1]: q,k ~ N(0,1) L2-normalised; v ~ N(0,1); beta = sigmoid(N); g = exp(-softplus(N));
+    S0 ~ N(0, 0.02); n ~ U{0..T} per sequence, shared by the sequence's layers."""
+    B = cfg["B_seq"] * cfg["L"]
+    T, Hk, Hv, D = cfg["T"], cfg["Hk"], cfg["Hv"], cfg["D"]
+    g = torch.Generator(device=device).manual_seed(seed)
+    norm = torch.nn.functional.normalize
+    x = dict(
+        q=norm(torch.randn(B, T, Hk, D, device=device, generator=g), dim=-1).bfloat16(),
+        k=norm(torch.randn(B, T, Hk, D, device=device, generator=g), dim=-1).bfloat16(),
+        v=torch.randn(B, T, Hv, D, device=device, generator=g).bfloat16(),
+        beta=torch.sigmoid(torch.randn(B, T, Hv, device=device, generator=g)).bfloat16(),
+        g=torch.exp(-torch.nn.functional.softplus(torch.randn(B, T, Hv, device=device, generator=g))).bfloat16(),
+        state=0.02 * torch.randn(B, Hv, D, D, device=device, generator=g),
+        n=torch.randint(0, T + 1, (cfg["B_seq"],), device=device, generator=g).repeat_interleave(cfg["L"]).int(),
+    )
+    return x
+
+
+def replay_bytes(n_sum_heads: float, heads: int) -> float:
+    """Algorithmic bytes of the replay: per head-state 65536 (state in) + 65536 (state out) +
+    n * [256 (v) + 128 (k share) + 128 (q share) + 2 (beta) + 2 (g) + 256 (y out)], bf16 inputs."""
+    return heads * 131072.0 + 772.0 * n_sum_heads
+
+
+def sdpa_flops(cfg=CFG2) -> float:
+    return 4.0 * cfg["B"] * cfg["Hq"] * cfg["T"] * cfg["N"] * cfg["D"]
+
+
+def sdpa_bytes(cfg=CFG2) -> float:
+    kv = 2.0 * cfg["B"] * cfg["Hkv"] * cfg["N"] * cfg["D"] * 2
+    qo = 2.0 * cfg["B"] * cfg["Hq"] * cfg["T"] * cfg["D"] * 2
+    return kv + qo
+
+
+# ------------------------------------------------------------------------------------------------
+# CPU arm (the oracle is the thing measured here, and only here)
+# ------------------------------------------------------------------------------------------------
+
+
+def cpu_replay_sample(seqs: int, repeats: int = 1):
+    """Times the CPU statement of the replay on `seqs` sequences x 36 layers of configs[1]."""
+    from oracle import c_oracle as CO
+    from oracle import dflash_oracle as O
+    cfg = CFG1
+    B = seqs * cfg["L"]
+    x = O.make_gdn_inputs(B, cfg["T"], cfg["Hk"], cfg["Hv"], cfg["D"], cfg["D"], SEED + 1000, False, "bf16")
+    rng = np.random.default_rng(SEED + 1001)
+    x["n"] = np.repeat(rng.integers(0, cfg["T"] + 1, seqs), cfg["L"]).astype(np.int32)
+    CO.load()
+    best = None
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        CO.gated_delta(x["q"], x["k"], x["v"], x["g"], x["beta"], x["state"], n=x["n"], want_tape=False)
+        dt = time.perf_counter() - t0
+        best = dt if best is None else min(best, dt)
+    heads = B * cfg["Hv"]
+    return heads / best, best, CO.num_threads(), heads
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    seqs = 16
+    # steps here are bounded samples of the workload: `seqs` of its 64 sequences per step
+    vals = []
+    for i in range(args.warmup + args.steps):
+        v, dt, threads, heads = cpu_replay_sample(seqs)
+        if i >= args.warmup:
+            vals.append((v, dt))
+    value = statistics.median(v for v, _ in vals)
+    ms = statistics.median(dt for _, dt in vals) * 1e3
+    sample = (f"{seqs} of 64 sequences x 36 layers x 32 heads per step ({heads} head-states), OpenMP row-wise C "
+              f"restatement of the reference's ops path, fp32")
+    line = {
+        "impl": "reference", "metric": "replayed_head_states_per_s", "value": value, "unit": "head-states/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": workload_name(), "sample": sample},
+        "cpu_baseline": {"value": value, "unit": "head-states/s", "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "head-states/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+def workload_name():
+    return ("configs[1] gated-delta tape replay: 64 seq x 36 layers x 32 v-heads (16 qk-heads), Dk=Dv=128, T=16, "
+            "bf16 q/k/v/beta/g, fp32 state, n~U{0..16} per sequence")
+
+
+# ------------------------------------------------------------------------------------------------
+# GPU arm
+# ------------------------------------------------------------------------------------------------
+
+
+def run_gpu(args):
+    import torch
+    import torch.distributed as dist
+
+    from swiftlm_b200 import host_api, kernels
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback); use --impl reference for the CPU arm")
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(x: float) -> float:
+        if world == 1:
+            return x
+        t = torch.tensor([x], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    peaks = measured_peaks()
+    cfg = CFG1
+    x = make_replay_inputs(torch, device, SEED + 1000 + rank)
+    heads = cfg["B_seq"] * cfg["L"] * cfg["Hv"]
+    n_sum_heads = float(x["n"].sum().item()) * cfg["Hv"]
+    alg_bytes = replay_bytes(n_sum_heads, heads)
+    # inputs (5.4 GB) and outputs (5.1 GB) exceed the 126 MB L2 many times over: no flush needed
+    y = torch.empty_like(x["v"])
+    state_out = torch.empty_like(x["state"])
+
+    def step():
+        kernels.gated_delta_into(x["q"], x["k"], x["v"], x["g"], x["beta"], x["state"], x["n"], y, state_out)
+
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()   # runs through warm-up (same workload) and the timed steps
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    launches0 = kernels.launch_count()
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    barrier()
+    t_start = torch.cuda.Event(enable_timing=True)
+    t_end = torch.cuda.Event(enable_timing=True)
+    t_start.record()
+    for e0, e1 in evs:
+        e0.record()
+        step()
+        e1.record()
+    t_end.record()
+    barrier()
+    launches = kernels.launch_count() - launches0
+    clocks = sampler.stop() if rank == 0 else None
+    total_ms = max_over_ranks(t_start.elapsed_time(t_end))
+    kernel_ms = statistics.mean(e0.elapsed_time(e1) for e0, e1 in evs)
+    kernels.device_status()
+    ms_per_step = total_ms / args.steps
+    value = world * heads / (ms_per_step * 1e-3)
+    achieved_gbs = alg_bytes / (kernel_ms * 1e-3) / 1e9
+    traffic = profiled_traffic().get("gdn_fast_forward", {}).get("dram_bytes_per_algorithmic_byte")
+
+    # ---- end to end through the host-buffer API (rank-local pinned buffers) ----
+    e2e_steps = max(1, min(args.steps, 3))
+    hx = host_api.pin_replay_inputs(x)
+    hout = host_api.alloc_replay_outputs(hx)
+    host_api.gated_delta_from_host(hx, hout)   # warm-up
+    barrier()
+    t0 = torch.cuda.Event(enable_timing=True)
+    t1 = torch.cuda.Event(enable_timing=True)
+    t0.record()
+    for _ in range(e2e_steps):
+        h2d, d2h = host_api.gated_delta_from_host(hx, hout)
+    t1.record()
+    barrier()
+    e2e_ms = max_over_ranks(t0.elapsed_time(t1)) / e2e_steps
+    e2e_value = world * heads / (e2e_ms * 1e-3)
+    del hx, hout
+
+    # ---- verify attention, configs[2] (rank-local, same on every rank) ----
+    sd = run_sdpa(torch, kernels, device, args, peaks)
+
+    if world > 1:
+        dist.barrier()
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    cpu = None
+    if world == 1 or True:
+        v, dt, threads, sample_heads = cpu_replay_sample(16, repeats=6)
+        cpu = {"value": v, "unit": "head-states/s", "cores": threads, "kind": "port",
+               "sample": f"16 of 64 sequences x 36 layers x 32 heads ({sample_heads} head-states, best of 6 passes, {dt:.2f} s each), OpenMP "
+                         f"row-wise C restatement of the reference's ops path"}
+
+    line = {
+        "metric": "replayed_head_states_per_s", "value": value, "unit": "head-states/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": workload_name(), "per_gpu_batch": "64 sequences (73728 head-states)",
+                   "global_batch": f"{64 * world} sequences", "parallelism": f"sequence-sharded x{world}, no collective",
+                   "l2": "inputs (5.4 GB) and outputs (5.1 GB) per step exceed the 126 MB L2; no flush needed",
+                   "seed": SEED + 1000},
+        "roofline": {"bound": "hbm", "kernel": "gdn_fast_kernel<bf16, forward>", "achieved": achieved_gbs,
+                     "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved_gbs / peaks["hbm_gbs"],
+                     "peak_source": peaks["source"], "algorithmic_bytes_per_launch": alg_bytes,
+                     "kernel_ms": kernel_ms,
+                     "traffic": None if traffic is None else traffic * alg_bytes},
+        "cpu_baseline": cpu,
+        "e2e": {"value": e2e_value, "unit": "head-states/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                "ms_per_step": e2e_ms, "steps": e2e_steps,
+                "note": "pinned host buffers for every input (state included) and every output, chunked by "
+                        "sequence and pipelined on copy/compute streams"},
+        "gpu_launches": launches,
+        "clocks": clocks,
+        "sdpa": sd,
+    }
+    print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def run_sdpa(torch, kernels, device, args, peaks):
+    cfg = CFG2
+    g = torch.Generator(device=device).manual_seed(SEED + 2000)
+    # three rotating K/V sets (808 MB) so that no step finds its K/V in the 126 MB L2
+    sets = []
+    for _ in range(3):
+        sets.append((torch.randn(cfg["B"], cfg["Hq"], 16, cfg["D"], device=device, generator=g).bfloat16(),
+                     torch.randn(cfg["B"], cfg["Hkv"], cfg["N"], cfg["D"], device=device, generator=g).bfloat16(),
+                     torch.randn(cfg["B"], cfg["Hkv"], cfg["N"], cfg["D"], device=device, generator=g).bfloat16()))
+    out = torch.empty_like(sets[0][0])
+    scale = 1.0 / 16.0
+    steps = max(args.steps, 10)
+    for i in range(max(args.warmup, 3)):
+        q, k, v = sets[i % 3]
+        kernels.batched_sdpa_2pass(q, k, v, scale, out=out)
+    torch.cuda.synchronize()
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+    for i, (e0, e1) in enumerate(evs):
+        q, k, v = sets[i % 3]
+        e0.record()
+        kernels.batched_sdpa_2pass(q, k, v, scale, out=out)
+        e1.record()
+    torch.cuda.synchronize()
+    kernels.device_status()
+    ms = statistics.median(e0.elapsed_time(e1) for e0, e1 in evs)
+    tflops = sdpa_flops() / (ms * 1e-3) / 1e12
+    gbs = sdpa_bytes() / (ms * 1e-3) / 1e9
+    return {"metric": "verify_sdpa_tflops", "value": tflops, "unit": "TFLOP/s", "ms_per_call": ms,
+            "config": "configs[2]: B=32, Hq=16, Hkv=2, T=16, D=256, N=4096+16, bf16, scale 1/16; 3 rotating K/V sets",
+            "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                         "frac": gbs / peaks["hbm_gbs"], "algorithmic_bytes_per_launch": sdpa_bytes(),
+                         "frac_of_bf16_peak": tflops / peaks["bf16_tflops"],
+                         "note": "arithmetic intensity 128 FLOP/B is below the ridge (~252): the HBM roofline "
+                                 "caps this shape at ~49% of dense bf16 peak"}}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_gpu(args)
+
+
+if __name__ == "__main__":
+    main()

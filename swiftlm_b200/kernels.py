@@ -209,3 +209,16 @@ def device_status() -> None:
 
 def launch_count() -> int:
     return int(_lib.lib().dflash_launch_count())
+
+
+def gated_delta_into(q, k, v, g, beta, state, n_per_seq, y, state_out, tape=None, mask=None) -> None:
+    """Allocation-free form of gated_delta_kernel_with_tape: every buffer is supplied by the
+    caller (contiguous, on the current device, dtypes as documented there).  state_out may be
+    the same tensor as state."""
+    B, T, Hk, Dk = q.shape
+    Hv, Dv = v.shape[2], v.shape[3]
+    mask_t, mdt = _mask_arg(mask)
+    _lib.check(_lib.lib().dflash_gated_delta_tape(
+        _ptr(q), _ptr(k), _ptr(v), _ptr(g), _ptr(beta), _ptr(state), _ptr(mask_t), _ptr(n_per_seq),
+        _ptr(y), _ptr(state_out), _ptr(tape), B, T, Hk, Hv, Dk, Dv, int(g.dim() == 4), _DT[q.dtype], mdt,
+        _stream()))
