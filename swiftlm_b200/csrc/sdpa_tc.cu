@@ -1,7 +1,672 @@
+// Block-verify attention on the 5th-generation tensor cores (tcgen05 + tensor memory).
+//
+// Shape of the problem: per (sequence, KV head) the 16 draft tokens of the G = Hq/Hkv grouped
+// query heads form one M = 16*G row tile (128 rows for G = 8) that attends to N keys: every K/V
+// byte is read from HBM exactly once per KV head.  At bf16 KV the shape is HBM-bound
+// (128 FLOP/B), so the kernel is organised around keeping TMA loads in flight; the tensor
+// pipe and the softmax run in the shadow of the loads.
+//
+// One persistent CTA per SM (no cluster, cta_group::1, no multicast), 6 warps:
+//   warp 0     TMA producer: Q tile (4 boxes of 128 rows x 64 elements) and a ring of 16 KiB
+//              K / V boxes (128 keys x 64 elements, 128-byte swizzle), order K0 K1 V0 K2 V1 ...
+//   warp 1     MMA issuer (one lane): S = Q K^T (128 x 128 x D, both operands in shared memory,
+//              K-major) into one of two S buffers in tensor memory; O += P V with P read from
+//              tensor memory (bf16, aliasing the S buffer) and V MN-major from shared memory.
+//              Owns the tensor-memory allocation.
+//   warps 2-5  softmax: one thread per query row.  Loads its row of S from tensor memory,
+//              applies the block-causal rule on the last tiles, keeps a running reference
+//              maximum and sum, writes P (bf16) back to tensor memory, rescales O only when the
+//              maximum grew by more than 2^8, and at the end of a segment normalises and stores.
+// KV is split across CTAs stream-K style: the (unit, 128-key tile) pairs of the whole batch
+// are cut into one contiguous range per CTA, so every CTA streams the same number of tiles.
+// A range that covers a whole unit writes the output directly; the others write fp32 partials
+// (unnormalised O, reference maximum, sum) that a small second kernel merges.
+//
+// Semantics: Sources/DFlash/DFlashKernels.swift:563-649 (partials) and :661-720 (reduce):
+// visibility n <= N_b - 16 + r, fp32 scores and accumulation, zero-sum guard.  Differences:
+// contiguous instead of strided split ownership, fp32 instead of input-dtype partials, exp2
+// with a pre-scaled exponent instead of exp.
+#include <cuda.h>
+
+#include <type_traits>
+
 #include "common.cuh"
+#include "ptx.cuh"
+
 namespace dflash {
+
 size_t sdpa_simple_workspace_bytes(int B, int Hq, int D);
-size_t sdpa_workspace_bytes(int B, int Hq, int Hkv, int D, int N) { return sdpa_simple_workspace_bytes(B, Hq, D) + 256; }
-bool sdpa_tc_supported(const SdpaArgs&) { return false; }
-int32_t launch_sdpa_tc(const SdpaArgs&, cudaStream_t) { return DFLASH_ERR_UNSUPPORTED; }
+
+namespace {
+
+constexpr int kBlockN = 128;            // keys per tile
+constexpr int kRowsM = 128;             // query rows per unit tile
+constexpr int kChunkBytes = 128 * 128;  // one TMA box: 128 rows x 64 16-bit elements
+constexpr int kThreads = 192;
+constexpr float kRescaleThreshold = 8.f;   // in log2 units
+
+struct TcParams {
+  SdpaArgs a;
+  int G, R, MT;            // group size, rows per (b, kvh), 128-row tiles per (b, kvh)
+  int units;               // B * Hkv * MT
+  long long total_tiles;   // only valid when kv_len == nullptr
+  float scale_log2;
+  int* slot_unit;          // [2 * gridDim.x]
+  float* part_o;           // [2 * gridDim.x][128][D]
+  float* part_m;           // [2 * gridDim.x][128]  (reference maximum, log2 units)
+  float* part_l;           // [2 * gridDim.x][128]
+  int* status;
+};
+
+template <int D>
+struct Smem {
+  static constexpr int kQChunks = D / 64;
+  static constexpr int kStages = (D == 256) ? 10 : 12;
+  static constexpr uint32_t q = 0;
+  static constexpr uint32_t ring = kQChunks * kChunkBytes;
+  static constexpr uint32_t bars = ring + kStages * kChunkBytes;
+  // barrier slots (8 bytes each)
+  static constexpr int b_q_full = 0, b_q_empty = 1, b_pv_done = 2, b_o_free = 3;
+  static constexpr int b_s_full = 4;                 // 2
+  static constexpr int b_p_full = 6;                 // 2
+  static constexpr int b_kv_full = 8;                // kStages
+  static constexpr int b_kv_empty = 8 + kStages;     // kStages
+  static constexpr int n_bars = 8 + 2 * kStages;
+  static constexpr uint32_t misc = bars + 8 * n_bars;   // tmem base, abort flag, range info
+  static constexpr uint32_t total = misc + 64;
+  static constexpr uint32_t alloc = total + 1024;
+};
+
+// ---- work decomposition -------------------------------------------------------------------
+struct Segment {
+  int unit;        // (b * Hkv + kvh) * MT + mt
+  int b, kvh, mt;
+  int n_keys;      // N_b
+  int tile_lo, tile_hi, tiles_in_unit;
+  int slot;        // -1: covers the whole unit, write the output directly
+};
+
+__device__ __forceinline__ int tiles_of(const TcParams& p, int b) {
+  const int n = p.a.kv_len ? p.a.kv_len[b] : p.a.N;
+  return (n + kBlockN - 1) / kBlockN;
+}
+
+// Iterates the segments of one CTA's tile range.  All roles run the same iterator.
+struct SegmentIter {
+  const TcParams& p;
+  long long pos, end;     // global tile positions of the CTA's range
+  int unit, tile;         // current unit and tile inside it
+  int first;              // 1 until the first segment has been produced
+  __device__ SegmentIter(const TcParams& p_, long long begin, long long end_, int unit0, int tile0)
+      : p(p_), pos(begin), end(end_), unit(unit0), tile(tile0), first(1) {}
+  __device__ bool next(Segment& s) {
+    if (pos >= end) return false;
+    const int per_b = p.a.Hkv * p.MT;
+    s.unit = unit;
+    s.b = unit / per_b;
+    s.kvh = (unit / p.MT) % p.a.Hkv;
+    s.mt = unit % p.MT;
+    s.n_keys = p.a.kv_len ? p.a.kv_len[s.b] : p.a.N;
+    s.tiles_in_unit = (s.n_keys + kBlockN - 1) / kBlockN;
+    s.tile_lo = tile;
+    const long long left = end - pos;
+    const int avail = s.tiles_in_unit - tile;
+    const int take = left < avail ? (int)left : avail;
+    s.tile_hi = tile + take;
+    const bool whole = (s.tile_lo == 0 && s.tile_hi == s.tiles_in_unit);
+    s.slot = whole ? -1 : (first ? 2 * (int)blockIdx.x : 2 * (int)blockIdx.x + 1);
+    first = 0;
+    pos += take;
+    tile = 0;
+    unit += 1;
+    return true;
+  }
+};
+
+__device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  // start address, leading / stride byte offsets (all >> 4), descriptor version 1, 128-byte swizzle
+  return (uint64_t)((smem_addr & 0x3FFFFu) >> 4) | ((uint64_t)(lbo_bytes >> 4) << 16) |
+         ((uint64_t)(sbo_bytes >> 4) << 32) | (1ull << 46) | (2ull << 61);
+}
+
+__device__ __forceinline__ bool wait_or_abort(void* bar, uint32_t parity, volatile int* abort_flag, int* status) {
+  for (uint32_t i = 0; i < ptx::kWaitPolls; ++i) {
+    if (ptx::mbar_try_wait(bar, parity)) return true;
+    if ((i & 63u) == 63u) {
+      if (*abort_flag) return false;
+      __nanosleep(40);
+    }
+  }
+  *abort_flag = 1;
+  atomicExch(status, 2);
+  return false;
+}
+
+__device__ __forceinline__ float fast_exp2(float x) {   // ex2.approx: exp2(-inf) = +0
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+template <typename T> __device__ __forceinline__ uint32_t pack2(float a, float b);
+template <> __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float a, float b) {
+  const __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
+template <> __device__ __forceinline__ uint32_t pack2<__half>(float a, float b) {
+  const __half2 v = __floats2half2_rn(a, b);
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
+
+template <typename InT, int D>
+__global__ void __launch_bounds__(kThreads, 1)
+sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+               const __grid_constant__ CUtensorMap map_v, const TcParams p) {
+  using SL = Smem<D>;
+  constexpr int kStages = SL::kStages;
+  constexpr int kQChunks = SL::kQChunks;            // 64-element chunks of the head dimension
+  constexpr uint32_t kFmt = sizeof(InT) == 2 && std::is_same<InT, __nv_bfloat16>::value ? 1u : 0u;
+  // instruction descriptors: fp32 accumulate, A/B format, majors, N >> 3, M >> 4
+  constexpr uint32_t kIdescQK = (1u << 4) | (kFmt << 7) | (kFmt << 10) | ((kBlockN >> 3) << 17) | ((kRowsM >> 4) << 24);
+  constexpr uint32_t kIdescPV = (1u << 4) | (kFmt << 7) | (kFmt << 10) | (1u << 16) | ((64u >> 3) << 17) | ((kRowsM >> 4) << 24);
+  constexpr uint32_t kTmemCols = 512;
+  constexpr uint32_t kColO = 0, kColS = D;          // O: D columns; S buffers: 2 x 128 columns
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* sm = smem_raw + ((1024u - (ptx::smem_u32(smem_raw) & 1023u)) & 1023u);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sm + SL::bars);
+  uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(sm + SL::misc);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(sm + SL::misc + 4);
+  int* range_info = reinterpret_cast<int*>(sm + SL::misc + 8);   // unit0, tile0
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const SdpaArgs& a = p.a;
+
+  // ---- the CTA's tile range ----
+  long long total = p.total_tiles;
+  if (a.kv_len) {
+    // ragged lengths: every CTA sums the per-sequence tile counts itself (B is small)
+    long long sum = 0;
+    for (int b = 0; b < a.B; ++b) sum += tiles_of(p, b);
+    total = sum * a.Hkv * p.MT;
+  }
+  const long long C = gridDim.x;
+  const long long begin = total * blockIdx.x / C, end = total * (blockIdx.x + 1) / C;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < SL::n_bars; ++i) {
+      const bool four = (i == SL::b_o_free) || (i == SL::b_p_full) || (i == SL::b_p_full + 1);
+      ptx::mbar_init(&bars[i], four ? 4 : 1);
+    }
+    *abort_flag = 0;
+    // locate (unit, tile) of `begin`
+    int unit = 0, tile = 0;
+    if (!a.kv_len) {
+      const int tpu = (a.N + kBlockN - 1) / kBlockN;
+      unit = (int)(begin / tpu);
+      tile = (int)(begin % tpu);
+    } else {
+      long long acc = 0;
+      const int per_b = a.Hkv * p.MT;
+      for (int b = 0; b < a.B; ++b) {
+        const long long tb = tiles_of(p, b);
+        if (begin < acc + tb * per_b) {
+          const long long off = begin - acc;
+          unit = b * per_b + (int)(off / tb);
+          tile = (int)(off % tb);
+          break;
+        }
+        acc += tb * per_b;
+      }
+    }
+    range_info[0] = unit;
+    range_info[1] = tile;
+    ptx::fence_mbar_init();
+    ptx::prefetch_tensormap(&map_q);
+    ptx::prefetch_tensormap(&map_k);
+    ptx::prefetch_tensormap(&map_v);
+    // slot table: rewritten below by the softmax warps for the slots this CTA uses
+    p.slot_unit[2 * blockIdx.x] = -1;
+    p.slot_unit[2 * blockIdx.x + 1] = -1;
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc(tmem_base_slot, kTmemCols);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+  const uint32_t tmem_base = *tmem_base_slot;
+  const int unit0 = range_info[0], tile0 = range_info[1];
+
+  if (warp == 0) {
+    // =================================== TMA producer ===================================
+    if (lane == 0 && begin < end) {
+      SegmentIter it(p, begin, end, unit0, tile0);
+      Segment s;
+      uint32_t fill = 0;        // ring slots filled so far
+      uint32_t seg_idx = 0;
+      bool ok = true;
+      auto load_chunk = [&](const CUtensorMap* map, const Segment& sg, int tile, int c) -> bool {
+        const uint32_t stage = fill % kStages;
+        if (fill >= (uint32_t)kStages && !wait_or_abort(&bars[SL::b_kv_empty + stage], ((fill / kStages) - 1) & 1, abort_flag, p.status))
+          return false;
+        ptx::mbar_arrive_expect_tx(&bars[SL::b_kv_full + stage], kChunkBytes);
+        const int n0 = tile * kBlockN;
+        if (a.page_table) {
+          const int page = a.page_table[(long long)sg.b * a.max_pages + n0 / a.page_tokens];
+          ptx::tma_load_4d(sm + SL::ring + stage * kChunkBytes, map, c * 64, n0 % a.page_tokens, sg.kvh, page,
+                           &bars[SL::b_kv_full + stage]);
+        } else {
+          ptx::tma_load_4d(sm + SL::ring + stage * kChunkBytes, map, c * 64, n0, sg.kvh, sg.b, &bars[SL::b_kv_full + stage]);
+        }
+        ++fill;
+        return true;
+      };
+      while (ok && it.next(s)) {
+        // Q tile of this unit: wait until the previous segment's S = Q K^T products are done with it
+        if (seg_idx > 0 && !wait_or_abort(&bars[SL::b_q_empty], (seg_idx - 1) & 1, abort_flag, p.status)) break;
+        ptx::mbar_arrive_expect_tx(&bars[SL::b_q_full], kQChunks * kChunkBytes);
+        for (int c = 0; c < kQChunks; ++c)
+          ptx::tma_load_3d(sm + SL::q + c * kChunkBytes, &map_q, c * 64, s.mt * kRowsM, s.b * a.Hkv + s.kvh, &bars[SL::b_q_full]);
+        // K_lo, then (K_{j+1}, V_j) pairs, then V_last: the order the MMA warp consumes them
+        for (int j = s.tile_lo; ok && j <= s.tile_hi; ++j) {
+          if (j < s.tile_hi)
+            for (int c = 0; ok && c < kQChunks; ++c) ok = load_chunk(&map_k, s, j, c);
+          if (j > s.tile_lo)
+            for (int c = 0; ok && c < kQChunks; ++c) ok = load_chunk(&map_v, s, j - 1, c);
+        }
+        ++seg_idx;
+      }
+    }
+  } else if (warp == 1) {
+    // ==================================== MMA issuer ====================================
+    if (lane == 0 && begin < end) {
+      SegmentIter it(p, begin, end, unit0, tile0);
+      Segment s;
+      uint32_t drain = 0;       // ring slots consumed so far
+      uint32_t seg_idx = 0;
+      uint32_t tile_ctr = 0;    // tiles issued so far (S buffer and barrier phases)
+      bool ok = true;
+      const uint32_t q_addr = ptx::smem_u32(sm + SL::q);
+      while (ok && it.next(s)) {
+        if (!wait_or_abort(&bars[SL::b_q_full], seg_idx & 1, abort_flag, p.status)) break;
+        ptx::tc_fence_after();
+        const int ntiles = s.tile_hi - s.tile_lo;
+        for (int jj = 0; ok && jj <= ntiles; ++jj) {
+          if (jj < ntiles) {
+            // ---- S[buf] = Q K_j^T ----
+            const uint32_t t = tile_ctr + jj, buf = t & 1;
+            const uint32_t d_tmem = tmem_base + kColS + buf * kBlockN;
+            for (int c = 0; ok && c < kQChunks; ++c) {
+              const uint32_t stage = drain % kStages;
+              ok = wait_or_abort(&bars[SL::b_kv_full + stage], (drain / kStages) & 1, abort_flag, p.status);
+              if (!ok) break;
+              ptx::tc_fence_after();
+              const uint32_t k_addr = ptx::smem_u32(sm + SL::ring + stage * kChunkBytes);
+#pragma unroll
+              for (int kk = 0; kk < 4; ++kk) {   // 4 x 16 elements per 64-element chunk
+                const uint64_t da = make_desc(q_addr + c * kChunkBytes + kk * 32, 16, 1024);
+                const uint64_t db = make_desc(k_addr + kk * 32, 16, 1024);
+                ptx::umma_ss(d_tmem, da, db, kIdescQK, (c | kk) ? 1u : 0u);
+              }
+              ptx::umma_commit(&bars[SL::b_kv_empty + stage]);   // K chunk free once these products retire
+              ++drain;
+            }
+            if (!ok) break;
+            ptx::umma_commit(&bars[SL::b_s_full + buf]);
+            if (jj == ntiles - 1) ptx::umma_commit(&bars[SL::b_q_empty]);   // last use of this Q tile
+          }
+          if (jj > 0) {
+            // ---- O += P_{j-1} V_{j-1} ----
+            const uint32_t t = tile_ctr + jj - 1, buf = t & 1;
+            if (jj == 1 && seg_idx > 0) {
+              // first product of a segment overwrites O: the previous segment's epilogue must have read it
+              ok = wait_or_abort(&bars[SL::b_o_free], (seg_idx - 1) & 1, abort_flag, p.status);
+              if (!ok) break;
+            }
+            ok = wait_or_abort(&bars[SL::b_p_full + buf], (t >> 1) & 1, abort_flag, p.status);
+            if (!ok) break;
+            ptx::tc_fence_after();
+            const uint32_t p_tmem = tmem_base + kColS + buf * kBlockN;   // P (16-bit pairs) aliases S
+            for (int c = 0; ok && c < kQChunks; ++c) {
+              const uint32_t stage = drain % kStages;
+              ok = wait_or_abort(&bars[SL::b_kv_full + stage], (drain / kStages) & 1, abort_flag, p.status);
+              if (!ok) break;
+              ptx::tc_fence_after();
+              const uint32_t v_addr = ptx::smem_u32(sm + SL::ring + stage * kChunkBytes);
+#pragma unroll
+              for (int kk = 0; kk < kBlockN / 16; ++kk) {   // 16 keys per instruction
+                const uint64_t db = make_desc(v_addr + kk * 2048, kChunkBytes, 1024);
+                ptx::umma_ts(tmem_base + kColO + c * 64, p_tmem + kk * 8, db, kIdescPV, (jj > 1 || kk > 0) ? 1u : 0u);
+              }
+              ptx::umma_commit(&bars[SL::b_kv_empty + stage]);
+              ++drain;
+            }
+            if (!ok) break;
+            ptx::umma_commit(&bars[SL::b_pv_done]);
+          }
+        }
+        tile_ctr += ntiles;
+        ++seg_idx;
+      }
+    }
+  } else {
+    // ====================================== softmax ======================================
+    const int wq = warp & 3;                       // tensor-memory lane quarter this warp may touch
+    const int row = wq * 32 + lane;                // query row of the unit tile = tensor-memory lane
+    const uint32_t lane_addr = (uint32_t)(wq * 32) << 16;
+    if (begin < end) {
+      SegmentIter it(p, begin, end, unit0, tile0);
+      Segment s;
+      uint32_t seg_idx = 0, tile_ctr = 0;
+      bool ok = true;
+      while (ok && it.next(s)) {
+        const int ntiles = s.tile_hi - s.tile_lo;
+        const int rr = s.mt * kRowsM + row;          // row inside the (b, kvh) group
+        const int tok = rr & 15;                     // draft token index of this row
+        const int last_visible = s.n_keys - 16 + tok;
+        float m_ref = -INFINITY;                     // reference maximum (raw score units)
+        float l_sum = 0.f;
+        for (int jj = 0; ok && jj < ntiles; ++jj) {
+          const uint32_t t = tile_ctr + jj, buf = t & 1;
+          const int j = s.tile_lo + jj;
+          ok = wait_or_abort(&bars[SL::b_s_full + buf], (t >> 1) & 1, abort_flag, p.status);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          ptx::tc_fence_after();
+          const uint32_t s_addr = tmem_base + lane_addr + kColS + buf * kBlockN;
+          uint32_t sr[4][32];
+#pragma unroll
+          for (int q4 = 0; q4 < 4; ++q4) ptx::tmem_ld32(s_addr + q4 * 32, sr[q4]);
+          ptx::tmem_ld_wait();
+          const int n_base = j * kBlockN;
+          const bool edge = n_base + kBlockN - 1 > s.n_keys - 16;   // tile touches the block keys or the end
+          float mx = -INFINITY;
+#pragma unroll
+          for (int q4 = 0; q4 < 4; ++q4)
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              float v = __uint_as_float(sr[q4][i]);
+              if (edge && n_base + q4 * 32 + i > last_visible) v = -INFINITY;
+              sr[q4][i] = __float_as_uint(v);
+              mx = fmaxf(mx, v);
+            }
+          // lazy rescale: move the reference only when the maximum grew by more than 2^8
+          float factor = 1.f;
+          const bool grow = (mx > m_ref) && ((mx - m_ref) * p.scale_log2 > kRescaleThreshold || m_ref == -INFINITY);
+          if (grow) {
+            factor = (m_ref == -INFINITY) ? 0.f : fast_exp2((m_ref - mx) * p.scale_log2);
+            m_ref = mx;
+          }
+          const bool need_rescale = jj > 0 && __any_sync(0xffffffffu, grow);
+          if (jj > 0) {
+            // Every phase of the product barrier is waited for exactly once and in order (a
+            // parity wait that skips a phase cannot tell "done" from "two phases behind").
+            // The next product cannot start before this one retires anyway.
+            ok = wait_or_abort(&bars[SL::b_pv_done], (t - 1) & 1, abort_flag, p.status);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+          }
+          if (need_rescale) {
+            // O holds the products up to tile j-1: scale this row
+            ptx::tc_fence_after();
+#pragma unroll 1
+            for (int c = 0; c < D / 32; ++c) {
+              uint32_t o[32];
+              ptx::tmem_ld32(tmem_base + lane_addr + kColO + c * 32, o);
+              ptx::tmem_ld_wait();
+#pragma unroll
+              for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * factor);
+              ptx::tmem_st32(tmem_base + lane_addr + kColO + c * 32, o);
+            }
+            ptx::tmem_st_wait();
+          }
+          l_sum *= factor;
+          const float neg_ref = (m_ref == -INFINITY) ? 0.f : -m_ref * p.scale_log2;
+          uint32_t pr[2][32];
+          float add = 0.f;
+#pragma unroll
+          for (int q4 = 0; q4 < 4; ++q4)
+#pragma unroll
+            for (int i = 0; i < 32; i += 2) {
+              const float p0 = fast_exp2(fmaf(__uint_as_float(sr[q4][i]), p.scale_log2, neg_ref));
+              const float p1 = fast_exp2(fmaf(__uint_as_float(sr[q4][i + 1]), p.scale_log2, neg_ref));
+              add += p0 + p1;
+              pr[q4 >> 1][(q4 & 1) * 16 + (i >> 1)] = pack2<InT>(p0, p1);
+            }
+          l_sum += add;
+          ptx::tmem_st32(s_addr, pr[0]);
+          ptx::tmem_st32(s_addr + 32, pr[1]);
+          ptx::tmem_st_wait();
+          ptx::tc_fence_before();
+          __syncwarp();
+          if (lane == 0) ptx::mbar_arrive(&bars[SL::b_p_full + buf]);
+        }
+        if (!ok) break;
+        // ---- segment epilogue: wait for the last product, then normalise / store ----
+        {
+          const uint32_t t_last = tile_ctr + ntiles - 1;
+          ok = wait_or_abort(&bars[SL::b_pv_done], t_last & 1, abort_flag, p.status);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          ptx::tc_fence_after();
+          const bool valid = rr < p.R;
+          if (s.slot < 0) {
+            const float inv = l_sum == 0.f ? 1.f : 1.f / l_sum;
+            InT* orow = reinterpret_cast<InT*>(a.out) +
+                        ((((long long)s.b * a.Hq + (long long)s.kvh * p.G + (rr >> 4)) * 16) + tok) * D;
+#pragma unroll 1
+            for (int c = 0; c < D / 32; ++c) {
+              uint32_t o[32];
+              ptx::tmem_ld32(tmem_base + lane_addr + kColO + c * 32, o);
+              ptx::tmem_ld_wait();
+              if (valid) {
+                uint32_t w[16];
+#pragma unroll
+                for (int i = 0; i < 16; ++i)
+                  w[i] = pack2<InT>(__uint_as_float(o[2 * i]) * inv, __uint_as_float(o[2 * i + 1]) * inv);
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+                  *reinterpret_cast<uint4*>(orow + c * 32 + i * 8) = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
+              }
+            }
+          } else {
+            float* prow = p.part_o + ((long long)s.slot * kRowsM + row) * D;
+#pragma unroll 1
+            for (int c = 0; c < D / 32; ++c) {
+              uint32_t o[32];
+              ptx::tmem_ld32(tmem_base + lane_addr + kColO + c * 32, o);
+              ptx::tmem_ld_wait();
+#pragma unroll
+              for (int i = 0; i < 8; ++i)
+                *reinterpret_cast<uint4*>(prow + c * 32 + i * 4) = make_uint4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
+            }
+            p.part_m[(long long)s.slot * kRowsM + row] = (m_ref == -INFINITY) ? -INFINITY : m_ref * p.scale_log2;
+            p.part_l[(long long)s.slot * kRowsM + row] = l_sum;
+            if (row == 0) p.slot_unit[s.slot] = s.unit;
+          }
+          ptx::tc_fence_before();
+          __syncwarp();
+          if (lane == 0) ptx::mbar_arrive(&bars[SL::b_o_free]);
+        }
+        tile_ctr += ntiles;
+        ++seg_idx;
+      }
+    }
+  }
+
+  ptx::tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    ptx::tc_fence_after();
+    ptx::tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// ---- merge of the split-KV partials ----------------------------------------------------------
+// One block per (unit, 16 rows); thread (r, c): row r of the group, D/16 consecutive columns.
+template <typename InT, int D>
+__global__ void __launch_bounds__(256) sdpa_tc_merge_kernel(const TcParams p, int n_slots) {
+  __shared__ int s_slots[64];
+  __shared__ int s_count;
+  const int unit = blockIdx.x, rgrp = blockIdx.y;
+  // slots of this unit, in slot order (a fixed summation order keeps results bit-reproducible)
+  if (threadIdx.x < 32) {
+    int count = 0;
+    for (int base = 0; base < n_slots; base += 32) {
+      const int i = base + threadIdx.x;
+      const bool hit = i < n_slots && p.slot_unit[i] == unit;
+      const unsigned m = __ballot_sync(0xffffffffu, hit);
+      const int pos = count + __popc(m & ((1u << threadIdx.x) - 1u));
+      if (hit && pos < 64) s_slots[pos] = i;
+      count += __popc(m);
+    }
+    if (threadIdx.x == 0) s_count = count;
+  }
+  __syncthreads();
+  const int cnt = s_count < 64 ? s_count : 64;
+  if (cnt == 0) return;   // the unit was written directly by a CTA that covered all of it
+  const SdpaArgs& a = p.a;
+  const int per_b = a.Hkv * p.MT;
+  const int b = unit / per_b, kvh = (unit / p.MT) % a.Hkv, mt = unit % p.MT;
+  const int r = rgrp * 16 + (threadIdx.x >> 4);          // row of the 128-row tile
+  const int rr = mt * kRowsM + r;
+  if (rr >= p.R) return;
+  constexpr int W = D / 16;
+  const int c0 = (threadIdx.x & 15) * W;
+  float mmax = -INFINITY;
+  for (int i = 0; i < cnt; ++i) mmax = fmaxf(mmax, p.part_m[(long long)s_slots[i] * kRowsM + r]);
+  float acc[W];
+#pragma unroll
+  for (int i = 0; i < W; ++i) acc[i] = 0.f;
+  float den = 0.f;
+  for (int i = 0; i < cnt; ++i) {
+    const long long base = (long long)s_slots[i] * kRowsM + r;
+    const float m = p.part_m[base];
+    const float f = (m == -INFINITY) ? 0.f : exp2f(m - mmax);
+    den += f * p.part_l[base];
+    const float4* src = reinterpret_cast<const float4*>(p.part_o + base * D + c0);
+#pragma unroll
+    for (int q = 0; q < W / 4; ++q) {
+      const float4 v = src[q];
+      acc[4 * q] += f * v.x; acc[4 * q + 1] += f * v.y; acc[4 * q + 2] += f * v.z; acc[4 * q + 3] += f * v.w;
+    }
+  }
+  const float inv = den == 0.f ? 1.f : 1.f / den;
+  InT* orow = reinterpret_cast<InT*>(a.out) + ((((long long)b * a.Hq + (long long)kvh * p.G + (rr >> 4)) * 16) + (rr & 15)) * D + c0;
+#pragma unroll
+  for (int q = 0; q < W / 8; ++q) {
+    uint32_t w[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) w[i] = pack2<InT>(acc[8 * q + 2 * i] * inv, acc[8 * q + 2 * i + 1] * inv);
+    *reinterpret_cast<uint4*>(orow + 8 * q) = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+}
+
+size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+size_t tc_workspace_bytes(int D) {
+  const size_t slots = 2 * (size_t)sm_count();
+  return align_up(slots * sizeof(int), 256) + slots * kRowsM * ((size_t)D + 2) * sizeof(float);
+}
+
+template <typename InT, int D>
+int32_t launch_typed(const SdpaArgs& a, cudaStream_t stream) {
+  using SL = Smem<D>;
+  EncodeTiledFn encode = tensor_map_encoder();
+  if (!encode) { set_error("cuTensorMapEncodeTiled is not available from this driver"); return DFLASH_ERR_CUDA; }
+  int* status = device_status_word();
+  if (!status) { set_error("no CUDA device"); return DFLASH_ERR_CUDA; }
+  const size_t need = tc_workspace_bytes(D);
+  if (!a.workspace || a.workspace_bytes < need) {
+    set_error("verify_sdpa: workspace of %zu bytes needed, %zu given", need, a.workspace_bytes);
+    return DFLASH_ERR_WORKSPACE;
+  }
+  TcParams p;
+  p.a = a;
+  p.G = a.Hq / a.Hkv;
+  p.R = p.G * 16;
+  p.MT = (p.R + kRowsM - 1) / kRowsM;
+  p.units = a.B * a.Hkv * p.MT;
+  const long long tiles_per_unit = (a.N + kBlockN - 1) / kBlockN;
+  p.total_tiles = tiles_per_unit * p.units;
+  p.scale_log2 = a.scale * 1.4426950408889634f;
+  p.status = status;
+  const int n_sm = sm_count();
+  long long grid = p.total_tiles < n_sm ? p.total_tiles : n_sm;   // upper bound also for ragged lengths
+  if (grid < 1) grid = 1;
+  const size_t slots = 2 * (size_t)n_sm;
+  uint8_t* ws = reinterpret_cast<uint8_t*>(a.workspace);
+  p.slot_unit = reinterpret_cast<int*>(ws);
+  p.part_o = reinterpret_cast<float*>(ws + align_up(slots * sizeof(int), 256));
+  p.part_m = p.part_o + slots * kRowsM * (size_t)D;
+  p.part_l = p.part_m + slots * kRowsM;
+
+  const CUtensorMapDataType dt = std::is_same<InT, __nv_bfloat16>::value ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  CUtensorMap mq, mk, mv;
+  {
+    // Q as (d, row in (b,kvh) group, b*Hkv+kvh): rows past the group read as zeros
+    const cuuint64_t dims[3] = {(cuuint64_t)D, (cuuint64_t)p.R, (cuuint64_t)a.B * a.Hkv};
+    const cuuint64_t strides[2] = {(cuuint64_t)D * 2, (cuuint64_t)p.R * D * 2};
+    const cuuint32_t box[3] = {64, (cuuint32_t)kRowsM, 1};
+    const cuuint32_t es[3] = {1, 1, 1};
+    const CUresult r = encode(&mq, dt, 3, const_cast<void*>(a.q), dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) { set_error("cuTensorMapEncodeTiled(q) failed with CUresult %d", (int)r); return DFLASH_ERR_CUDA; }
+  }
+  auto encode_kv = [&](CUtensorMap* m, const void* base) -> CUresult {
+    cuuint64_t dims[4], strides[3];
+    if (a.page_table) {
+      // pool [num_pages, Hkv, page_tokens, D]; the page count is not passed: bound it by the table's range
+      dims[0] = D; dims[1] = a.page_tokens; dims[2] = a.Hkv; dims[3] = (cuuint64_t)1 << 22;
+      strides[0] = (cuuint64_t)D * 2; strides[1] = (cuuint64_t)a.page_tokens * D * 2; strides[2] = (cuuint64_t)a.Hkv * a.page_tokens * D * 2;
+    } else {
+      dims[0] = D; dims[1] = a.N; dims[2] = a.Hkv; dims[3] = a.B;
+      strides[0] = (cuuint64_t)D * 2; strides[1] = (cuuint64_t)a.N * D * 2; strides[2] = (cuuint64_t)a.Hkv * a.N * D * 2;
+    }
+    const cuuint32_t box[4] = {64, (cuuint32_t)kBlockN, 1, 1};
+    const cuuint32_t es[4] = {1, 1, 1, 1};
+    return encode(m, dt, 4, const_cast<void*>(base), dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  };
+  CUresult r = encode_kv(&mk, a.k);
+  if (r == CUDA_SUCCESS) r = encode_kv(&mv, a.v);
+  if (r != CUDA_SUCCESS) { set_error("cuTensorMapEncodeTiled(k/v) failed with CUresult %d", (int)r); return DFLASH_ERR_CUDA; }
+
+  auto kernel = sdpa_tc_kernel<InT, D>;
+  DFLASH_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SL::alloc));
+  kernel<<<(unsigned)grid, kThreads, SL::alloc, stream>>>(mq, mk, mv, p);
+  DFLASH_LAUNCH_CHECK();
+  count_launch();
+  sdpa_tc_merge_kernel<InT, D><<<dim3(p.units, kRowsM / 16), 256, 0, stream>>>(p, (int)(2 * grid));
+  DFLASH_LAUNCH_CHECK();
+  count_launch();
+  return DFLASH_OK;
+}
+
+}  // namespace
+
+size_t sdpa_workspace_bytes(int B, int Hq, int Hkv, int D, int N) {
+  (void)Hkv; (void)N;
+  const size_t simple = sdpa_simple_workspace_bytes(B, Hq, D);
+  const size_t tc = tc_workspace_bytes(D);
+  return (simple > tc ? simple : tc) + 256;
+}
+
+bool sdpa_tc_supported(const SdpaArgs& a) {
+  if (a.mask) return false;                          // additive masks take the general path
+  if (a.D != 128 && a.D != 256) return false;
+  if (a.dtype != DFLASH_BF16 && a.dtype != DFLASH_F16) return false;
+  if (a.kv_len && a.B > 4096) return false;
+  if (!(a.scale > 0.f)) return false;                // the running maximum assumes a positive scale
+  if (!a.workspace || a.workspace_bytes < tc_workspace_bytes(a.D)) return false;
+  return true;
+}
+
+int32_t launch_sdpa_tc(const SdpaArgs& a, cudaStream_t stream) {
+  if (a.dtype == DFLASH_BF16) return a.D == 256 ? launch_typed<__nv_bfloat16, 256>(a, stream) : launch_typed<__nv_bfloat16, 128>(a, stream);
+  return a.D == 256 ? launch_typed<__half, 256>(a, stream) : launch_typed<__half, 128>(a, stream);
+}
+
 }  // namespace dflash

@@ -1,0 +1,112 @@
+"""CPU tests of the host-side mirror: rollback-cache indexing contract (integer, exact),
+partition plans, and the N > 1 path over gloo with two CPU ranks."""
+import os
+import socket
+import sys
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from oracle import dflash_oracle as O
+from swiftlm_b200 import partition
+from swiftlm_b200.rollback_cache import RecurrentRollbackCache, restore_after_acceptance
+
+
+def test_conv_window_rebuild_matches_oracle_exactly():
+    c = RecurrentRollbackCache(conv_kernel_size=4)
+    snap = torch.arange(2 * 3 * 5).reshape(2, 3, 5).float()
+    qkv = 100 + torch.arange(2 * 16 * 5).reshape(2, 16, 5).float()
+    c.state = [snap, None]
+    c.arm_rollback()
+    c.record_tape(None, None, None, qkv)
+    for steps in (1, 2, 7, 16):
+        got = c.rebuild_conv_state(steps)
+        want = O.rebuild_conv_state(snap.numpy(), qkv.numpy(), steps, 4)
+        np.testing.assert_array_equal(got.numpy(), want)
+    # per-sequence step counts: each row equals the scalar rule for its own count
+    steps = torch.tensor([3, 12])
+    got = c.rebuild_conv_state(steps)
+    for b in range(2):
+        want = O.rebuild_conv_state(snap.numpy()[b:b + 1], qkv.numpy()[b:b + 1], int(steps[b]), 4)
+        np.testing.assert_array_equal(got[b:b + 1].numpy(), want)
+    # no snapshot -> zero prefix; kernel size 1 -> no window
+    c2 = RecurrentRollbackCache(conv_kernel_size=4)
+    c2.arm_rollback()
+    c2.record_tape(None, None, None, qkv)
+    np.testing.assert_array_equal(c2.rebuild_conv_state(1).numpy(), O.rebuild_conv_state(None, qkv.numpy(), 1, 4))
+    c3 = RecurrentRollbackCache(conv_kernel_size=1)
+    c3.arm_rollback()
+    c3.record_tape(None, None, None, qkv)
+    assert c3.rebuild_conv_state(1) is None
+
+
+def test_arm_record_clear_and_full_accept_shortcut():
+    c = RecurrentRollbackCache()
+    assert not c.is_armed
+    c.state = [torch.zeros(1, 3, 4), torch.ones(1, 2, 8, 8)]
+    c.arm_rollback(prefix_len=7)
+    assert c.is_armed and c._snapshot[1] is c.state[1]          # snapshot by reference, no copy
+    c.state[1] = torch.full((1, 2, 8, 8), 5.0)                  # the verify pass moved the state on
+    c.record_tape(torch.zeros(1, 16, 2, 8), torch.zeros(1, 16, 1, 8), torch.zeros(1, 16, 2), torch.zeros(1, 16, 4))
+    restore_after_acceptance([c], target_len=10, acceptance_length=15, drafted_tokens=15)
+    assert not c.is_armed and c._tape is None and float(c.state[1][0, 0, 0, 0]) == 5.0   # kept the verify state
+    c.offset = 20
+    assert c.trim(6) == 6 and c.offset == 14 and c.trim(100) == 14 and c.offset == 0
+    # rollback without a snapshot only clears
+    c.rollback(3)
+    assert not c.is_armed
+
+
+def test_partition_helpers():
+    assert partition.plan(64, 8) == [(8 * i, 8 * i + 8) for i in range(8)]
+    assert partition.sequences_for_rank(10, 3, 4) == (8, 10)
+    pairs = [partition.kv_pairs_for_rank(8, 2, r, 8) for r in range(8)]
+    assert pairs[0] == [(0, 0), (0, 1)] and pairs[7] == [(7, 0), (7, 1)]
+    assert sorted(sum(pairs, [])) == [(s, h) for s in range(8) for h in range(2)]
+    odd = [partition.kv_pairs_for_rank(5, 2, r, 4) for r in range(4)]
+    assert [len(x) for x in odd] == [3, 3, 2, 2] and len(set(sum(odd, []))) == 10
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    return port
+
+
+def _gloo_worker(rank, world, port, n_seq, out_dir):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    lo, hi = partition.sequences_for_rank(n_seq, rank, world)
+    # each rank "verifies" its own sequences: acceptance from the CPU oracle on seeded tokens
+    rng = np.random.default_rng(99)
+    post = rng.integers(0, 50, (n_seq, 16)).astype(np.int32)
+    ids = np.concatenate([rng.integers(0, 50, (n_seq, 1)), post[:, :-1]], axis=1).astype(np.int32)
+    for b in range(n_seq):
+        cut = rng.integers(0, 16)
+        if cut < 15:
+            ids[b, cut + 1] = (ids[b, cut + 1] + 1) % 50
+    acc_local, nxt_local = [], []
+    for b in range(lo, hi):
+        a, _, staged = O.accept_block(ids[b], post[b])
+        acc_local.append(a)
+        nxt_local.append(staged)
+    acc, nxt = partition.all_gather_acceptance(torch.tensor(acc_local, dtype=torch.int32),
+                                               torch.tensor(nxt_local, dtype=torch.int32), n_seq)
+    want = [O.accept_block(ids[b], post[b]) for b in range(n_seq)]
+    assert acc.tolist() == [w[0] for w in want] and nxt.tolist() == [w[2] for w in want]
+    dist.barrier()
+    dist.destroy_process_group()
+    open(os.path.join(out_dir, f"ok{rank}"), "w").close()
+
+
+@pytest.mark.parametrize("n_seq", [64, 7])
+def test_sequence_sharded_step_with_gloo_all_gather(tmp_path, n_seq):
+    world = 2
+    port = _free_port()
+    mp.spawn(_gloo_worker, args=(world, port, n_seq, str(tmp_path)), nprocs=world, join=True)
+    assert all(os.path.exists(tmp_path / f"ok{r}") for r in range(world))
