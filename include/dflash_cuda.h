@@ -102,6 +102,21 @@ int32_t dflash_verify_sdpa(const void* q, const void* k, const void* v, const in
 
 size_t dflash_verify_sdpa_workspace_bytes(int32_t B, int32_t Hq, int32_t Hkv, int32_t D, int32_t N);
 
+/* Same computation as dflash_verify_sdpa for a caller that cannot supply scratch memory (a host
+ * whose device-memory budget is fixed and whose allocator is closed to plug-ins, or a request path
+ * that must never reach cudaMalloc).  It has no counterpart in the reference.  The split-KV
+ * partials live in a 40 MiB device array that is part of the library image (every GPU that loads
+ * the library holds it until exit): enough for head_dim <= 256 on up to 158 SMs; a call that needs
+ * more returns DFLASH_ERR_WORKSPACE.  Nothing is allocated.  The first call on a device resolves
+ * the array's address and loads the kernels: make it before any stream capture.  All calls share
+ * the array (it keeps the previous call's contents; nothing needs clearing), so calls that
+ * overlap on the GPU race: serialise them. */
+int32_t dflash_verify_sdpa_noalloc(const void* q, const void* k, const void* v, const int32_t* page_table,
+                                   const int32_t* kv_len_per_seq, const void* mask, void* out, int32_t B,
+                                   int32_t Hq, int32_t Hkv, int32_t T, int32_t D, int32_t N,
+                                   int32_t page_tokens, int32_t max_pages, float scale, int32_t dtype,
+                                   int32_t kv_format, void* stream);
+
 /* ---------------------------------------------------------------------------------------------
  * Acceptance bookkeeping on the device (no host round trip of the accepted length).
  * dflash_greedy_tokens replaces DFlashRuntime.greedyTokensWithMask,
