@@ -6,14 +6,14 @@
 // (128 FLOP/B), so the kernel is organised around keeping TMA loads in flight; the tensor
 // pipe and the softmax run in the shadow of the loads.
 //
-// One persistent CTA per SM (no cluster, cta_group::1, no multicast), 6 warps:
+// One persistent CTA per SM (no cluster, cta_group::1, no multicast), 10 warps:
 //   warp 0     TMA producer: Q tile (4 boxes of 128 rows x 64 elements) and a ring of 16 KiB
 //              K / V boxes (128 keys x 64 elements, 128-byte swizzle), order K0 K1 V0 K2 V1 ...
 //   warp 1     MMA issuer (one lane): S = Q K^T (128 x 128 x D, both operands in shared memory,
 //              K-major) into one of two S buffers in tensor memory; O += P V with P read from
 //              tensor memory (bf16, aliasing the S buffer) and V MN-major from shared memory.
 //              Owns the tensor-memory allocation.
-//   warps 2-5  softmax: one thread per query row.  Loads its row of S from tensor memory,
+//   warps 2-9  softmax: two threads per query row (64 key columns each).  Loads its part of S,
 //              applies the block-causal rule on the last tiles, keeps a running reference
 //              maximum and sum, writes P (bf16) back to tensor memory, rescales O only when the
 //              maximum grew by more than 2^8, and at the end of a segment normalises and stores.
@@ -42,7 +42,7 @@ namespace {
 constexpr int kBlockN = 128;            // keys per tile
 constexpr int kRowsM = 128;             // query rows per unit tile
 constexpr int kChunkBytes = 128 * 128;  // one TMA box: 128 rows x 64 16-bit elements
-constexpr int kThreads = 192;
+constexpr int kThreads = 320;          // TMA warp, MMA warp, 8 softmax warps
 constexpr float kRescaleThreshold = 8.f;   // in log2 units
 
 struct TcParams {
@@ -73,8 +73,10 @@ struct Smem {
   static constexpr int b_kv_empty = 8 + kStages;     // kStages
   static constexpr int n_bars = 8 + 2 * kStages;
   static constexpr uint32_t misc = bars + 8 * n_bars;   // tmem base, abort flag, range info
-  static constexpr uint32_t total = misc + 64;
-  static constexpr uint32_t alloc = total + 1024;
+  static constexpr uint32_t xseq = misc + 64;            // exchange sequence numbers [2][2][4]
+  static constexpr uint32_t xch = xseq + 64;             // exchange values [2 slots][2 halves][128 rows]
+  static constexpr uint32_t total = xch + 2 * 2 * 128 * 4;
+  static constexpr uint32_t alloc = total;               // the dynamic shared window starts 1024-byte aligned (checked)
 };
 
 // ---- work decomposition -------------------------------------------------------------------
@@ -172,8 +174,12 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
   constexpr uint32_t kTmemCols = 512;
   constexpr uint32_t kColO = 0, kColS = D;          // O: D columns; S buffers: 2 x 128 columns
 
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* sm = smem_raw + ((1024u - (ptx::smem_u32(smem_raw) & 1023u)) & 1023u);
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* sm = smem_raw;
+  if ((ptx::smem_u32(sm) & 1023u) != 0u) {   // swizzled tiles need 1024-byte alignment; never seen violated
+    if (threadIdx.x == 0) atomicExch(p.status, 4);
+    return;
+  }
   uint64_t* bars = reinterpret_cast<uint64_t*>(sm + SL::bars);
   uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(sm + SL::misc);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(sm + SL::misc + 4);
@@ -196,9 +202,10 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
   if (threadIdx.x == 0) {
     for (int i = 0; i < SL::n_bars; ++i) {
       const bool four = (i == SL::b_o_free) || (i == SL::b_p_full) || (i == SL::b_p_full + 1);
-      ptx::mbar_init(&bars[i], four ? 4 : 1);
+      ptx::mbar_init(&bars[i], four ? 8 : 1);
     }
     *abort_flag = 0;
+    for (int i = 0; i < 16; ++i) reinterpret_cast<volatile uint32_t*>(sm + SL::xseq)[i] = 0;
     // locate (unit, tile) of `begin`
     int unit = 0, tile = 0;
     if (!a.kv_len) {
@@ -303,13 +310,14 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
               ok = wait_or_abort(&bars[SL::b_kv_full + stage], (drain / kStages) & 1, abort_flag, p.status);
               if (!ok) break;
               ptx::tc_fence_after();
-              const uint32_t k_addr = ptx::smem_u32(sm + SL::ring + stage * kChunkBytes);
-#pragma unroll
-              for (int kk = 0; kk < 4; ++kk) {   // 4 x 16 elements per 64-element chunk
-                const uint64_t da = make_desc(q_addr + c * kChunkBytes + kk * 32, 16, 1024);
-                const uint64_t db = make_desc(k_addr + kk * 32, 16, 1024);
-                ptx::umma_ss(d_tmem, da, db, kIdescQK, (c | kk) ? 1u : 0u);
-              }
+              // descriptors differ only in the start-address field: +2 (32 bytes) per 16-element step
+              const uint64_t da0 = make_desc(q_addr + c * kChunkBytes, 16, 1024);
+              const uint64_t db0 = make_desc(ptx::smem_u32(sm + SL::ring + stage * kChunkBytes), 16, 1024);
+              if (c == 0) ptx::umma_ss_first(d_tmem, da0, db0, kIdescQK);
+              else ptx::umma_ss_acc(d_tmem, da0, db0, kIdescQK);
+              ptx::umma_ss_acc(d_tmem, da0 + 2, db0 + 2, kIdescQK);
+              ptx::umma_ss_acc(d_tmem, da0 + 4, db0 + 4, kIdescQK);
+              ptx::umma_ss_acc(d_tmem, da0 + 6, db0 + 6, kIdescQK);
               ptx::umma_commit(&bars[SL::b_kv_empty + stage]);   // K chunk free once these products retire
               ++drain;
             }
@@ -334,12 +342,14 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
               ok = wait_or_abort(&bars[SL::b_kv_full + stage], (drain / kStages) & 1, abort_flag, p.status);
               if (!ok) break;
               ptx::tc_fence_after();
-              const uint32_t v_addr = ptx::smem_u32(sm + SL::ring + stage * kChunkBytes);
+              // 16 keys per instruction: +128 (2048 bytes) in the start-address field, +8 P columns
+              const uint64_t db0 = make_desc(ptx::smem_u32(sm + SL::ring + stage * kChunkBytes), kChunkBytes, 1024);
+              const uint32_t o_tmem = tmem_base + kColO + c * 64;
+              if (jj > 1) ptx::umma_ts_acc(o_tmem, p_tmem, db0, kIdescPV);
+              else ptx::umma_ts_first(o_tmem, p_tmem, db0, kIdescPV);
 #pragma unroll
-              for (int kk = 0; kk < kBlockN / 16; ++kk) {   // 16 keys per instruction
-                const uint64_t db = make_desc(v_addr + kk * 2048, kChunkBytes, 1024);
-                ptx::umma_ts(tmem_base + kColO + c * 64, p_tmem + kk * 8, db, kIdescPV, (jj > 1 || kk > 0) ? 1u : 0u);
-              }
+              for (int kk = 1; kk < kBlockN / 16; ++kk)
+                ptx::umma_ts_acc(o_tmem, p_tmem + kk * 8, db0 + (uint64_t)kk * 128, kIdescPV);
               ptx::umma_commit(&bars[SL::b_kv_empty + stage]);
               ++drain;
             }
@@ -353,21 +363,52 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     }
   } else {
     // ====================================== softmax ======================================
+    // Two threads per query row: warps 2-5 take key columns 0-63 of every tile (and the lower
+    // half of O's columns), warps 6-9 columns 64-127 (upper half).  Both warps of a pair touch
+    // the same tensor-memory lane quarter.  The two partial row maxima of a tile (and the two
+    // partial sums at the end of a segment) are exchanged through shared memory.
     const int wq = warp & 3;                       // tensor-memory lane quarter this warp may touch
+    const int half = (warp - 2) >> 2;              // which 64 key columns / which half of O
     const int row = wq * 32 + lane;                // query row of the unit tile = tensor-memory lane
     const uint32_t lane_addr = (uint32_t)(wq * 32) << 16;
+    float* xch = reinterpret_cast<float*>(sm + SL::xch);                 // [2 slots][2 halves][128 rows]
+    volatile uint32_t* xseq = reinterpret_cast<volatile uint32_t*>(sm + SL::xseq);   // [2 slots][2 halves][4 quarters]
+    uint32_t xcount = 0;                            // exchanges done so far (same in both halves)
+    // publish `mine`, return the partner's value for the same row; false if the partner never came
+    auto exchange = [&](float mine, float& theirs) -> bool {
+      const uint32_t slot = xcount & 1u;
+      xch[(slot * 2 + half) * kRowsM + row] = mine;
+      __syncwarp();
+      __threadfence_block();
+      if (lane == 0) xseq[(slot * 2 + half) * 4 + wq] = xcount + 1;
+      bool got = false;
+      for (uint32_t i = 0; i < ptx::kWaitPolls; ++i) {
+        if (xseq[(slot * 2 + (half ^ 1)) * 4 + wq] >= xcount + 1) { got = true; break; }
+        if ((i & 63u) == 63u && *abort_flag) break;
+      }
+      got = __all_sync(0xffffffffu, got);
+      if (!got) {
+        if (lane == 0 && !*abort_flag) { *abort_flag = 1; atomicExch(p.status, 3); }
+        return false;
+      }
+      __threadfence_block();
+      theirs = xch[(slot * 2 + (half ^ 1)) * kRowsM + row];
+      ++xcount;
+      return true;
+    };
     if (begin < end) {
       SegmentIter it(p, begin, end, unit0, tile0);
       Segment s;
       uint32_t seg_idx = 0, tile_ctr = 0;
       bool ok = true;
+      constexpr int kOHalf = D / 2;                 // O columns handled by this thread
       while (ok && it.next(s)) {
         const int ntiles = s.tile_hi - s.tile_lo;
         const int rr = s.mt * kRowsM + row;          // row inside the (b, kvh) group
         const int tok = rr & 15;                     // draft token index of this row
         const int last_visible = s.n_keys - 16 + tok;
-        float m_ref = -INFINITY;                     // reference maximum (raw score units)
-        float l_sum = 0.f;
+        float m_ref = -INFINITY;                     // reference maximum (raw score units), same in both halves
+        float l_sum = 0.f;                           // this half's share of the row sum
         for (int jj = 0; ok && jj < ntiles; ++jj) {
           const uint32_t t = tile_ctr + jj, buf = t & 1;
           const int j = s.tile_lo + jj;
@@ -376,22 +417,28 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
           if (!ok) break;
           ptx::tc_fence_after();
           const uint32_t s_addr = tmem_base + lane_addr + kColS + buf * kBlockN;
-          uint32_t sr[4][32];
-#pragma unroll
-          for (int q4 = 0; q4 < 4; ++q4) ptx::tmem_ld32(s_addr + q4 * 32, sr[q4]);
+          uint32_t sr[2][32];
+          ptx::tmem_ld32(s_addr + half * 64, sr[0]);
+          ptx::tmem_ld32(s_addr + half * 64 + 32, sr[1]);
           ptx::tmem_ld_wait();
-          const int n_base = j * kBlockN;
-          const bool edge = n_base + kBlockN - 1 > s.n_keys - 16;   // tile touches the block keys or the end
-          float mx = -INFINITY;
+          const int n_base = j * kBlockN + half * 64;
+          if (n_base + 63 > s.n_keys - 16) {        // this half touches the block keys or the end
 #pragma unroll
-          for (int q4 = 0; q4 < 4; ++q4)
+            for (int q2 = 0; q2 < 2; ++q2)
 #pragma unroll
-            for (int i = 0; i < 32; ++i) {
-              float v = __uint_as_float(sr[q4][i]);
-              if (edge && n_base + q4 * 32 + i > last_visible) v = -INFINITY;
-              sr[q4][i] = __float_as_uint(v);
-              mx = fmaxf(mx, v);
-            }
+              for (int i = 0; i < 32; ++i)
+                if (n_base + q2 * 32 + i > last_visible) sr[q2][i] = __float_as_uint(-INFINITY);
+          }
+          float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+          for (int q2 = 0; q2 < 2; ++q2)
+#pragma unroll
+            for (int i = 0; i < 32; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(sr[q2][i]));
+          float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+          float other;
+          ok = exchange(mx, other);
+          if (!ok) break;
+          mx = fmaxf(mx, other);
           // lazy rescale: move the reference only when the maximum grew by more than 2^8
           float factor = 1.f;
           const bool grow = (mx > m_ref) && ((mx - m_ref) * p.scale_log2 > kRescaleThreshold || m_ref == -INFINITY);
@@ -400,44 +447,45 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
             m_ref = mx;
           }
           const bool need_rescale = jj > 0 && __any_sync(0xffffffffu, grow);
+          l_sum *= factor;
+          const float neg_ref = (m_ref == -INFINITY) ? 0.f : -m_ref * p.scale_log2;
+          uint32_t pr[32];
+          float add4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+          for (int q2 = 0; q2 < 2; ++q2)
+#pragma unroll
+            for (int i = 0; i < 32; i += 2) {
+              const float p0 = fast_exp2(fmaf(__uint_as_float(sr[q2][i]), p.scale_log2, neg_ref));
+              const float p1 = fast_exp2(fmaf(__uint_as_float(sr[q2][i + 1]), p.scale_log2, neg_ref));
+              add4[(i >> 1) & 3] += p0 + p1;
+              pr[q2 * 16 + (i >> 1)] = pack2<InT>(p0, p1);
+            }
+          l_sum += (add4[0] + add4[1]) + (add4[2] + add4[3]);
           if (jj > 0) {
             // Every phase of the product barrier is waited for exactly once and in order (a
             // parity wait that skips a phase cannot tell "done" from "two phases behind").
-            // The next product cannot start before this one retires anyway.
+            // It sits after the exponentials: the next product cannot start before the
+            // previous one retires anyway, so nothing is lost by waiting here.
             ok = wait_or_abort(&bars[SL::b_pv_done], (t - 1) & 1, abort_flag, p.status);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
           }
           if (need_rescale) {
-            // O holds the products up to tile j-1: scale this row
+            // O holds the products up to tile j-1: scale this row's half of the columns
             ptx::tc_fence_after();
 #pragma unroll 1
-            for (int c = 0; c < D / 32; ++c) {
+            for (int c = 0; c < kOHalf / 32; ++c) {
               uint32_t o[32];
-              ptx::tmem_ld32(tmem_base + lane_addr + kColO + c * 32, o);
+              const uint32_t o_addr = tmem_base + lane_addr + kColO + half * kOHalf + c * 32;
+              ptx::tmem_ld32(o_addr, o);
               ptx::tmem_ld_wait();
 #pragma unroll
               for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * factor);
-              ptx::tmem_st32(tmem_base + lane_addr + kColO + c * 32, o);
+              ptx::tmem_st32(o_addr, o);
             }
             ptx::tmem_st_wait();
           }
-          l_sum *= factor;
-          const float neg_ref = (m_ref == -INFINITY) ? 0.f : -m_ref * p.scale_log2;
-          uint32_t pr[2][32];
-          float add = 0.f;
-#pragma unroll
-          for (int q4 = 0; q4 < 4; ++q4)
-#pragma unroll
-            for (int i = 0; i < 32; i += 2) {
-              const float p0 = fast_exp2(fmaf(__uint_as_float(sr[q4][i]), p.scale_log2, neg_ref));
-              const float p1 = fast_exp2(fmaf(__uint_as_float(sr[q4][i + 1]), p.scale_log2, neg_ref));
-              add += p0 + p1;
-              pr[q4 >> 1][(q4 & 1) * 16 + (i >> 1)] = pack2<InT>(p0, p1);
-            }
-          l_sum += add;
-          ptx::tmem_st32(s_addr, pr[0]);
-          ptx::tmem_st32(s_addr + 32, pr[1]);
+          ptx::tmem_st32(s_addr + half * 32, pr);   // P: 16-bit pairs, key 2c and 2c+1 in column c
           ptx::tmem_st_wait();
           ptx::tc_fence_before();
           __syncwarp();
@@ -450,16 +498,20 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
           ok = wait_or_abort(&bars[SL::b_pv_done], t_last & 1, abort_flag, p.status);
           ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
+          float l_other;
+          ok = exchange(l_sum, l_other);
+          if (!ok) break;
+          const float l_tot = half == 0 ? l_sum + l_other : l_other + l_sum;   // same order in both halves
           ptx::tc_fence_after();
           const bool valid = rr < p.R;
           if (s.slot < 0) {
-            const float inv = l_sum == 0.f ? 1.f : 1.f / l_sum;
+            const float inv = l_tot == 0.f ? 1.f : 1.f / l_tot;
             InT* orow = reinterpret_cast<InT*>(a.out) +
-                        ((((long long)s.b * a.Hq + (long long)s.kvh * p.G + (rr >> 4)) * 16) + tok) * D;
+                        ((((long long)s.b * a.Hq + (long long)s.kvh * p.G + (rr >> 4)) * 16) + tok) * D + half * kOHalf;
 #pragma unroll 1
-            for (int c = 0; c < D / 32; ++c) {
+            for (int c = 0; c < kOHalf / 32; ++c) {
               uint32_t o[32];
-              ptx::tmem_ld32(tmem_base + lane_addr + kColO + c * 32, o);
+              ptx::tmem_ld32(tmem_base + lane_addr + kColO + half * kOHalf + c * 32, o);
               ptx::tmem_ld_wait();
               if (valid) {
                 uint32_t w[16];
@@ -472,19 +524,21 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
               }
             }
           } else {
-            float* prow = p.part_o + ((long long)s.slot * kRowsM + row) * D;
+            float* prow = p.part_o + ((long long)s.slot * kRowsM + row) * D + half * kOHalf;
 #pragma unroll 1
-            for (int c = 0; c < D / 32; ++c) {
+            for (int c = 0; c < kOHalf / 32; ++c) {
               uint32_t o[32];
-              ptx::tmem_ld32(tmem_base + lane_addr + kColO + c * 32, o);
+              ptx::tmem_ld32(tmem_base + lane_addr + kColO + half * kOHalf + c * 32, o);
               ptx::tmem_ld_wait();
 #pragma unroll
               for (int i = 0; i < 8; ++i)
                 *reinterpret_cast<uint4*>(prow + c * 32 + i * 4) = make_uint4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
             }
-            p.part_m[(long long)s.slot * kRowsM + row] = (m_ref == -INFINITY) ? -INFINITY : m_ref * p.scale_log2;
-            p.part_l[(long long)s.slot * kRowsM + row] = l_sum;
-            if (row == 0) p.slot_unit[s.slot] = s.unit;
+            if (half == 0) {
+              p.part_m[(long long)s.slot * kRowsM + row] = (m_ref == -INFINITY) ? -INFINITY : m_ref * p.scale_log2;
+              p.part_l[(long long)s.slot * kRowsM + row] = l_tot;
+              if (row == 0) p.slot_unit[s.slot] = s.unit;
+            }
           }
           ptx::tc_fence_before();
           __syncwarp();
