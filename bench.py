@@ -375,13 +375,59 @@ def run_sdpa(torch, kernels, device, args, peaks):
                                  "caps this shape at ~49% of dense bf16 peak"}}
 
 
+def run_case(args):
+    """Small single-kernel cases for profiler captures (a few hundred MB to ~1.5 GB on the device):
+    replay_small = 16 of the 64 sequences of configs[1]; sdpa_small = configs[2] itself (0.28 GB)."""
+    import torch
+
+    from swiftlm_b200 import kernels
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(0)
+    if args.case == "replay_small":
+        cfg = dict(CFG1, B_seq=16)
+        x = make_replay_inputs(torch, device, SEED + 1000, cfg)
+        y = torch.empty_like(x["v"])
+        out = torch.empty_like(x["state"])
+        for _ in range(args.warmup + args.steps):
+            kernels.gated_delta_into(x["q"], x["k"], x["v"], x["g"], x["beta"], x["state"], x["n"], y, out)
+        units = cfg["B_seq"] * cfg["L"] * cfg["Hv"]
+        alg = replay_bytes(float(x["n"].sum().item()) * cfg["Hv"], units)
+        info = {"case": args.case, "head_states": units, "algorithmic_bytes_per_launch": alg}
+    elif args.case == "delta_replay_small":
+        cfg = dict(CFG1, B_seq=16)
+        x = make_replay_inputs(torch, device, SEED + 1000, cfg)
+        tape = torch.randn(x["v"].shape, device=device)
+        for _ in range(args.warmup + args.steps):
+            kernels.tape_replay_kernel(tape, x["k"], x["g"], x["state"], n_per_seq=x["n"])
+        units = cfg["B_seq"] * cfg["L"] * cfg["Hv"]
+        info = {"case": args.case, "head_states": units,
+                "algorithmic_bytes_per_launch": units * 131072.0 + 642.0 * float(x["n"].sum().item()) * cfg["Hv"]}
+    else:
+        cfg = CFG2
+        g = torch.Generator(device=device).manual_seed(SEED + 2000)
+        q = torch.randn(cfg["B"], cfg["Hq"], 16, cfg["D"], device=device, generator=g).bfloat16()
+        k = torch.randn(cfg["B"], cfg["Hkv"], cfg["N"], cfg["D"], device=device, generator=g).bfloat16()
+        v = torch.randn(cfg["B"], cfg["Hkv"], cfg["N"], cfg["D"], device=device, generator=g).bfloat16()
+        out = torch.empty_like(q)
+        for _ in range(args.warmup + args.steps):
+            kernels.batched_sdpa_2pass(q, k, v, 1.0 / 16.0, out=out)
+        info = {"case": args.case, "flops_per_launch": sdpa_flops(), "algorithmic_bytes_per_launch": sdpa_bytes()}
+    torch.cuda.synchronize()
+    kernels.device_status()
+    print(json.dumps(info))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--case", default=None, choices=["replay_small", "delta_replay_small", "sdpa_small"],
+                    help="run one small single-kernel case (for profiler captures) instead of the benchmark")
     args = ap.parse_args()
+    if args.case:
+        return run_case(args)
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
     if args.impl == "reference":
         run_reference(args)

@@ -136,6 +136,23 @@ int32_t dflash_accept_lengths(const uint32_t* posterior, const int32_t* verify_i
                               void* stream);
 
 /* ---------------------------------------------------------------------------------------------
+ * TurboQuant 3-bit KV codec, 128-dimension blocks (a 256-dimension head vector is two blocks).
+ * Follows the codec as stated in the reference's tests/test_turbo_quant.cpp: V path :69-75, K path
+ * with residual sign bits :85-98, primitives :14-22 (the production encoder lives in a dependency
+ * that is not part of the reference tree).  Results are bit-identical to that statement.
+ *   x / out  [n_blocks,128] dtype (f32, bf16, f16)
+ *   packed   uint8[n_blocks,48]  3-bit centroid indices, little-endian bit stream
+ *   signs    uint8[n_blocks,16]  K only: sign bits of the rotated residual (NULL for V)
+ *   norm     uint16[n_blocks]    fp16 bits: ||k|| (K) or ||v|| / ||centroid vector|| (V)
+ *   rnorm    uint16[n_blocks]    K only: fp16 bits of the residual norm (NULL for V)
+ */
+int32_t dflash_turbo_encode(const void* x, uint8_t* packed, uint8_t* signs, uint16_t* norm, uint16_t* rnorm,
+                            int64_t n_blocks, int32_t is_key, int32_t in_dtype, void* stream);
+int32_t dflash_turbo_decode(const uint8_t* packed, const uint8_t* signs, const uint16_t* norm,
+                            const uint16_t* rnorm, void* out, int64_t n_blocks, int32_t is_key,
+                            int32_t out_dtype, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
  * Host-side helpers.
  */
 /* Splits `units` independent work units (sequences for replay, (sequence, KV head) pairs for

@@ -185,6 +185,23 @@ int32_t dflash_accept_lengths(const uint32_t* posterior, const int32_t* verify_i
                                reinterpret_cast<cudaStream_t>(stream));
 }
 
+int32_t dflash_turbo_encode(const void* x, uint8_t* packed, uint8_t* signs, uint16_t* norm, uint16_t* rnorm,
+                            int64_t n_blocks, int32_t is_key, int32_t in_dtype, void* stream) {
+  if (!x || !packed || !norm || (is_key && (!signs || !rnorm))) return bad("null tensor pointer");
+  if (n_blocks <= 0) return bad("non-positive dimension");
+  return launch_turbo_encode(x, packed, signs, norm, rnorm, n_blocks, is_key ? 1 : 0, in_dtype,
+                             reinterpret_cast<cudaStream_t>(stream));
+}
+
+int32_t dflash_turbo_decode(const uint8_t* packed, const uint8_t* signs, const uint16_t* norm,
+                            const uint16_t* rnorm, void* out, int64_t n_blocks, int32_t is_key,
+                            int32_t out_dtype, void* stream) {
+  if (!packed || !norm || !out || (is_key && (!signs || !rnorm))) return bad("null tensor pointer");
+  if (n_blocks <= 0) return bad("non-positive dimension");
+  return launch_turbo_decode(packed, signs, norm, rnorm, out, n_blocks, is_key ? 1 : 0, out_dtype,
+                             reinterpret_cast<cudaStream_t>(stream));
+}
+
 int32_t dflash_partition_plan(int32_t units, int32_t n_gpus, int32_t* begin_end_host) {
   if (units < 0 || n_gpus <= 0 || !begin_end_host) return bad("partition_plan arguments");
   const int base = units / n_gpus, extra = units % n_gpus;

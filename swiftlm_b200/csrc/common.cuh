@@ -118,4 +118,9 @@ int32_t launch_accept_lengths(const uint32_t* posterior, const int32_t* verify_i
                               int32_t* next_token, int32_t* replay_len, int B, int T,
                               cudaStream_t stream);
 
+int32_t launch_turbo_encode(const void* x, uint8_t* packed, uint8_t* signs, uint16_t* norm, uint16_t* rnorm,
+                            long long n, int is_key, int in_dtype, cudaStream_t stream);
+int32_t launch_turbo_decode(const uint8_t* packed, const uint8_t* signs, const uint16_t* norm, const uint16_t* rnorm,
+                            void* out, long long n, int is_key, int out_dtype, cudaStream_t stream);
+
 }  // namespace dflash

@@ -1,0 +1,215 @@
+// TurboQuant 3-bit KV codec on the GPU, 128-dimension blocks.
+//
+// Follows the codec as the reference states it in tests/test_turbo_quant.cpp of the SwiftLM
+// tree: L2 normalisation, sign-flip / Walsh-Hadamard rotation (:14-17), nearest of 8 centroids
+// by boundary search (:18), little-endian 3-bit packing (:19-20), fp16 norms by truncation
+// (:21-22); V stores fp16(norm / centroid-vector norm) (:69-74); K additionally stores the sign
+// bits of the QJL-rotated residual and its fp16 norm and decodes as
+// (centroids rotated back + QJL_C/128 * rnorm * qrot(signs)) * norm (:85-98).
+// A head vector of 256 dimensions is two independent 128-blocks.
+//
+// The codec is integer/byte work whose results must match the reference bit for bit, so every
+// floating-point operation is performed in the reference's order with explicitly rounded
+// adds and multiplies (no fused multiply-add): one thread owns one 128-block and walks it
+// sequentially in shared memory (element i of thread t at [i][t]: conflict-free).
+#include "common.cuh"
+#include "turbo_tables.cuh"
+
+namespace dflash {
+namespace {
+
+constexpr int kBlock = 128;
+constexpr int kThreadsPerCta = 64;
+
+__device__ __forceinline__ float sgn(const unsigned int* neg, int i) { return (neg[i >> 5] >> (i & 31)) & 1u ? -1.f : 1.f; }
+
+struct Vec {   // a 128-vector in shared memory, strided by the CTA width
+  float* p;
+  __device__ __forceinline__ float& operator[](int i) const { return p[i * kThreadsPerCta]; }
+};
+
+__device__ void fwht128(const Vec& x) {   // :14
+  for (int h = 1; h < kBlock; h *= 2)
+    for (int i = 0; i < kBlock; i += 2 * h)
+      for (int j = i; j < i + h; ++j) {
+        const float a = x[j], b = x[j + h];
+        x[j] = __fadd_rn(a, b);
+        x[j + h] = __fsub_rn(a, b);
+      }
+  for (int i = 0; i < kBlock; ++i) x[i] = __fmul_rn(x[i], 0.08838834764831845f);
+}
+__device__ void rot(const Vec& x, const unsigned int* first, const unsigned int* second) {   // :15-17
+  for (int i = 0; i < kBlock; ++i) x[i] = __fmul_rn(x[i], sgn(first, i));
+  fwht128(x);
+  for (int i = 0; i < kBlock; ++i) x[i] = __fmul_rn(x[i], sgn(second, i));
+}
+__device__ __forceinline__ int nearest3(float v) {   // :18
+  int idx = 0;
+#pragma unroll
+  for (int i = 0; i < 7; ++i) idx += !(v < TURBO_B3[i]);
+  return idx;
+}
+__device__ __forceinline__ uint16_t to_f16_trunc(float f) {   // :21
+  const uint32_t u = __float_as_uint(f);
+  const uint16_t s = (uint16_t)((u >> 16) & 0x8000u);
+  const int32_t e = (int32_t)((u >> 23) & 0xFF) - 127 + 15;
+  const uint32_t m = u & 0x7FFFFFu;
+  if (e <= 0) return s;
+  if (e >= 31) return (uint16_t)(s | 0x7C00u);
+  return (uint16_t)(s | (uint16_t)(e << 10) | (uint16_t)(m >> 13));
+}
+__device__ __forceinline__ float from_f16_bits(uint16_t h) {   // :22
+  const uint32_t s = (uint32_t)(h & 0x8000u) << 16, e = (h >> 10) & 0x1Fu, m = h & 0x3FFu;
+  uint32_t u;
+  if (!e) u = s;
+  else if (e == 31) u = s | (0xFFu << 23) | m;
+  else u = s | ((e + 127 - 15) << 23) | (m << 13);
+  return __uint_as_float(u);
+}
+
+template <typename InT>
+__global__ void __launch_bounds__(kThreadsPerCta)
+turbo_encode_kernel(const InT* __restrict__ x, uint8_t* __restrict__ packed, uint8_t* __restrict__ signs,
+                    uint16_t* __restrict__ norm, uint16_t* __restrict__ rnorm, long long n, int is_key) {
+  extern __shared__ float sh[];
+  const long long v = (long long)blockIdx.x * kThreadsPerCta + threadIdx.x;
+  if (v >= n) return;
+  const Vec nrm{sh + threadIdx.x};                                        // normalised input
+  const Vec rotv{sh + kBlock * kThreadsPerCta + threadIdx.x};             // work vector
+  const InT* src = x + v * kBlock;
+  float ns = 0.f;
+  for (int i = 0; i < kBlock; ++i) {
+    const float f = to_f32(src[i]);
+    rotv[i] = f;
+    ns = __fadd_rn(ns, __fmul_rn(f, f));
+  }
+  const float gn = __fsqrt_rn(ns), inv = gn > 1e-10f ? __fdiv_rn(1.f, gn) : 0.f;
+  for (int i = 0; i < kBlock; ++i) {
+    const float f = __fmul_rn(rotv[i], inv);
+    nrm[i] = f;
+    rotv[i] = f;
+  }
+  rot(rotv, TURBO_S1_NEG, TURBO_S2_NEG);
+  // 3-bit indices: pack as a little-endian bit stream (:19), 8 indices -> 3 bytes
+  uint8_t* pk = packed + v * 48;
+  float rs = 0.f;
+  for (int g8 = 0; g8 < 16; ++g8) {
+    uint32_t bits = 0;
+    for (int e = 0; e < 8; ++e) {
+      const int idx = nearest3(rotv[g8 * 8 + e]);
+      bits |= (uint32_t)idx << (3 * e);
+      rs = __fadd_rn(rs, __fmul_rn(TURBO_C3[idx], TURBO_C3[idx]));
+      rotv[g8 * 8 + e] = TURBO_C3[idx];                                   // centroid vector, for the K residual
+    }
+    pk[3 * g8] = (uint8_t)bits;
+    pk[3 * g8 + 1] = (uint8_t)(bits >> 8);
+    pk[3 * g8 + 2] = (uint8_t)(bits >> 16);
+  }
+  if (!is_key) {
+    const float rn2 = __fsqrt_rn(rs);
+    norm[v] = to_f16_trunc(rn2 > 1e-10f ? __fdiv_rn(gn, rn2) : gn);        // :73
+    return;
+  }
+  rot(rotv, TURBO_S2_NEG, TURBO_S1_NEG);                                   // inverse rotation of the centroids (:91)
+  float rns = 0.f;
+  for (int i = 0; i < kBlock; ++i) {
+    const float r = __fsub_rn(nrm[i], rotv[i]);
+    rotv[i] = r;
+    rns = __fadd_rn(rns, __fmul_rn(r, r));
+  }
+  rot(rotv, TURBO_Q1_NEG, TURBO_Q2_NEG);                                   // :93
+  uint8_t* sg = signs + v * 16;
+  for (int byte = 0; byte < 16; ++byte) {
+    uint32_t m = 0;
+    for (int e = 0; e < 8; ++e) m |= (rotv[byte * 8 + e] >= 0.f ? 1u : 0u) << e;
+    sg[byte] = (uint8_t)m;
+  }
+  norm[v] = to_f16_trunc(gn);
+  rnorm[v] = to_f16_trunc(__fsqrt_rn(rns));
+}
+
+template <typename OutT>
+__global__ void __launch_bounds__(kThreadsPerCta)
+turbo_decode_kernel(const uint8_t* __restrict__ packed, const uint8_t* __restrict__ signs,
+                    const uint16_t* __restrict__ norm, const uint16_t* __restrict__ rnorm, OutT* __restrict__ out,
+                    long long n, int is_key) {
+  extern __shared__ float sh[];
+  const long long v = (long long)blockIdx.x * kThreadsPerCta + threadIdx.x;
+  if (v >= n) return;
+  const Vec dec{sh + threadIdx.x};
+  const Vec sf{sh + kBlock * kThreadsPerCta + threadIdx.x};
+  const uint8_t* pk = packed + v * 48;
+  for (int g8 = 0; g8 < 16; ++g8) {
+    const uint32_t bits = pk[3 * g8] | ((uint32_t)pk[3 * g8 + 1] << 8) | ((uint32_t)pk[3 * g8 + 2] << 16);
+    for (int e = 0; e < 8; ++e) dec[g8 * 8 + e] = TURBO_C3[(bits >> (3 * e)) & 7u];
+  }
+  rot(dec, TURBO_S2_NEG, TURBO_S1_NEG);
+  const float sc = from_f16_bits(norm[v]);
+  OutT* dst = out + v * kBlock;
+  if (!is_key) {
+    for (int i = 0; i < kBlock; ++i) dst[i] = from_f32<OutT>(__fmul_rn(dec[i], sc));           // :75
+    return;
+  }
+  const uint8_t* sg = signs + v * 16;
+  for (int i = 0; i < kBlock; ++i) sf[i] = (sg[i >> 3] >> (i & 7)) & 1u ? 1.f : -1.f;
+  rot(sf, TURBO_Q1_NEG, TURBO_Q2_NEG);
+  const float qs = __fmul_rn(__fdiv_rn(TURBO_QJL_C, 128.f), from_f16_bits(rnorm[v]));           // :98
+  for (int i = 0; i < kBlock; ++i)
+    dst[i] = from_f32<OutT>(__fmul_rn(__fadd_rn(dec[i], __fmul_rn(sf[i], qs)), sc));
+}
+
+}  // namespace
+
+int32_t launch_turbo_encode(const void* x, uint8_t* packed, uint8_t* signs, uint16_t* norm, uint16_t* rnorm,
+                            long long n, int is_key, int in_dtype, cudaStream_t stream) {
+  const unsigned grid = (unsigned)((n + kThreadsPerCta - 1) / kThreadsPerCta);
+  const size_t smem = 2 * kBlock * kThreadsPerCta * sizeof(float);
+  switch (in_dtype) {
+    case DFLASH_F32:
+      DFLASH_CUDA_CHECK(cudaFuncSetAttribute(turbo_encode_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+      turbo_encode_kernel<float><<<grid, kThreadsPerCta, smem, stream>>>((const float*)x, packed, signs, norm, rnorm, n, is_key);
+      break;
+    case DFLASH_BF16:
+      DFLASH_CUDA_CHECK(cudaFuncSetAttribute(turbo_encode_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+      turbo_encode_kernel<__nv_bfloat16><<<grid, kThreadsPerCta, smem, stream>>>((const __nv_bfloat16*)x, packed, signs, norm, rnorm, n, is_key);
+      break;
+    case DFLASH_F16:
+      DFLASH_CUDA_CHECK(cudaFuncSetAttribute(turbo_encode_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+      turbo_encode_kernel<__half><<<grid, kThreadsPerCta, smem, stream>>>((const __half*)x, packed, signs, norm, rnorm, n, is_key);
+      break;
+    default:
+      set_error("turbo_encode: unsupported dtype %d", in_dtype);
+      return DFLASH_ERR_UNSUPPORTED;
+  }
+  DFLASH_LAUNCH_CHECK();
+  count_launch();
+  return DFLASH_OK;
+}
+
+int32_t launch_turbo_decode(const uint8_t* packed, const uint8_t* signs, const uint16_t* norm, const uint16_t* rnorm,
+                            void* out, long long n, int is_key, int out_dtype, cudaStream_t stream) {
+  const unsigned grid = (unsigned)((n + kThreadsPerCta - 1) / kThreadsPerCta);
+  const size_t smem = 2 * kBlock * kThreadsPerCta * sizeof(float);
+  switch (out_dtype) {
+    case DFLASH_F32:
+      DFLASH_CUDA_CHECK(cudaFuncSetAttribute(turbo_decode_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+      turbo_decode_kernel<float><<<grid, kThreadsPerCta, smem, stream>>>(packed, signs, norm, rnorm, (float*)out, n, is_key);
+      break;
+    case DFLASH_BF16:
+      DFLASH_CUDA_CHECK(cudaFuncSetAttribute(turbo_decode_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+      turbo_decode_kernel<__nv_bfloat16><<<grid, kThreadsPerCta, smem, stream>>>(packed, signs, norm, rnorm, (__nv_bfloat16*)out, n, is_key);
+      break;
+    case DFLASH_F16:
+      DFLASH_CUDA_CHECK(cudaFuncSetAttribute(turbo_decode_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+      turbo_decode_kernel<__half><<<grid, kThreadsPerCta, smem, stream>>>(packed, signs, norm, rnorm, (__half*)out, n, is_key);
+      break;
+    default:
+      set_error("turbo_decode: unsupported dtype %d", out_dtype);
+      return DFLASH_ERR_UNSUPPORTED;
+  }
+  DFLASH_LAUNCH_CHECK();
+  count_launch();
+  return DFLASH_OK;
+}
+
+}  // namespace dflash

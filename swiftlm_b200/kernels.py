@@ -222,3 +222,34 @@ def gated_delta_into(q, k, v, g, beta, state, n_per_seq, y, state_out, tape=None
         _ptr(q), _ptr(k), _ptr(v), _ptr(g), _ptr(beta), _ptr(state), _ptr(mask_t), _ptr(n_per_seq),
         _ptr(y), _ptr(state_out), _ptr(tape), B, T, Hk, Hv, Dk, Dv, int(g.dim() == 4), _DT[q.dtype], mdt,
         _stream()))
+
+
+def turbo_encode(x: torch.Tensor, is_key: bool):
+    """TurboQuant 3-bit encode of 128-dimension blocks (tests/test_turbo_quant.cpp:69-74 for V,
+    :85-94 for K in the reference tree).  x [..., 128*m]; returns packed uint8 [..., m, 48],
+    signs uint8 [..., m, 16] or None (V), norm and rnorm (or None) as fp16 bit patterns in int16 tensors."""
+    _need_cuda(x)
+    if x.shape[-1] % 128 != 0:
+        raise _lib.DFlashUnsupported(_lib.ERR_UNSUPPORTED, "last dimension must be a multiple of 128")
+    x = x.contiguous()
+    lead = tuple(x.shape[:-1]) + (x.shape[-1] // 128,)
+    n = x.numel() // 128
+    packed = torch.empty(lead + (48,), dtype=torch.uint8, device=x.device)
+    norm = torch.empty(lead, dtype=torch.int16, device=x.device)
+    signs = torch.empty(lead + (16,), dtype=torch.uint8, device=x.device) if is_key else None
+    rnorm = torch.empty(lead, dtype=torch.int16, device=x.device) if is_key else None
+    _lib.check(_lib.lib().dflash_turbo_encode(_ptr(x), _ptr(packed), _ptr(signs), _ptr(norm), _ptr(rnorm), n,
+                                             int(is_key), _DT[x.dtype], _stream()))
+    return packed, signs, norm, rnorm
+
+
+def turbo_decode(packed, signs, norm, rnorm, dtype=torch.bfloat16) -> torch.Tensor:
+    """Inverse of turbo_encode (tests/test_turbo_quant.cpp:74-75 and :96-98): returns [..., 128*m]."""
+    _need_cuda(packed, norm)
+    is_key = signs is not None
+    lead = tuple(norm.shape)
+    n = norm.numel()
+    out = torch.empty(lead[:-1] + (lead[-1] * 128,), dtype=dtype, device=packed.device)
+    _lib.check(_lib.lib().dflash_turbo_decode(_ptr(packed.contiguous()), _ptr(signs), _ptr(norm.contiguous()),
+                                             _ptr(rnorm), _ptr(out), n, int(is_key), _DT[dtype], _stream()))
+    return out
