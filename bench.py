@@ -47,13 +47,12 @@ def measured_peaks():
     return dict(hbm_gbs=6650.0, bf16_tflops=1590.0, bf16_tflops_sustained=1400.0, source="fallback")
 
 
-def profiled_traffic():
-    """DRAM bytes per unit from the committed ncu summaries (profiles/traffic.json), or {}."""
-    path = os.path.join(ROOT, "profiles", "traffic.json")
-    if os.path.exists(path):
-        with open(path) as f:
-            return json.load(f)
-    return {}
+# DRAM bytes moved per algorithmic byte, from the committed ncu captures (dram__bytes_read.sum +
+# dram__bytes_write.sum of one launch on a smaller case of the same kernel; traffic grows in
+# proportion to the units processed):
+#   profiles/gdn_fast_forward_replay_small.md   2.5559 GB moved / 2.5627 GB algorithmic
+#   profiles/sdpa_tc_sdpa_small.md              284.4 MB (main kernel) + 27.0 MB (merge) / 277.9 MB
+TRAFFIC_PER_ALGORITHMIC_BYTE = {"gdn_fast_forward": 0.9974, "sdpa_tc": 1.1205}
 
 
 class ClockSampler:
@@ -276,7 +275,7 @@ def run_gpu(args):
     ms_per_step = total_ms / args.steps
     value = world * heads / (ms_per_step * 1e-3)
     achieved_gbs = alg_bytes / (kernel_ms * 1e-3) / 1e9
-    traffic = profiled_traffic().get("gdn_fast_forward", {}).get("dram_bytes_per_algorithmic_byte")
+    traffic = TRAFFIC_PER_ALGORITHMIC_BYTE["gdn_fast_forward"]
 
     # ---- end to end through the host-buffer API (rank-local pinned buffers) ----
     e2e_steps = max(1, min(args.steps, 3))
@@ -324,7 +323,7 @@ def run_gpu(args):
                      "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved_gbs / peaks["hbm_gbs"],
                      "peak_source": peaks["source"], "algorithmic_bytes_per_launch": alg_bytes,
                      "kernel_ms": kernel_ms,
-                     "traffic": None if traffic is None else traffic * alg_bytes},
+                     "traffic": traffic * alg_bytes},
         "cpu_baseline": cpu,
         "e2e": {"value": e2e_value, "unit": "head-states/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "ms_per_step": e2e_ms, "steps": e2e_steps,
@@ -370,6 +369,7 @@ def run_sdpa(torch, kernels, device, args, peaks):
             "config": "configs[2]: B=32, Hq=16, Hkv=2, T=16, D=256, N=4096+16, bf16, scale 1/16; 3 rotating K/V sets",
             "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                          "frac": gbs / peaks["hbm_gbs"], "algorithmic_bytes_per_launch": sdpa_bytes(),
+                         "traffic": TRAFFIC_PER_ALGORITHMIC_BYTE["sdpa_tc"] * sdpa_bytes(),
                          "frac_of_bf16_peak": tflops / peaks["bf16_tflops"],
                          "note": "arithmetic intensity 128 FLOP/B is below the ridge (~252): the HBM roofline "
                                  "caps this shape at ~49% of dense bf16 peak"}}
