@@ -74,6 +74,17 @@ def build(force: bool = False, verbose: bool = False) -> str:
         if r.returncode != 0:
             sys.stderr.write(r.stdout + r.stderr)
             raise RuntimeError("link failed")
+    # host program: the kernel micro-benchmark (counterpart of the reference's DFlashKernelBench)
+    bench_src = os.path.join(PKG, "host", "dflash_kernel_bench.cu")
+    bench_bin = os.path.join(PKG, "bin", "dflash_kernel_bench")
+    os.makedirs(os.path.dirname(bench_bin), exist_ok=True)
+    if force or _newer(bench_bin, [bench_src, LIB] + headers):
+        cmd = [nvcc, "-std=c++17", "-O2", "-gencode", "arch=compute_100a,code=sm_100a", bench_src, "-o", bench_bin,
+               "-L" + LIBDIR, "-ldflash_cuda", "-Xlinker", "-rpath", "-Xlinker", "$ORIGIN/../lib"]
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode != 0:
+            sys.stderr.write(r.stdout + r.stderr)
+            raise RuntimeError("building dflash_kernel_bench failed")
     return LIB
 
 

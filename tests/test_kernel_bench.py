@@ -1,0 +1,32 @@
+"""The C++ micro-benchmark (counterpart of the reference's Sources/DFlashKernelBench/main.swift)."""
+import os
+import re
+import subprocess
+
+import pytest
+
+from swiftlm_b200 import build
+
+BIN = os.path.join(os.path.dirname(build.__file__), "bin", "dflash_kernel_bench")
+
+
+def test_bench_binary_is_built():
+    build.build()
+    assert os.access(BIN, os.X_OK)
+
+
+@pytest.mark.gpu
+def test_bench_runs_every_section():
+    build.build()
+    r = subprocess.run([BIN, "--iterations", "5", "--warmup", "2", "--kernels", "tape,gdelta,sdpa"],
+                       capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stdout + r.stderr
+    lines = [l for l in r.stdout.splitlines() if " med " in l]
+    # 4 replay variants + 4 forward variants + 3 context lengths (main.swift:127-137, 172-186, 204)
+    assert len(lines) == 11, r.stdout
+    for l in lines:
+        m = re.search(r"med\s+([\d.]+) us\s+min\s+([\d.]+) us\s+max\s+([\d.]+) us\s+([\d.]+) GB/s", l)
+        assert m, l
+        med, mn, mx = float(m.group(1)), float(m.group(2)), float(m.group(3))
+        assert 0 < mn <= med <= mx
+    assert r.stdout.rstrip().endswith("Done.")
