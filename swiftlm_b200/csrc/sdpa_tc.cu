@@ -20,7 +20,14 @@
 // KV is split across CTAs stream-K style: the (unit, 128-key tile) pairs of the whole batch
 // are cut into one contiguous range per CTA, so every CTA streams the same number of tiles.
 // A range that covers a whole unit writes the output directly; the others write fp32 partials
-// (unnormalised O, reference maximum, sum) that a small second kernel merges.
+// (unnormalised O, reference maximum, sum).  Where a unit is cut into at most kFusedMax ranges
+// the CTA that finishes last merges them itself: every range publishes a per-launch tag in an
+// arrival flag after its partials, then looks at the flags of the unit's other ranges; whoever
+// sees them all set does the merge (two CTAs finishing together may both do it and store the same
+// bytes).  Nobody waits for anybody.  Units cut into more ranges (long context, small batch) are
+// merged by a second kernel with one block per 16 rows.  When the units divide the SMs well
+// (units * c >= 80 % of the SMs for an integer c <= kFusedMax) every unit is cut into exactly c
+// equal ranges instead, so that no CTA pays for two range epilogues.
 //
 // Semantics: Sources/DFlash/DFlashKernels.swift:563-649 (partials) and :661-720 (reduce):
 // visibility n <= N_b - 16 + r, fp32 scores and accumulation, zero-sum guard.  Differences:
@@ -28,10 +35,35 @@
 // with a pre-scaled exponent instead of exp.
 #include <cuda.h>
 
+#include <atomic>
+#include <cstdlib>
+#include <random>
 #include <type_traits>
 
 #include "common.cuh"
 #include "ptx.cuh"
+
+// Optional timeline instrumentation (compile with -DDFLASH_SDPA_TRACE; never part of the shipped
+// library): per CTA 64 words of %globaltimer stamps and clock64 wait accumulators.
+#ifdef DFLASH_SDPA_TRACE
+__device__ unsigned long long g_sdpa_trace[256 * 64];
+__device__ __forceinline__ unsigned long long gtime() { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
+#define TR_STAMP(i) do { g_sdpa_trace[blockIdx.x * 64 + (i)] = gtime(); } while (0)
+#define TR_T0() const long long tr_t0_ = clock64()
+#define TR_DECL() long long tr_acc_[8] = {0, 0, 0, 0, 0, 0, 0, 0}
+#define TR_ACC(i) do { tr_acc_[(i) - 16] += clock64() - tr_t0_; } while (0)
+#define TR_FLUSH(lo, hi) do { for (int i_ = (lo); i_ <= (hi); ++i_) g_sdpa_trace[blockIdx.x * 64 + i_] = (unsigned long long)tr_acc_[i_ - 16]; } while (0)
+extern "C" int dflash_debug_trace(unsigned long long* out, int n, int clear) {
+  if (clear) { static unsigned long long z[256 * 64]; return (int)cudaMemcpyToSymbol(g_sdpa_trace, z, sizeof z); }
+  return (int)cudaMemcpyFromSymbol(out, g_sdpa_trace, sizeof(unsigned long long) * n);
+}
+#else
+#define TR_STAMP(i) do {} while (0)
+#define TR_T0() do {} while (0)
+#define TR_ACC(i) do {} while (0)
+#define TR_DECL() do {} while (0)
+#define TR_FLUSH(lo, hi) do {} while (0)
+#endif
 
 namespace dflash {
 
@@ -44,6 +76,7 @@ constexpr int kRowsM = 128;             // query rows per unit tile
 constexpr int kChunkBytes = 128 * 128;  // one TMA box: 128 rows x 64 16-bit elements
 constexpr int kThreads = 320;          // TMA warp, MMA warp, 8 softmax warps
 constexpr float kRescaleThreshold = 8.f;   // in log2 units
+constexpr int kFusedMax = 4;               // a unit cut into at most this many ranges is merged by its last finisher
 
 struct TcParams {
   SdpaArgs a;
@@ -51,8 +84,11 @@ struct TcParams {
   int units;               // B * Hkv * MT
   long long total_tiles;   // only valid when kv_len == nullptr
   float scale_log2;
-  int* slot_unit;          // [2 * gridDim.x]
-  float* part_o;           // [2 * gridDim.x][128][D]
+  int split;               // 0: stream-K ranges; c > 0: every unit cut into c equal ranges (uniform N only)
+  unsigned long long epoch;            // tag of this launch, never 0
+  unsigned long long* flags;           // [2 * gridDim.x] arrival flags (hold the epoch of the launch that set them)
+  int* slot_unit;          // [2 * gridDim.x]; -1: empty, or merged inside the main kernel
+  float* part_o;           // [2 * gridDim.x][D / 4][128 rows][4]: a warp's 32 rows store 512 contiguous bytes
   float* part_m;           // [2 * gridDim.x][128]  (reference maximum, log2 units)
   float* part_l;           // [2 * gridDim.x][128]
   int* status;
@@ -61,7 +97,7 @@ struct TcParams {
 template <int D>
 struct Smem {
   static constexpr int kQChunks = D / 64;
-  static constexpr int kStages = (D == 256) ? 10 : 12;
+  static constexpr int kStages = (D == 256) ? 10 : 12;   // even: V chunks are consumed in pairs
   static constexpr uint32_t q = 0;
   static constexpr uint32_t ring = kQChunks * kChunkBytes;
   static constexpr uint32_t bars = ring + kStages * kChunkBytes;
@@ -72,7 +108,7 @@ struct Smem {
   static constexpr int b_kv_full = 8;                // kStages
   static constexpr int b_kv_empty = 8 + kStages;     // kStages
   static constexpr int n_bars = 8 + 2 * kStages;
-  static constexpr uint32_t misc = bars + 8 * n_bars;   // tmem base, abort flag, range info
+  static constexpr uint32_t misc = bars + 8 * n_bars;   // tmem base, abort flag, range info, group counter, merge decision
   static constexpr uint32_t xseq = misc + 64;            // exchange sequence numbers [2][2][4]
   static constexpr uint32_t xch = xseq + 64;             // exchange values [2 slots][2 halves][128 rows]
   static constexpr uint32_t total = xch + 2 * 2 * 128 * 4;
@@ -86,7 +122,32 @@ struct Segment {
   int n_keys;      // N_b
   int tile_lo, tile_hi, tiles_in_unit;
   int slot;        // -1: covers the whole unit, write the output directly
+  long long unit_begin;   // global tile position of the unit's tile 0
 };
+
+// The decomposition: which global tile positions a CTA owns, and which CTA owns a position.
+__device__ __forceinline__ void cta_range(const TcParams& p, long long total, int cta, long long& begin, long long& end) {
+  if (p.split > 0) {
+    const long long tpu = (p.a.N + kBlockN - 1) / kBlockN;
+    const long long u = cta / p.split, k = cta % p.split;
+    begin = u * tpu + tpu * k / p.split;
+    end = u * tpu + tpu * (k + 1) / p.split;
+  } else {
+    // never more ranges than tiles (ragged lengths can leave CTAs idle): no range is empty
+    const long long C = (long long)gridDim.x < total ? (long long)gridDim.x : total;
+    begin = cta < C ? total * cta / C : 0;
+    end = cta < C ? total * (cta + 1) / C : 0;
+  }
+}
+__device__ __forceinline__ int cta_of(const TcParams& p, long long total, long long pos) {
+  if (p.split > 0) {
+    const long long tpu = (p.a.N + kBlockN - 1) / kBlockN;
+    const long long u = pos / tpu, t = pos % tpu;
+    return (int)(u * p.split + ((t + 1) * p.split - 1) / tpu);
+  }
+  const long long C = (long long)gridDim.x < total ? (long long)gridDim.x : total;
+  return (int)(((pos + 1) * C - 1) / total);
+}
 
 __device__ __forceinline__ int tiles_of(const TcParams& p, int b) {
   const int n = p.a.kv_len ? p.a.kv_len[b] : p.a.N;
@@ -116,7 +177,10 @@ struct SegmentIter {
     const int take = left < avail ? (int)left : avail;
     s.tile_hi = tile + take;
     const bool whole = (s.tile_lo == 0 && s.tile_hi == s.tiles_in_unit);
-    s.slot = whole ? -1 : (first ? 2 * (int)blockIdx.x : 2 * (int)blockIdx.x + 1);
+    // a CTA has at most one range that continues a unit (its first) and one that opens a unit
+    // without finishing it (its last): slots 2i and 2i + 1
+    s.slot = whole ? -1 : (s.tile_lo > 0 ? 2 * (int)blockIdx.x : 2 * (int)blockIdx.x + 1);
+    s.unit_begin = pos - tile;
     first = 0;
     pos += take;
     tile = 0;
@@ -150,6 +214,16 @@ __device__ __forceinline__ float fast_exp2(float x) {   // ex2.approx: exp2(-inf
   return y;
 }
 
+__device__ __forceinline__ void st_release_u64(unsigned long long* p, unsigned long long v) {
+  asm volatile("st.release.gpu.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+__device__ __forceinline__ unsigned long long ld_acquire_u64(const unsigned long long* p) {
+  unsigned long long v;
+  asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void fence_sc() { asm volatile("fence.sc.gpu;" ::: "memory"); }
+
 template <typename T> __device__ __forceinline__ uint32_t pack2(float a, float b);
 template <> __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float a, float b) {
   const __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
@@ -170,7 +244,7 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
   constexpr uint32_t kFmt = sizeof(InT) == 2 && std::is_same<InT, __nv_bfloat16>::value ? 1u : 0u;
   // instruction descriptors: fp32 accumulate, A/B format, majors, N >> 3, M >> 4
   constexpr uint32_t kIdescQK = (1u << 4) | (kFmt << 7) | (kFmt << 10) | ((kBlockN >> 3) << 17) | ((kRowsM >> 4) << 24);
-  constexpr uint32_t kIdescPV = (1u << 4) | (kFmt << 7) | (kFmt << 10) | (1u << 16) | ((64u >> 3) << 17) | ((kRowsM >> 4) << 24);
+  constexpr uint32_t kIdescPV = (1u << 4) | (kFmt << 7) | (kFmt << 10) | (1u << 16) | ((128u >> 3) << 17) | ((kRowsM >> 4) << 24);
   constexpr uint32_t kTmemCols = 512;
   constexpr uint32_t kColO = 0, kColS = D;          // O: D columns; S buffers: 2 x 128 columns
 
@@ -187,6 +261,8 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const SdpaArgs& a = p.a;
+  if (threadIdx.x == 0) TR_STAMP(0);
+  TR_DECL();
 
   // ---- the CTA's tile range ----
   long long total = p.total_tiles;
@@ -196,15 +272,19 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     for (int b = 0; b < a.B; ++b) sum += tiles_of(p, b);
     total = sum * a.Hkv * p.MT;
   }
-  const long long C = gridDim.x;
-  const long long begin = total * blockIdx.x / C, end = total * (blockIdx.x + 1) / C;
+  long long begin, end;
+  cta_range(p, total, blockIdx.x, begin, end);
 
   if (threadIdx.x == 0) {
+    ptx::prefetch_tensormap(&map_q);
+    ptx::prefetch_tensormap(&map_k);
+    ptx::prefetch_tensormap(&map_v);
     for (int i = 0; i < SL::n_bars; ++i) {
       const bool four = (i == SL::b_o_free) || (i == SL::b_p_full) || (i == SL::b_p_full + 1);
       ptx::mbar_init(&bars[i], four ? 8 : 1);
     }
     *abort_flag = 0;
+    reinterpret_cast<volatile uint32_t*>(sm + SL::misc)[4] = 0;   // group counter
     for (int i = 0; i < 16; ++i) reinterpret_cast<volatile uint32_t*>(sm + SL::xseq)[i] = 0;
     // locate (unit, tile) of `begin`
     int unit = 0, tile = 0;
@@ -229,9 +309,6 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     range_info[0] = unit;
     range_info[1] = tile;
     ptx::fence_mbar_init();
-    ptx::prefetch_tensormap(&map_q);
-    ptx::prefetch_tensormap(&map_k);
-    ptx::prefetch_tensormap(&map_v);
     // slot table: rewritten below by the softmax warps for the slots this CTA uses
     p.slot_unit[2 * blockIdx.x] = -1;
     p.slot_unit[2 * blockIdx.x + 1] = -1;
@@ -240,11 +317,21 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     ptx::tmem_alloc(tmem_base_slot, kTmemCols);
     ptx::tmem_relinquish();
   }
-  ptx::tc_fence_before();
-  __syncthreads();
-  ptx::tc_fence_after();
-  const uint32_t tmem_base = *tmem_base_slot;
+  // The producer warp needs only what its own lane 0 set up (barriers, range): it arrives and goes
+  // on to issue loads while the other warps still wait for the tensor-memory allocation.
+  uint32_t tmem_base = 0;
+  if (warp == 0) {
+    __syncwarp();
+    __threadfence_block();
+    asm volatile("bar.arrive 1, %0;" ::"n"(kThreads) : "memory");
+  } else {
+    ptx::tc_fence_before();
+    asm volatile("bar.sync 1, %0;" ::"n"(kThreads) : "memory");
+    ptx::tc_fence_after();
+    tmem_base = *tmem_base_slot;
+  }
   const int unit0 = range_info[0], tile0 = range_info[1];
+  if (threadIdx.x == 0) TR_STAMP(1);
 
   if (warp == 0) {
     // =================================== TMA producer ===================================
@@ -256,8 +343,12 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       bool ok = true;
       auto load_chunk = [&](const CUtensorMap* map, const Segment& sg, int tile, int c) -> bool {
         const uint32_t stage = fill % kStages;
-        if (fill >= (uint32_t)kStages && !wait_or_abort(&bars[SL::b_kv_empty + stage], ((fill / kStages) - 1) & 1, abort_flag, p.status))
-          return false;
+        {
+          TR_T0();
+          if (fill >= (uint32_t)kStages && !wait_or_abort(&bars[SL::b_kv_empty + stage], ((fill / kStages) - 1) & 1, abort_flag, p.status))
+            return false;
+          TR_ACC(16);
+        }
         ptx::mbar_arrive_expect_tx(&bars[SL::b_kv_full + stage], kChunkBytes);
         const int n0 = tile * kBlockN;
         if (a.page_table) {
@@ -307,18 +398,27 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
             const uint32_t d_tmem = tmem_base + kColS + buf * kBlockN;
             for (int c = 0; ok && c < kQChunks; ++c) {
               const uint32_t stage = drain % kStages;
-              ok = wait_or_abort(&bars[SL::b_kv_full + stage], (drain / kStages) & 1, abort_flag, p.status);
+              {
+                TR_T0();
+                ok = wait_or_abort(&bars[SL::b_kv_full + stage], (drain / kStages) & 1, abort_flag, p.status);
+                TR_ACC(17);
+                if (drain == 0) TR_STAMP(2);
+              }
               if (!ok) break;
               ptx::tc_fence_after();
               // descriptors differ only in the start-address field: +2 (32 bytes) per 16-element step
               const uint64_t da0 = make_desc(q_addr + c * kChunkBytes, 16, 1024);
               const uint64_t db0 = make_desc(ptx::smem_u32(sm + SL::ring + stage * kChunkBytes), 16, 1024);
-              if (c == 0) ptx::umma_ss_first(d_tmem, da0, db0, kIdescQK);
-              else ptx::umma_ss_acc(d_tmem, da0, db0, kIdescQK);
-              ptx::umma_ss_acc(d_tmem, da0 + 2, db0 + 2, kIdescQK);
-              ptx::umma_ss_acc(d_tmem, da0 + 4, db0 + 4, kIdescQK);
-              ptx::umma_ss_acc(d_tmem, da0 + 6, db0 + 6, kIdescQK);
-              ptx::umma_commit(&bars[SL::b_kv_empty + stage]);   // K chunk free once these products retire
+              {
+                TR_T0();
+                if (c == 0) ptx::umma_ss_first(d_tmem, da0, db0, kIdescQK);
+                else ptx::umma_ss_acc(d_tmem, da0, db0, kIdescQK);
+                ptx::umma_ss_acc(d_tmem, da0 + 2, db0 + 2, kIdescQK);
+                ptx::umma_ss_acc(d_tmem, da0 + 4, db0 + 4, kIdescQK);
+                ptx::umma_ss_acc(d_tmem, da0 + 6, db0 + 6, kIdescQK);
+                ptx::umma_commit(&bars[SL::b_kv_empty + stage]);   // K chunk free once these products retire
+                TR_ACC(22);
+              }
               ++drain;
             }
             if (!ok) break;
@@ -333,25 +433,43 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
               ok = wait_or_abort(&bars[SL::b_o_free], (seg_idx - 1) & 1, abort_flag, p.status);
               if (!ok) break;
             }
-            ok = wait_or_abort(&bars[SL::b_p_full + buf], (t >> 1) & 1, abort_flag, p.status);
+            {
+              TR_T0();
+              ok = wait_or_abort(&bars[SL::b_p_full + buf], (t >> 1) & 1, abort_flag, p.status);
+              TR_ACC(19);
+            }
             if (!ok) break;
             ptx::tc_fence_after();
             const uint32_t p_tmem = tmem_base + kColS + buf * kBlockN;   // P (16-bit pairs) aliases S
-            for (int c = 0; ok && c < kQChunks; ++c) {
+            // Two 64-column V chunks per instruction (N = 128): an instruction costs about 100
+            // clocks whether N is 64 or 128.  The pair sits in consecutive ring stages (loads come
+            // in groups of kQChunks, kStages is even, so a pair never straddles the wrap); the
+            // descriptor's leading-dimension offset is the 16 KiB from one chunk to the next.
+            for (int cp = 0; ok && cp < kQChunks / 2; ++cp) {
               const uint32_t stage = drain % kStages;
-              ok = wait_or_abort(&bars[SL::b_kv_full + stage], (drain / kStages) & 1, abort_flag, p.status);
+              {
+                TR_T0();
+                ok = wait_or_abort(&bars[SL::b_kv_full + stage], (drain / kStages) & 1, abort_flag, p.status) &&
+                     wait_or_abort(&bars[SL::b_kv_full + stage + 1], (drain / kStages) & 1, abort_flag, p.status);
+                TR_ACC(18);
+              }
               if (!ok) break;
               ptx::tc_fence_after();
               // 16 keys per instruction: +128 (2048 bytes) in the start-address field, +8 P columns
               const uint64_t db0 = make_desc(ptx::smem_u32(sm + SL::ring + stage * kChunkBytes), kChunkBytes, 1024);
-              const uint32_t o_tmem = tmem_base + kColO + c * 64;
-              if (jj > 1) ptx::umma_ts_acc(o_tmem, p_tmem, db0, kIdescPV);
-              else ptx::umma_ts_first(o_tmem, p_tmem, db0, kIdescPV);
+              const uint32_t o_tmem = tmem_base + kColO + cp * 128;
+              {
+                TR_T0();
+                if (jj > 1) ptx::umma_ts_acc(o_tmem, p_tmem, db0, kIdescPV);
+                else ptx::umma_ts_first(o_tmem, p_tmem, db0, kIdescPV);
 #pragma unroll
-              for (int kk = 1; kk < kBlockN / 16; ++kk)
-                ptx::umma_ts_acc(o_tmem, p_tmem + kk * 8, db0 + (uint64_t)kk * 128, kIdescPV);
-              ptx::umma_commit(&bars[SL::b_kv_empty + stage]);
-              ++drain;
+                for (int kk = 1; kk < kBlockN / 16; ++kk)
+                  ptx::umma_ts_acc(o_tmem, p_tmem + kk * 8, db0 + (uint64_t)kk * 128, kIdescPV);
+                ptx::umma_commit(&bars[SL::b_kv_empty + stage]);
+                ptx::umma_commit(&bars[SL::b_kv_empty + stage + 1]);
+                TR_ACC(23);
+              }
+              drain += 2;
             }
             if (!ok) break;
             ptx::umma_commit(&bars[SL::b_pv_done]);
@@ -396,6 +514,30 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       ++xcount;
       return true;
     };
+    // Meeting point of the eight softmax warps (bounded like every other wait in this kernel).
+    volatile uint32_t* gctr = reinterpret_cast<volatile uint32_t*>(sm + SL::misc) + 4;
+    volatile int* merge_go = reinterpret_cast<volatile int*>(sm + SL::misc) + 5;
+    uint32_t gcount = 0;
+    auto group_sync = [&]() -> bool {
+      ++gcount;
+      __syncwarp();
+      if (lane == 0) {
+        __threadfence_block();
+        atomicAdd(const_cast<uint32_t*>(gctr), 1u);
+      }
+      bool got = false;
+      for (uint32_t i = 0; i < ptx::kWaitPolls; ++i) {
+        if (*gctr >= gcount * 8u) { got = true; break; }
+        if ((i & 63u) == 63u && *abort_flag) break;
+      }
+      got = __all_sync(0xffffffffu, got);
+      if (!got) {
+        if (lane == 0 && !*abort_flag) { *abort_flag = 1; atomicExch(p.status, 5); }
+        return false;
+      }
+      __threadfence_block();
+      return true;
+    };
     if (begin < end) {
       SegmentIter it(p, begin, end, unit0, tile0);
       Segment s;
@@ -412,7 +554,11 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         for (int jj = 0; ok && jj < ntiles; ++jj) {
           const uint32_t t = tile_ctr + jj, buf = t & 1;
           const int j = s.tile_lo + jj;
-          ok = wait_or_abort(&bars[SL::b_s_full + buf], (t >> 1) & 1, abort_flag, p.status);
+          {
+            TR_T0();
+            ok = wait_or_abort(&bars[SL::b_s_full + buf], (t >> 1) & 1, abort_flag, p.status);
+            TR_ACC(20); if (threadIdx.x == 64) { if (t == 0) TR_STAMP(3); if (t < 40) TR_STAMP(24 + t); }
+          }
           ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
           ptx::tc_fence_after();
@@ -466,7 +612,9 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
             // parity wait that skips a phase cannot tell "done" from "two phases behind").
             // It sits after the exponentials: the next product cannot start before the
             // previous one retires anyway, so nothing is lost by waiting here.
+            TR_T0();
             ok = wait_or_abort(&bars[SL::b_pv_done], (t - 1) & 1, abort_flag, p.status);
+            TR_ACC(21);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
           }
@@ -495,9 +643,11 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         // ---- segment epilogue: wait for the last product, then normalise / store ----
         {
           const uint32_t t_last = tile_ctr + ntiles - 1;
+          if (threadIdx.x == 64) TR_STAMP(4 + 4 * (seg_idx > 0));
           ok = wait_or_abort(&bars[SL::b_pv_done], t_last & 1, abort_flag, p.status);
           ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
+          if (threadIdx.x == 64) TR_STAMP(5 + 4 * (seg_idx > 0));
           float l_other;
           ok = exchange(l_sum, l_other);
           if (!ok) break;
@@ -524,22 +674,149 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
               }
             }
           } else {
-            float* prow = p.part_o + ((long long)s.slot * kRowsM + row) * D + half * kOHalf;
+            // ---- partial range: publish (O, m, l); merge here if this CTA is the unit's last finisher ----
+            const float m_log2 = (m_ref == -INFINITY) ? -INFINITY : m_ref * p.scale_log2;
+            float* pslot = p.part_o + (long long)s.slot * kRowsM * D;
 #pragma unroll 1
-            for (int c = 0; c < kOHalf / 32; ++c) {
-              uint32_t o[32];
-              ptx::tmem_ld32(tmem_base + lane_addr + kColO + half * kOHalf + c * 32, o);
+            for (int c = 0; c < kOHalf / 32; c += 2) {
+              uint32_t o[2][32];
+              ptx::tmem_ld32(tmem_base + lane_addr + kColO + half * kOHalf + c * 32, o[0]);
+              ptx::tmem_ld32(tmem_base + lane_addr + kColO + half * kOHalf + c * 32 + 32, o[1]);
               ptx::tmem_ld_wait();
+              const int col4 = (half * kOHalf + c * 32) >> 2;
 #pragma unroll
-              for (int i = 0; i < 8; ++i)
-                *reinterpret_cast<uint4*>(prow + c * 32 + i * 4) = make_uint4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
+              for (int h2 = 0; h2 < 2; ++h2)
+#pragma unroll
+                for (int i = 0; i < 8; ++i)
+                  *reinterpret_cast<uint4*>(pslot + ((long long)(col4 + h2 * 8 + i) * kRowsM + row) * 4) =
+                      make_uint4(o[h2][4 * i], o[h2][4 * i + 1], o[h2][4 * i + 2], o[h2][4 * i + 3]);
             }
             if (half == 0) {
-              p.part_m[(long long)s.slot * kRowsM + row] = (m_ref == -INFINITY) ? -INFINITY : m_ref * p.scale_log2;
+              p.part_m[(long long)s.slot * kRowsM + row] = m_log2;
               p.part_l[(long long)s.slot * kRowsM + row] = l_tot;
-              if (row == 0) p.slot_unit[s.slot] = s.unit;
+            }
+            // the unit's ranges live in CTAs cta_first .. cta_last
+            const int cta_first = cta_of(p, total, s.unit_begin);
+            const int cta_last = cta_of(p, total, s.unit_begin + s.tiles_in_unit - 1);
+            const int nseg = cta_last - cta_first + 1;
+            if (nseg > kFusedMax) {
+              if (half == 0 && row == 0) p.slot_unit[s.slot] = s.unit;      // left to the merge kernel
+            } else {
+              // the group's stores are ordered before the leader's release by the meeting point
+              // (block scope) followed by the leader's device-scope fence
+              ok = group_sync();
+              if (!ok) break;
+              if (threadIdx.x == 64) TR_STAMP(6 + 4 * (seg_idx > 0));
+              if (warp == 2 && lane == 0) {
+                __threadfence();
+                st_release_u64(p.flags + s.slot, p.epoch);
+                fence_sc();
+                bool all = true;
+                for (int i = cta_first; i <= cta_last; ++i) {
+                  const int sl = (i == cta_first) ? 2 * i + 1 : 2 * i;
+                  if (sl != s.slot) all = all && (ld_acquire_u64(p.flags + sl) == p.epoch);
+                }
+                *merge_go = all ? 1 : 0;
+              }
+              ok = group_sync();
+              if (!ok) break;
+              if (*merge_go) {
+                // slot order = key order; this CTA's own range takes its place in the same order,
+                // so the result does not depend on which CTA merges
+                float f[kFusedMax], mmax = -INFINITY, den = 0.f;
+                int sl[kFusedMax];
+#pragma unroll
+                for (int i = 0; i < kFusedMax; ++i) {
+                  sl[i] = (i == 0) ? 2 * cta_first + 1 : 2 * (cta_first + i);
+                  f[i] = -INFINITY;
+                  if (i < nseg) {
+                    f[i] = sl[i] == s.slot ? m_log2 : __ldcg(p.part_m + (long long)sl[i] * kRowsM + row);
+                    mmax = fmaxf(mmax, f[i]);
+                  }
+                }
+#pragma unroll
+                for (int i = 0; i < kFusedMax; ++i) {
+                  f[i] = (f[i] == -INFINITY) ? 0.f : exp2f(f[i] - mmax);
+                  if (i < nseg) den += f[i] * (sl[i] == s.slot ? l_tot : __ldcg(p.part_l + (long long)sl[i] * kRowsM + row));
+                }
+                const float inv = den == 0.f ? 1.f : 1.f / den;
+                InT* orow = reinterpret_cast<InT*>(a.out) +
+                            ((((long long)s.b * a.Hq + (long long)s.kvh * p.G + (rr >> 4)) * 16) + tok) * D + half * kOHalf;
+                auto store32 = [&](int c, const float (&acc)[32]) {
+                  if (valid) {
+                    uint32_t w[16];
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) w[i] = pack2<InT>(acc[2 * i] * inv, acc[2 * i + 1] * inv);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i)
+                      *reinterpret_cast<uint4*>(orow + c * 32 + i * 8) = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
+                  }
+                };
+                if (nseg == 2) {
+                  // the common case: the other range's columns are fetched one chunk ahead
+                  const bool own_first = sl[0] == s.slot;
+                  const float f_own = own_first ? f[0] : f[1], f_oth = own_first ? f[1] : f[0];
+                  const float* src = p.part_o + (long long)(own_first ? sl[1] : sl[0]) * kRowsM * D;
+                  float4 nxt[8];
+                  auto fetch = [&](int c) {
+                    const int col4 = (half * kOHalf + c * 32) >> 2;
+#pragma unroll
+                    for (int i = 0; i < 8; ++i)
+                      nxt[i] = __ldcg(reinterpret_cast<const float4*>(src + ((long long)(col4 + i) * kRowsM + row) * 4));
+                  };
+                  fetch(0);
+#pragma unroll
+                  for (int c = 0; c < kOHalf / 32; ++c) {
+                    uint32_t o[32];
+                    ptx::tmem_ld32(tmem_base + lane_addr + kColO + half * kOHalf + c * 32, o);
+                    float oth[32];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) { oth[4 * i] = nxt[i].x; oth[4 * i + 1] = nxt[i].y; oth[4 * i + 2] = nxt[i].z; oth[4 * i + 3] = nxt[i].w; }
+                    if (c + 1 < kOHalf / 32) fetch(c + 1);
+                    ptx::tmem_ld_wait();
+                    float acc[32];
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                      const float mine = __uint_as_float(o[i]);
+                      // slot order: 0 + f0 v0, then + f1 v1 (as the general path below computes it)
+                      acc[i] = own_first ? fmaf(f_oth, oth[i], fmaf(f_own, mine, 0.f)) : fmaf(f_own, mine, fmaf(f_oth, oth[i], 0.f));
+                    }
+                    store32(c, acc);
+                  }
+                } else {
+#pragma unroll 1
+                  for (int c = 0; c < kOHalf / 32; ++c) {
+                    uint32_t o[32];
+                    ptx::tmem_ld32(tmem_base + lane_addr + kColO + half * kOHalf + c * 32, o);
+                    ptx::tmem_ld_wait();
+                    float acc[32];
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) acc[i] = 0.f;
+                    const int col4 = (half * kOHalf + c * 32) >> 2;
+#pragma unroll
+                    for (int g = 0; g < kFusedMax; ++g) {
+                      if (g < nseg) {
+                        if (sl[g] == s.slot) {
+#pragma unroll
+                          for (int i = 0; i < 32; ++i) acc[i] = fmaf(f[g], __uint_as_float(o[i]), acc[i]);
+                        } else {
+                          const float* src = p.part_o + (long long)sl[g] * kRowsM * D;
+#pragma unroll
+                          for (int i = 0; i < 8; ++i) {
+                            const float4 v4 = __ldcg(reinterpret_cast<const float4*>(src + ((long long)(col4 + i) * kRowsM + row) * 4));
+                            acc[4 * i] = fmaf(f[g], v4.x, acc[4 * i]); acc[4 * i + 1] = fmaf(f[g], v4.y, acc[4 * i + 1]);
+                            acc[4 * i + 2] = fmaf(f[g], v4.z, acc[4 * i + 2]); acc[4 * i + 3] = fmaf(f[g], v4.w, acc[4 * i + 3]);
+                          }
+                        }
+                      }
+                    }
+                    store32(c, acc);
+                  }
+                }
+              }
             }
           }
+          if (threadIdx.x == 64) TR_STAMP(7 + 4 * (seg_idx > 0));
           ptx::tc_fence_before();
           __syncwarp();
           if (lane == 0) ptx::mbar_arrive(&bars[SL::b_o_free]);
@@ -550,8 +827,12 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     }
   }
 
+  if (threadIdx.x == 0) TR_FLUSH(16, 16);
+  if (threadIdx.x == 32) { TR_FLUSH(17, 19); TR_FLUSH(22, 23); }
+  if (threadIdx.x == 64) TR_FLUSH(20, 21);
   ptx::tc_fence_before();
   __syncthreads();
+  if (threadIdx.x == 0) TR_STAMP(12);
   if (warp == 1) {
     ptx::tc_fence_after();
     ptx::tmem_dealloc(tmem_base, kTmemCols);
@@ -600,10 +881,10 @@ __global__ void __launch_bounds__(256) sdpa_tc_merge_kernel(const TcParams p, in
     const float m = p.part_m[base];
     const float f = (m == -INFINITY) ? 0.f : exp2f(m - mmax);
     den += f * p.part_l[base];
-    const float4* src = reinterpret_cast<const float4*>(p.part_o + base * D + c0);
+    const float* src = p.part_o + (long long)s_slots[i] * kRowsM * D;
 #pragma unroll
     for (int q = 0; q < W / 4; ++q) {
-      const float4 v = src[q];
+      const float4 v = *reinterpret_cast<const float4*>(src + ((long long)(c0 / 4 + q) * kRowsM + r) * 4);
       acc[4 * q] += f * v.x; acc[4 * q + 1] += f * v.y; acc[4 * q + 2] += f * v.z; acc[4 * q + 3] += f * v.w;
     }
   }
@@ -622,7 +903,19 @@ size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
 size_t tc_workspace_bytes(int D) {
   const size_t slots = 2 * (size_t)sm_count();
-  return align_up(slots * sizeof(int), 256) + slots * kRowsM * ((size_t)D + 2) * sizeof(float);
+  return align_up(slots * sizeof(int), 256) + align_up(slots * sizeof(unsigned long long), 256) +
+         slots * kRowsM * ((size_t)D + 2) * sizeof(float);
+}
+
+// Tag of a launch: arrival flags left in a workspace by earlier launches (or whatever else the
+// memory held) must not compare equal to it.  Starts from a per-process random value.
+unsigned long long next_epoch() {
+  static std::atomic<unsigned long long> counter{[] {
+    std::random_device rd;
+    return (((unsigned long long)rd() << 32) ^ rd()) | 1ull;
+  }()};
+  unsigned long long e = counter.fetch_add(1);
+  return e ? e : counter.fetch_add(1);
 }
 
 template <typename InT, int D>
@@ -650,10 +943,33 @@ int32_t launch_typed(const SdpaArgs& a, cudaStream_t stream) {
   const int n_sm = sm_count();
   long long grid = p.total_tiles < n_sm ? p.total_tiles : n_sm;   // upper bound also for ragged lengths
   if (grid < 1) grid = 1;
+  // equal cuts of every unit when the units divide the SMs well, stream-K ranges otherwise
+  p.split = 0;
+  bool need_merge_kernel = true;
+  if (!a.kv_len) {
+    const int c = n_sm / p.units;
+    static const int mode = [] { const char* e = getenv("DFLASH_SDPA_SPLIT"); return e ? atoi(e) : -1; }();   // -1 auto, 0 stream-K
+    if (mode != 0 && c >= 1 && c <= kFusedMax && tiles_per_unit >= c && (long long)p.units * c * 5 >= (long long)n_sm * 4) {
+      p.split = c;
+      grid = (long long)p.units * c;
+      need_merge_kernel = false;
+    } else {
+      // stream-K: the merge kernel is only needed if some unit is cut into more than kFusedMax ranges
+      int worst = 1;
+      for (int u = 0; u < p.units; ++u) {
+        const long long lo = (long long)u * tiles_per_unit, hi = lo + tiles_per_unit - 1;
+        const int n = (int)(((hi + 1) * grid - 1) / p.total_tiles - ((lo + 1) * grid - 1) / p.total_tiles) + 1;
+        worst = n > worst ? n : worst;
+      }
+      need_merge_kernel = worst > kFusedMax;
+    }
+  }
+  p.epoch = next_epoch();
   const size_t slots = 2 * (size_t)n_sm;
   uint8_t* ws = reinterpret_cast<uint8_t*>(a.workspace);
   p.slot_unit = reinterpret_cast<int*>(ws);
-  p.part_o = reinterpret_cast<float*>(ws + align_up(slots * sizeof(int), 256));
+  p.flags = reinterpret_cast<unsigned long long*>(ws + align_up(slots * sizeof(int), 256));
+  p.part_o = reinterpret_cast<float*>(ws + align_up(slots * sizeof(int), 256) + align_up(slots * sizeof(unsigned long long), 256));
   p.part_m = p.part_o + slots * kRowsM * (size_t)D;
   p.part_l = p.part_m + slots * kRowsM;
 
@@ -693,9 +1009,11 @@ int32_t launch_typed(const SdpaArgs& a, cudaStream_t stream) {
   kernel<<<(unsigned)grid, kThreads, SL::alloc, stream>>>(mq, mk, mv, p);
   DFLASH_LAUNCH_CHECK();
   count_launch();
-  sdpa_tc_merge_kernel<InT, D><<<dim3(p.units, kRowsM / 16), 256, 0, stream>>>(p, (int)(2 * grid));
-  DFLASH_LAUNCH_CHECK();
-  count_launch();
+  if (need_merge_kernel) {
+    sdpa_tc_merge_kernel<InT, D><<<dim3(p.units, kRowsM / 16), 256, 0, stream>>>(p, (int)(2 * grid));
+    DFLASH_LAUNCH_CHECK();
+    count_launch();
+  }
   return DFLASH_OK;
 }
 
