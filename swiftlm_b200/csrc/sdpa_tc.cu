@@ -85,6 +85,8 @@ struct TcParams {
   long long total_tiles;   // only valid when kv_len == nullptr
   float scale_log2;
   int split;               // 0: stream-K ranges; c > 0: every unit cut into c equal ranges (uniform N only)
+  int pair;                // 1: split == 2 and the two CTAs of a unit form a cluster that merges through
+                           //    distributed shared memory (no partials in global memory)
   unsigned long long epoch;            // tag of this launch, never 0
   unsigned long long* flags;           // [2 * gridDim.x] arrival flags (hold the epoch of the launch that set them)
   int* slot_unit;          // [2 * gridDim.x]; -1: empty, or merged inside the main kernel
@@ -107,7 +109,9 @@ struct Smem {
   static constexpr int b_p_full = 6;                 // 2
   static constexpr int b_kv_full = 8;                // kStages
   static constexpr int b_kv_empty = 8 + kStages;     // kStages
-  static constexpr int n_bars = 8 + 2 * kStages;
+  static constexpr int b_peer_ready = 8 + 2 * kStages;   // the cluster partner has stopped using its ring
+  static constexpr int b_peer_data = 9 + 2 * kStages;    // the partner's columns have landed here (256 arrivals)
+  static constexpr int n_bars = 10 + 2 * kStages;
   static constexpr uint32_t misc = bars + 8 * n_bars;   // tmem base, abort flag, range info, group counter, merge decision
   static constexpr uint32_t xseq = misc + 64;            // exchange sequence numbers [2][2][4]
   static constexpr uint32_t xch = xseq + 64;             // exchange values [2 slots][2 halves][128 rows]
@@ -224,6 +228,45 @@ __device__ __forceinline__ unsigned long long ld_acquire_u64(const unsigned long
 }
 __device__ __forceinline__ void fence_sc() { asm volatile("fence.sc.gpu;" ::: "memory"); }
 
+// ---- distributed shared memory of a two-CTA cluster ----
+__device__ __forceinline__ uint32_t cluster_rank() { uint32_t r; asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r)); return r; }
+__device__ __forceinline__ uint32_t peer_addr(const void* local, uint32_t rank) {   // same offset in CTA `rank` of the cluster
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(ptx::smem_u32(local)), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void peer_arrive(uint32_t remote_bar) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(remote_bar) : "memory");
+}
+__device__ __forceinline__ void peer_store(uint32_t remote, float a, float b, float c, float d) {
+  asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(remote), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+__device__ __forceinline__ void peer_store1(uint32_t remote, float a) {
+  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(a) : "memory");
+}
+__device__ __forceinline__ bool try_wait_cluster(void* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+               : "=r"(ok) : "r"(ptx::smem_u32(bar)), "r"(parity) : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ bool wait_peer_or_abort(void* bar, uint32_t parity, volatile int* abort_flag, int* status) {
+  for (uint32_t i = 0; i < ptx::kWaitPolls; ++i) {
+    if (try_wait_cluster(bar, parity)) return true;
+    if ((i & 63u) == 63u) {
+      if (*abort_flag) return false;
+      __nanosleep(40);
+    }
+  }
+  *abort_flag = 1;
+  atomicExch(status, 6);
+  return false;
+}
+
+
 template <typename T> __device__ __forceinline__ uint32_t pack2(float a, float b);
 template <> __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float a, float b) {
   const __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
@@ -281,7 +324,7 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     ptx::prefetch_tensormap(&map_v);
     for (int i = 0; i < SL::n_bars; ++i) {
       const bool four = (i == SL::b_o_free) || (i == SL::b_p_full) || (i == SL::b_p_full + 1);
-      ptx::mbar_init(&bars[i], four ? 8 : 1);
+      ptx::mbar_init(&bars[i], i == SL::b_peer_data ? 256 : (four ? 8 : 1));
     }
     *abort_flag = 0;
     reinterpret_cast<volatile uint32_t*>(sm + SL::misc)[4] = 0;   // group counter
@@ -654,7 +697,84 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
           const float l_tot = half == 0 ? l_sum + l_other : l_other + l_sum;   // same order in both halves
           ptx::tc_fence_after();
           const bool valid = rr < p.R;
-          if (s.slot < 0) {
+          if (p.pair) {
+            // ---- the unit's other half of the keys is in the cluster partner: swap columns ----
+            // Each thread owns two quarters of the head dimension; it keeps quarter 2*half + rank and
+            // sends quarter 2*half + (1 - rank) to the same thread of the partner, whose ring buffer
+            // is free once the partner has said so.
+            constexpr int kQuart = D / 4;
+            const uint32_t rank = cluster_rank(), peer = rank ^ 1u;
+            const float m_log2 = (m_ref == -INFINITY) ? -INFINITY : m_ref * p.scale_log2;
+            float* recv = reinterpret_cast<float*>(sm + SL::ring);              // [half][kQuart / 4][128 rows][4]
+            ok = group_sync();                                                 // every warp is done with xch and the ring
+            if (!ok) break;
+            if (warp == 2 && lane == 0) peer_arrive(peer_addr(&bars[SL::b_peer_ready], peer));
+            ok = wait_peer_or_abort(&bars[SL::b_peer_ready], 0, abort_flag, p.status);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            if (half == 0) {
+              peer_store1(peer_addr(xch + row, peer), m_log2);
+              peer_store1(peer_addr(xch + kRowsM + row, peer), l_tot);
+            }
+            {
+              const int q_send = 2 * half + (int)peer;
+              const uint32_t dst = peer_addr(recv + ((long long)(half * (kQuart / 4)) * kRowsM + row) * 4, peer);
+#pragma unroll
+              for (int c = 0; c < kQuart / 32; ++c) {
+                uint32_t o[32];
+                ptx::tmem_ld32(tmem_base + lane_addr + kColO + q_send * kQuart + c * 32, o);
+                ptx::tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 8; ++i)
+                  peer_store(dst + (uint32_t)((c * 8 + i) * kRowsM * 16), __uint_as_float(o[4 * i]), __uint_as_float(o[4 * i + 1]),
+                             __uint_as_float(o[4 * i + 2]), __uint_as_float(o[4 * i + 3]));
+              }
+            }
+            peer_arrive(peer_addr(&bars[SL::b_peer_data], peer));              // release: this thread's stores first
+            ok = wait_peer_or_abort(&bars[SL::b_peer_data], 0, abort_flag, p.status);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            {
+              // rank 0 holds the earlier keys: fixed order (rank 0, rank 1) in both CTAs
+              const float m_peer = xch[row], l_peer = xch[kRowsM + row];
+              const float m0 = rank == 0 ? m_log2 : m_peer, m1 = rank == 0 ? m_peer : m_log2;
+              const float l0 = rank == 0 ? l_tot : l_peer, l1 = rank == 0 ? l_peer : l_tot;
+              const float mmax = fmaxf(m0, m1);
+              const float f0 = (m0 == -INFINITY) ? 0.f : exp2f(m0 - mmax), f1 = (m1 == -INFINITY) ? 0.f : exp2f(m1 - mmax);
+              const float den = f0 * l0 + f1 * l1;
+              const float inv = den == 0.f ? 1.f : 1.f / den;
+              const float f_own = rank == 0 ? f0 : f1, f_oth = rank == 0 ? f1 : f0;
+              const int q_keep = 2 * half + (int)rank;
+              InT* orow = reinterpret_cast<InT*>(a.out) +
+                          ((((long long)s.b * a.Hq + (long long)s.kvh * p.G + (rr >> 4)) * 16) + tok) * D + q_keep * kQuart;
+              const float4* src = reinterpret_cast<const float4*>(recv) + (long long)(half * (kQuart / 4)) * kRowsM + row;
+#pragma unroll
+              for (int c = 0; c < kQuart / 32; ++c) {
+                uint32_t o[32];
+                ptx::tmem_ld32(tmem_base + lane_addr + kColO + q_keep * kQuart + c * 32, o);
+                ptx::tmem_ld_wait();
+                uint32_t w[16];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                  const float4 v4 = src[(c * 8 + i) * kRowsM];
+                  const float oth[4] = {v4.x, v4.y, v4.z, v4.w};
+                  float r4[4];
+#pragma unroll
+                  for (int e = 0; e < 4; ++e) {
+                    const float mine = __uint_as_float(o[4 * i + e]);
+                    r4[e] = (rank == 0 ? fmaf(f_oth, oth[e], f_own * mine) : fmaf(f_own, mine, f_oth * oth[e])) * inv;
+                  }
+                  w[2 * i] = pack2<InT>(r4[0], r4[1]);
+                  w[2 * i + 1] = pack2<InT>(r4[2], r4[3]);
+                }
+                if (valid) {
+#pragma unroll
+                  for (int i = 0; i < 4; ++i)
+                    *reinterpret_cast<uint4*>(orow + c * 32 + i * 8) = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
+                }
+              }
+            }
+          } else if (s.slot < 0) {
             const float inv = l_tot == 0.f ? 1.f : 1.f / l_tot;
             InT* orow = reinterpret_cast<InT*>(a.out) +
                         ((((long long)s.b * a.Hq + (long long)s.kvh * p.G + (rr >> 4)) * 16) + tok) * D + half * kOHalf;
@@ -827,6 +947,9 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     }
   }
 
+  // No CTA of a pair may leave while its partner can still write into its shared memory.  Every
+  // wait above is bounded, so both always get here.
+  if (p.pair) cluster_sync_all();
   if (threadIdx.x == 0) TR_FLUSH(16, 16);
   if (threadIdx.x == 32) { TR_FLUSH(17, 19); TR_FLUSH(22, 23); }
   if (threadIdx.x == 64) TR_FLUSH(20, 21);
@@ -945,12 +1068,14 @@ int32_t launch_typed(const SdpaArgs& a, cudaStream_t stream) {
   if (grid < 1) grid = 1;
   // equal cuts of every unit when the units divide the SMs well, stream-K ranges otherwise
   p.split = 0;
+  p.pair = 0;
   bool need_merge_kernel = true;
   if (!a.kv_len) {
     const int c = n_sm / p.units;
     static const int mode = [] { const char* e = getenv("DFLASH_SDPA_SPLIT"); return e ? atoi(e) : -1; }();   // -1 auto, 0 stream-K
     if (mode != 0 && c >= 1 && c <= kFusedMax && tiles_per_unit >= c && (long long)p.units * c * 5 >= (long long)n_sm * 4) {
       p.split = c;
+      p.pair = c == 2 ? 1 : 0;
       grid = (long long)p.units * c;
       need_merge_kernel = false;
     } else {
@@ -1006,7 +1131,23 @@ int32_t launch_typed(const SdpaArgs& a, cudaStream_t stream) {
 
   auto kernel = sdpa_tc_kernel<InT, D>;
   DFLASH_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SL::alloc));
-  kernel<<<(unsigned)grid, kThreads, SL::alloc, stream>>>(mq, mk, mv, p);
+  if (p.pair) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = SL::alloc;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    DFLASH_CUDA_CHECK(cudaLaunchKernelEx(&cfg, kernel, mq, mk, mv, p));
+  } else {
+    kernel<<<(unsigned)grid, kThreads, SL::alloc, stream>>>(mq, mk, mv, p);
+  }
   DFLASH_LAUNCH_CHECK();
   count_launch();
   if (need_merge_kernel) {
