@@ -5,6 +5,8 @@
 #include <cstdio>
 #include <mutex>
 
+#include <cstdlib>
+
 #include "common.cuh"
 #include "ptx.cuh"
 
@@ -118,6 +120,9 @@ int32_t dflash_gated_delta_tape(const void* q, const void* k, const void* v, con
   GdnArgs a{q, k, v, g, beta, state_in, mask, n_per_seq, y, state_out, tape,
             B, T, Hk, Hv, Dk, Dv, g_is_vector ? 1 : 0, in_dtype, mask_dtype, false};
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  // DFLASH_GDN_TC=0 keeps the block on the CUDA-core kernel (for comparisons)
+  static const bool use_tc = [] { const char* e = getenv("DFLASH_GDN_TC"); return !(e && e[0] == '0'); }();
+  if (use_tc && gdn_tc_supported(a)) return launch_gdn_tc(a, s);
   if (gdn_fast_supported(a)) return launch_gdn_fast(a, s);
   return launch_gdn_generic(a, s);
 }

@@ -93,6 +93,10 @@ int32_t launch_gdn_generic(const GdnArgs& a, cudaStream_t stream);
 // Dk == Dv == 128, scalar gate, T <= 16: TMA-pipelined persistent kernel.
 bool gdn_fast_supported(const GdnArgs& a);
 int32_t launch_gdn_fast(const GdnArgs& a, cudaStream_t stream);
+// Forward only, bf16 inputs, Dk == Dv == 128, scalar gate, T <= 16: the block's 16 steps as
+// three tensor-core products plus a per-row triangular recurrence.
+bool gdn_tc_supported(const GdnArgs& a);
+int32_t launch_gdn_tc(const GdnArgs& a, cudaStream_t stream);
 
 struct SdpaArgs {
   const void *q, *k, *v;

@@ -1,0 +1,671 @@
+// Gated-delta forward with tape for one DFlash verify block on the tensor cores
+// (Dk = Dv = 128, scalar gate, T <= 16, bf16 per-token inputs, fp32 state).
+//
+// The 16 steps of a block are not run one after another.  With S0 the incoming state, G_t the
+// product of the gates up to step t and Gam[s,t] the product of the gates after s up to t, the
+// recurrence  S <- g S;  delta = beta (v - S k);  S <- S + delta (x) k;  y = S q  unrolls to
+//     kv_t    = G_t (S0 k_t) + sum_{s<t}  Gam[s,t] (k_s . k_t) delta_s
+//     delta_t = beta_t (v_t - kv_t)
+//     y_t     = G_t (S0 q_t) + sum_{s<=t} Gam[s,t] (k_s . q_t) delta_s
+//     S_T     = G_T S0 + sum_s (Gam[s,T] delta_s) (x) k_s
+// so the work on the 128 x 128 state becomes three small matrix products,
+//     [S0 K^T | S0 Q^T]   128 x 128 x 32        (tcgen05, S0 split into two bf16 terms)
+//     [K K^T  | K Q^T ]    16 x 128 x 32        (tcgen05, exact in fp32)
+//     E K                 128 x  16 x 128       (tcgen05, E = Gam delta split into three bf16 terms)
+// plus a 16-step triangular recurrence per state row that one thread solves in registers.  A
+// step that does not run (beyond the accepted length, or masked) gets gate 1 and beta 0: its
+// delta is exactly 0, its y is forced to 0 and the state passes through it unchanged.
+//
+// S0 k and S0 q see S0 to 16 significant bits (2^-17 relative); the state itself is carried in
+// fp32: S_T = G_T * S0 + (E K) with S0 read from the fp32 tile, and E is split exactly (24 bits).
+// For a sequence with no running step the output state equals the input bit for bit.
+//
+// One persistent CTA per SM: eight compute warps and one helper warp.  Per work item
+// (sequence, v-head), with the phases of neighbouring items interleaved:
+//   load    TMA: the fp32 state tile (four 128-byte-swizzled boxes), K and Q rows of the block
+//           (swizzled, they are tensor-core operands as they land), V rows.  The state tile has
+//           one landing buffer, refilled for the next item as soon as the split has read it.
+//   split   compute warps, two threads per state row: S0 -> two bf16 operand tiles in the tensor
+//           cores' K-major layout, and G_T * S0 in fp32 -> the item's accumulator in tensor memory
+//   mma     helper lane: [S0 K^T | S0 Q^T] into tensor memory; under it the compute warps move
+//           the PREVIOUS item's finished state from tensor memory to a staging tile, which a TMA
+//           store sends out
+//   solve   warps 0-3, one thread per state row: the recurrence; delta (tape) and y leave for
+//           global memory; E goes to tensor memory as the A operand of the last product
+//   mma     helper lane: the accumulator += E K; then, under the next split, the next item's Gram
+//           products, which the helper warp scales by the gate products into the other table slot
+// Every wait is bounded; a wait that gives up sets the device status word and the CTA leaves.
+//
+// Reference semantics: Sources/DFlash/DFlashKernels.swift:122-199 (kernel), :409-466 (CPU statement).
+#include <cuda.h>
+
+#include "common.cuh"
+#include "ptx.cuh"
+
+// Optional phase timing (compile with -DDFLASH_GDN_TRACE; never part of the shipped library).
+#ifdef DFLASH_GDN_TRACE
+__device__ unsigned long long g_gdn_trace[256 * 10 * 16];
+#define PH_DECL() long long ph_[10] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0}; long long ph_t_ = clock64()
+#define PH(i) do { const long long n_ = clock64(); ph_[i] += n_ - ph_t_; ph_t_ = n_; } while (0)
+#define PH_FLUSH() do { if ((threadIdx.x & 31) == 0) for (int i_ = 0; i_ < 10; ++i_) g_gdn_trace[(blockIdx.x * 10 + (threadIdx.x >> 5)) * 16 + i_] = (unsigned long long)ph_[i_]; } while (0)
+extern "C" int dflash_gdn_trace(unsigned long long* out, int n) { return (int)cudaMemcpyFromSymbol(out, g_gdn_trace, sizeof(unsigned long long) * n); }
+#else
+#define PH_DECL() do {} while (0)
+#define PH(i) do {} while (0)
+#define PH_FLUSH() do {} while (0)
+#endif
+
+namespace dflash {
+namespace {
+
+constexpr int kD = 128;
+constexpr int kT = 16;
+constexpr int kComputeThreads = 256;
+constexpr int kThreads = kComputeThreads + 64;   // + two helper warps: warp 8 scalars and tables, warp 9 TMA and tensor-core issue
+constexpr int kPairThreads = kComputeThreads + 32;   // participants of the compute <-> one-helper named barriers
+
+// shared memory map (bytes); every tensor-core / TMA tile starts on a 1024-byte boundary
+constexpr uint32_t kL = 0;                       // 64 KiB: landing tile of the fp32 state [4 boxes][128 rows][32 floats]
+constexpr uint32_t kY = 65536;                   // 64 KiB: staging tile of the outgoing state, same layout
+constexpr uint32_t kX = 2 * 65536;               // 2 x 32 KiB: bf16 operand tiles hi, lo: [2 chunks][128 rows][64]
+constexpr uint32_t kKQ = kX + 2 * 32768;         // 2 x 8 KiB: [2 chunks][32 rows: 16 k, 16 q][64]
+constexpr uint32_t kV = kKQ + 2 * 8192;          // 2 x 4 KiB: [16 steps][128] bf16
+constexpr uint32_t kTab = kV + 2 * 4096;         // 2 slots of coefficient tables
+constexpr uint32_t kTabSlot = 2304;
+constexpr uint32_t kTabKK = 0;                   //   [t][s] beta_t Gam[s,t] k_s.k_t (s < t), fp32
+constexpr uint32_t kTabKQ = 1024;                //   [t][s] Gam[s,t] k_s.q_t (s <= t)
+constexpr uint32_t kTabGp = 2048;                //   [t] G_t
+constexpr uint32_t kTabGe = 2048 + 64;           //   [s] Gam[s,T]
+constexpr uint32_t kTabBG = 2048 + 128;          //   [t] beta_t G_t
+constexpr uint32_t kScal = kTab + 2 * kTabSlot;  // 2 slots x { gate'[16], beta'[16], bits }
+constexpr uint32_t kScalSlot = 160;
+constexpr uint32_t kBars = kScal + 2 * kScalSlot;   // 7 mbarriers: state loads x 2, Gram, W, E K, K/Q/V loads x 2
+constexpr uint32_t kMisc = kBars + 64;              // tensor-memory base
+constexpr uint32_t kSmemBytes = 226 * 1024;         // the Gram product reads 16 KiB past each K/Q chunk (rows it ignores)
+static_assert(kMisc + 16 <= kSmemBytes, "shared memory map");
+static_assert(kKQ + 8192 + 4096 + 16384 <= kSmemBytes, "Gram operand over-read stays inside the allocation");
+
+constexpr uint32_t kStateBytes = 65536, kTokenBytes = 8192 + 4096;
+
+// tensor memory columns
+constexpr uint32_t kColW = 0;      // [S0 K^T | S0 Q^T]: 32
+constexpr uint32_t kColGram = 32;  // 32
+constexpr uint32_t kColE = 64;     // E as bf16 pairs: 3 x 8
+constexpr uint32_t kColD = 128;    // 2 x 128: the items' accumulators G_T S0 + E K
+constexpr uint32_t kTmemCols = 512;
+
+__device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  return (uint64_t)((smem_addr & 0x3FFFFu) >> 4) | ((uint64_t)(lbo_bytes >> 4) << 16) |
+         ((uint64_t)(sbo_bytes >> 4) << 32) | (1ull << 46) | (2ull << 61);
+}
+__device__ __forceinline__ uint32_t pack_rn(float a, float b) {
+  const __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
+// upper halves of two floats as a bf16 pair (truncation): a in the low half
+__device__ __forceinline__ uint32_t pack_trunc(float a, float b) {
+  return __byte_perm(__float_as_uint(a), __float_as_uint(b), 0x7632);
+}
+__device__ __forceinline__ float trunc16(float a) { return __uint_as_float(__float_as_uint(a) & 0xffff0000u); }
+
+struct TcMaps {
+  CUtensorMap state_in, state_out, k, q, v;
+};
+
+__global__ void __launch_bounds__(kThreads, 1)
+gdn_tc_kernel(const __grid_constant__ TcMaps maps, const GdnArgs a, int* status) {
+  extern __shared__ __align__(1024) uint8_t sm[];
+  if ((ptx::smem_u32(sm) & 1023u) != 0u) {
+    if (threadIdx.x == 0) atomicExch(status, 4);
+    return;
+  }
+  const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
+  const bool helper = w >= 8, aux = w == 8, mma = w == 9;
+  const int T = a.T;
+  const int rep = a.Hv / a.Hk;
+  const uint32_t n_items = (uint32_t)a.B * (uint32_t)a.Hv;
+  const uint32_t G = gridDim.x;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sm + kBars);   // 0,1: state loads; 2: Gram; 3: W; 4: E K; 5,6: K/Q/V loads
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sm + kMisc);
+  const __nv_bfloat16* gg = reinterpret_cast<const __nv_bfloat16*>(a.g);
+  const __nv_bfloat16* gbeta = reinterpret_cast<const __nv_bfloat16*>(a.beta);
+
+  auto decode = [&](uint32_t i, int& b, int& hv) {   // 32-bit arithmetic on purpose
+    const uint32_t p = i / (uint32_t)rep, sub = i - p * (uint32_t)rep;
+    const uint32_t hk = p / (uint32_t)a.B;
+    b = (int)(p - hk * (uint32_t)a.B);
+    hv = (int)(hk * (uint32_t)rep + sub);
+  };
+  auto step_on = [&](int b, int t) -> bool {
+    bool on = t < T;
+    if (on && a.n_per_seq) on = t < a.n_per_seq[b];
+    if (on && a.mask) on = mask_on(a.mask, a.mask_dtype, b * T + t);
+    return on;
+  };
+  // scalars of item (b, hv): gate' (1 where the step does not run), beta' (0 there), step bits.
+  // The helper warp fetches them into registers early and publishes them later.
+  auto fetch_scalars = [&](int b, int hv, float& g, float& be, bool& on) {
+    // all loads are issued before any is used: their latencies overlap
+    const int t = lane < T ? lane : 0;
+    const long long bt = (long long)b * T + t;
+    const __nv_bfloat16 graw = gg[bt * a.Hv + hv], braw = gbeta[bt * a.Hv + hv];
+    on = lane < kT && step_on(b, lane);
+    g = on ? __bfloat162float(graw) : 1.f;
+    be = on ? __bfloat162float(braw) : 0.f;
+  };
+  auto publish_scalars = [&](int slot, float g, float be, bool on) {
+    const uint32_t m = __ballot_sync(0xffffffffu, on);
+    float* sc = reinterpret_cast<float*>(sm + kScal + slot * kScalSlot);
+    if (lane < kT) { sc[lane] = g; sc[16 + lane] = be; }
+    if (lane == 0) reinterpret_cast<uint32_t*>(sc)[32] = m;
+    __syncwarp();
+  };
+  // The boxes of an item are issued from several lanes of one warp (a single lane takes a few
+  // hundred clocks per box).
+  auto issue_state_load = [&](int b, int hv, int buf) {   // a whole warp
+    void* bar = &bars[buf];
+    if (lane == 0) ptx::mbar_arrive_expect_tx(bar, kStateBytes);
+    __syncwarp();
+    if (lane < 4) ptx::tma_load_2d(sm + kL + lane * 16384, &maps.state_in, lane * 32, (b * a.Hv + hv) * kD, bar);
+    __syncwarp();
+  };
+  auto issue_token_loads = [&](int b, int hv, int buf) {   // a whole warp
+    void* tbar = &bars[5 + buf];
+    if (lane == 0) ptx::mbar_arrive_expect_tx(tbar, kTokenBytes);
+    __syncwarp();
+    const int hk = hv / rep;
+    if (lane < 4) {
+      const int c = lane >> 1;
+      if (lane & 1) ptx::tma_load_4d(sm + kKQ + buf * 8192 + c * 4096 + 2048, &maps.q, c * 64, hk, 0, b, tbar);
+      else ptx::tma_load_4d(sm + kKQ + buf * 8192 + c * 4096, &maps.k, c * 64, hk, 0, b, tbar);
+    } else if (lane == 4) {
+      ptx::tma_load_4d(sm + kV + buf * 4096, &maps.v, 0, hv, 0, b, tbar);
+    }
+    __syncwarp();
+  };
+  // instruction descriptors: fp32 accumulate, bf16 A and B, N >> 3, M >> 4 (and B MN-major for E K)
+  constexpr uint32_t kIdescW = (1u << 4) | (1u << 7) | (1u << 10) | ((32u >> 3) << 17) | ((128u >> 4) << 24);
+  constexpr uint32_t kIdescD = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
+  // Gram products of the item in buffer buf: rows of [K; Q] against [K; Q]; only rows 0-15 (the k rows) are read back
+  auto issue_gram = [&](uint32_t tmem, int buf) {   // one thread
+    const uint32_t kq_addr = ptx::smem_u32(sm + kKQ + buf * 8192);
+#pragma unroll
+    for (int kk = 0; kk < 8; ++kk) {
+      const uint64_t d = make_desc(kq_addr + (kk >> 2) * 4096, 16, 1024) + 2 * (kk & 3);
+      if (kk == 0) ptx::umma_ss_first(tmem + kColGram, d, d, kIdescW);
+      else ptx::umma_ss_acc(tmem + kColGram, d, d, kIdescW);
+    }
+    ptx::umma_commit(&bars[2]);
+  };
+  // the helper warp: Gram rows out of tensor memory, scaled by gate products (and beta), into table slot
+  auto build_tables = [&](uint32_t tmem, int slot) {
+    uint32_t gr[32];
+    ptx::tmem_ld32(tmem + kColGram, gr);   // lane s < 16: k_s.k_t (t < 16), k_s.q_t
+    ptx::tmem_ld_wait();
+    const float* sc = reinterpret_cast<const float*>(sm + kScal + slot * kScalSlot);
+    uint8_t* tab = sm + kTab + slot * kTabSlot;
+    float* tkk = reinterpret_cast<float*>(tab + kTabKK);
+    float* tkq = reinterpret_cast<float*>(tab + kTabKQ);
+    // lanes 0-15: row s of the scaled Gram tables; lanes 16-31: the prefix products G_t.
+    // The scalars go to registers first: the table stores below could alias them for the compiler.
+    {
+      float gt[kT], bt[kT];
+#pragma unroll
+      for (int q4 = 0; q4 < 4; ++q4) {
+        const float4 g4 = reinterpret_cast<const float4*>(sc)[q4], b4 = reinterpret_cast<const float4*>(sc + 16)[q4];
+        gt[4 * q4] = g4.x; gt[4 * q4 + 1] = g4.y; gt[4 * q4 + 2] = g4.z; gt[4 * q4 + 3] = g4.w;
+        bt[4 * q4] = b4.x; bt[4 * q4 + 1] = b4.y; bt[4 * q4 + 2] = b4.z; bt[4 * q4 + 3] = b4.w;
+      }
+      const int s = lane & 15;
+      const bool pre = lane >= kT;
+      float gam = 1.f, bsel = 0.f;
+      float okk[kT], okq[kT];
+#pragma unroll
+      for (int t = 0; t < kT; ++t) {
+        if (pre ? t <= s : t > s) gam *= gt[t];
+        if (t == s) bsel = bt[t];
+        okk[t] = t > s ? bt[t] * gam * __uint_as_float(gr[t]) : 0.f;
+        okq[t] = t >= s ? gam * __uint_as_float(gr[16 + t]) : 0.f;
+      }
+      if (!pre) {
+#pragma unroll
+        for (int t = 0; t < kT; ++t) { tkk[t * 16 + s] = okk[t]; tkq[t * 16 + s] = okq[t]; }
+        reinterpret_cast<float*>(tab + kTabGe)[s] = gam;
+      } else {
+        reinterpret_cast<float*>(tab + kTabGp)[s] = gam;
+        reinterpret_cast<float*>(tab + kTabBG)[s] = bsel * gam;
+      }
+    }
+    ptx::tc_fence_before();
+    __syncwarp();
+  };
+
+  // ---- prologue ----
+  uint32_t item = blockIdx.x;
+  if (tid == 0) {
+    for (int i = 0; i < 7; ++i) ptx::mbar_init(&bars[i], 1);
+    ptx::fence_mbar_init();
+  }
+  if (mma && lane == 0) {
+    ptx::prefetch_tensormap(&maps.state_in);
+    ptx::prefetch_tensormap(&maps.k);
+    ptx::prefetch_tensormap(&maps.q);
+    ptx::prefetch_tensormap(&maps.v);
+    ptx::prefetch_tensormap(&maps.state_out);
+  }
+  if (aux) {
+    ptx::tmem_alloc(tmem_slot, kTmemCols);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+  int b_cur = 0, hv_cur = 0;
+  bool failed = false;
+  __nv_bfloat16 h_g = __float2bfloat16(1.f), h_b = __float2bfloat16(0.f);   // scalar warp: gate / beta of the next item
+  int h_n = 0;       // its accepted length, compared only when published (the load has a whole iteration to land)
+  bool h_m = false;  // its mask bit
+  if (item < n_items) {
+    decode(item, b_cur, hv_cur);
+    if (mma) {
+      issue_token_loads(b_cur, hv_cur, 0);
+      issue_state_load(b_cur, hv_cur, 0);
+      failed = !ptx::mbar_wait(&bars[5], 0);
+      if (lane == 0) { ptx::tc_fence_after(); issue_gram(tmem, 0); }
+      __syncwarp();
+    } else if (aux) {
+      float g0, be0;
+      bool on0;
+      fetch_scalars(b_cur, hv_cur, g0, be0, on0);
+      publish_scalars(0, g0, be0, on0);
+      if (item + G < n_items) {
+        int b1, hv1;
+        decode(item + G, b1, hv1);
+        const long long bt = (long long)b1 * T + (lane < T ? lane : 0);
+        h_g = gg[bt * a.Hv + hv1];
+        h_b = gbeta[bt * a.Hv + hv1];
+        h_n = a.n_per_seq ? a.n_per_seq[b1] : T;
+        h_m = lane < T && (!a.mask || mask_on(a.mask, a.mask_dtype, b1 * T + lane));
+      }
+      failed = !ptx::mbar_wait(&bars[2], 0);
+      ptx::tc_fence_after();
+      build_tables(tmem, 0);
+    }
+  }
+  __syncthreads();   // the first item's scalars and tables are in place
+  if (aux && item < n_items) asm volatile("bar.arrive 4, %0;" ::"n"(kPairThreads) : "memory");
+
+  const int row = 32 * (w & 3) + lane;               // state row = tensor-memory lane of this thread
+  const uint32_t lane_addr = (uint32_t)(32 * (w & 3)) << 16;
+  const int half = (w >> 2) & 1;                      // which 64 state columns this thread handles in the output pass
+  uint32_t gram_uses = 1;                             // phases of the Gram barrier consumed so far (helper warp)
+
+  // previous item's finished state: tensor memory -> staging tile -> TMA store (compute warps)
+  auto flush_state = [&](int dbuf, int b, int hv, uint32_t ek_parity) -> bool {
+    if (tid == 0) ptx::bulk_wait_read_all();          // the staging tile's previous store has been read
+    bool ok = ptx::mbar_wait(&bars[4], ek_parity);
+    ptx::tc_fence_after();
+    asm volatile("bar.sync 1, %0;" ::"n"(kComputeThreads) : "memory");
+#pragma unroll
+    for (int bb = 0; bb < 2; ++bb) {
+      uint32_t dr[32];
+      ptx::tmem_ld32(tmem + lane_addr + kColD + 128 * dbuf + 64 * half + 32 * bb, dr);
+      ptx::tmem_ld_wait();
+#pragma unroll
+      for (int g = 0; g < 8; ++g)
+        *reinterpret_cast<uint4*>(sm + kY + (2 * half + bb) * 16384 + row * 128 + ((g ^ (row & 7)) << 4)) =
+            make_uint4(dr[4 * g], dr[4 * g + 1], dr[4 * g + 2], dr[4 * g + 3]);
+    }
+    ptx::fence_proxy_async();
+    ptx::tc_fence_before();
+    asm volatile("bar.sync 1, %0;" ::"n"(kComputeThreads) : "memory");
+    if (tid == 0) {
+      const int row0 = (b * a.Hv + hv) * kD;
+#pragma unroll
+      for (int box = 0; box < 4; ++box) ptx::tma_store_2d(&maps.state_out, box * 32, row0, sm + kY + box * 16384);
+      ptx::bulk_commit_group();
+    }
+    return ok;
+  };
+
+  PH_DECL();
+  int b_prev = 0, hv_prev = 0, it = 0;
+  for (; item < n_items; ++it, item += G) {
+    const int buf = it & 1;
+    const uint32_t par = (uint32_t)it & 1u;
+    const uint32_t nxt = item + G;
+    const bool has_next = nxt < n_items;
+    int b_nxt = 0, hv_nxt = 0;
+    if (has_next) decode(nxt, b_nxt, hv_nxt);
+    uint8_t* KQ = sm + kKQ + buf * 8192;
+    const float* sc = reinterpret_cast<const float*>(sm + kScal + buf * kScalSlot);
+    const uint8_t* tab = sm + kTab + buf * kTabSlot;
+
+    // ---- this item's state, K, Q, V have landed ----
+    if (!helper) failed = !ptx::mbar_wait(&bars[buf], (uint32_t)(it >> 1) & 1u);
+    PH(0);
+
+    // ---- split: S0 = hi + lo + (dropped 2^-17), both bf16, K-major; G_T S0 -> this item's accumulator ----
+    if (!helper) {
+      float g_T = 1.f;
+#pragma unroll
+      for (int t = 0; t < kT; ++t) g_T *= sc[t];
+#pragma unroll
+      for (int bb = 0; bb < 2; ++bb) {
+        const int box = 2 * half + bb;                  // 32 state columns
+        float4 x4[8];
+#pragma unroll
+        for (int g = 0; g < 8; ++g)
+          x4[g] = *reinterpret_cast<const float4*>(sm + kL + box * 16384 + row * 128 + ((g ^ (row & 7)) << 4));
+        uint32_t acc[32];
+#pragma unroll
+        for (int g = 0; g < 8; ++g) {
+          acc[4 * g] = __float_as_uint(g_T * x4[g].x);
+          acc[4 * g + 1] = __float_as_uint(g_T * x4[g].y);
+          acc[4 * g + 2] = __float_as_uint(g_T * x4[g].z);
+          acc[4 * g + 3] = __float_as_uint(g_T * x4[g].w);
+        }
+        ptx::tmem_st32(tmem + lane_addr + kColD + 128 * buf + 32 * box, acc);
+        // operand tiles: chunk = box / 2 (64 columns), 16-byte granule = 8 columns
+#pragma unroll
+        for (int gg8 = 0; gg8 < 4; ++gg8) {
+          const float x[8] = {x4[2 * gg8].x, x4[2 * gg8].y, x4[2 * gg8].z, x4[2 * gg8].w,
+                              x4[2 * gg8 + 1].x, x4[2 * gg8 + 1].y, x4[2 * gg8 + 1].z, x4[2 * gg8 + 1].w};
+          uint32_t hi[4], lo[4];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            hi[i] = pack_trunc(x[2 * i], x[2 * i + 1]);
+            lo[i] = pack_rn(x[2 * i] - trunc16(x[2 * i]), x[2 * i + 1] - trunc16(x[2 * i + 1]));
+          }
+          const int gran = (box & 1) * 4 + gg8;
+          uint8_t* dst = sm + kX + (box >> 1) * 16384 + row * 128 + ((gran ^ (row & 7)) << 4);
+          *reinterpret_cast<uint4*>(dst) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+          *reinterpret_cast<uint4*>(dst + 32768) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+        }
+      }
+      ptx::fence_proxy_async();
+      ptx::tmem_st_wait();
+    }
+    ptx::tc_fence_before();
+    PH(1);
+    // split -> products and next loads: the compute warps only signal, the helper warps wait (named barrier 3)
+    if (helper) asm volatile("bar.sync 3, %0;" ::"n"(kThreads) : "memory");
+    else asm volatile("bar.arrive 3, %0;" ::"n"(kThreads) : "memory");
+    PH(2);
+
+    if (mma) {
+      // ---- issuing warp: the next item's state load (its landing tile is free again), this item's
+      //      [S0 K^T | S0 Q^T], then the next item's K, Q, V loads ----
+      if (has_next) issue_state_load(b_nxt, hv_nxt, buf ^ 1);
+      if (lane == 0) {
+        ptx::tc_fence_after();
+        const uint32_t kq_addr = ptx::smem_u32(KQ), x_addr = ptx::smem_u32(sm + kX);
+#pragma unroll
+        for (int sp = 0; sp < 2; ++sp)
+#pragma unroll
+          for (int kk = 0; kk < 8; ++kk) {
+            const uint64_t da = make_desc(x_addr + sp * 32768 + (kk >> 2) * 16384, 16, 1024) + 2 * (kk & 3);
+            const uint64_t db = make_desc(kq_addr + (kk >> 2) * 4096, 16, 1024) + 2 * (kk & 3);
+            if (sp == 0 && kk == 0) ptx::umma_ss_first(tmem + kColW, da, db, kIdescW);
+            else ptx::umma_ss_acc(tmem + kColW, da, db, kIdescW);
+          }
+        ptx::umma_commit(&bars[3]);
+      }
+      __syncwarp();
+      if (it > 0) failed = !ptx::mbar_wait(&bars[4], par ^ 1u);   // E K of the previous item no longer reads its K rows
+      if (has_next) issue_token_loads(b_nxt, hv_nxt, buf ^ 1);
+    } else if (aux) {
+      // ---- scalar warp: the next item's gates, betas and step bits ----
+      if (has_next) {
+        const bool h_on = h_m && lane < h_n;
+        publish_scalars(buf ^ 1, h_on ? __bfloat162float(h_g) : 1.f, h_on ? __bfloat162float(h_b) : 0.f, h_on);
+      }
+      // gates and betas of the item after the next: in registers until the next iteration publishes them
+      if (nxt + G < n_items) {
+        int b2, hv2;
+        decode(nxt + G, b2, hv2);
+        const long long bt = (long long)b2 * T + (lane < T ? lane : 0);
+        h_g = gg[bt * a.Hv + hv2];
+        h_b = gbeta[bt * a.Hv + hv2];
+        h_n = a.n_per_seq ? a.n_per_seq[b2] : T;
+        h_m = lane < T && (!a.mask || mask_on(a.mask, a.mask_dtype, b2 * T + lane));
+      }
+      PH(8);
+    } else {
+      // ---- compute warps, under the helper's products: the previous item's state goes out ----
+      if (it > 0 && !flush_state(buf ^ 1, b_prev, hv_prev, par ^ 1u)) failed = true;
+      asm volatile("bar.sync 4, %0;" ::"n"(kPairThreads) : "memory");   // this item's tables are in place
+    }
+    PH(3);
+
+    // ---- solve: two threads per state row.  Warps 0-3 run the delta recurrence, hand the deltas
+    //      over through shared memory, then build E and write the tape; warps 4-7 form y ----
+    if (!helper) {
+      failed = !ptx::mbar_wait(&bars[3], par) || failed;
+      failed = !ptx::mbar_wait(&bars[5 + buf], (uint32_t)(it >> 1) & 1u) || failed;
+      ptx::tc_fence_after();
+      uint32_t wr[32];
+      ptx::tmem_ld32(tmem + lane_addr + kColW, wr);   // S0 k_t (t < 16), S0 q_t
+      ptx::tmem_ld_wait();
+      PH(9);
+      const uint32_t bits = reinterpret_cast<const uint32_t*>(sc)[32];
+      float* dx = reinterpret_cast<float*>(sm + kX);   // [t][row]: the operand tiles are idle until the next split
+      const long long obase = ((long long)b_cur * T * a.Hv + hv_cur) * kD + row;
+      const long long ostep = (long long)a.Hv * kD;
+      float d[kT];
+      if (w < 4) {
+        const __nv_bfloat16* vt = reinterpret_cast<const __nv_bfloat16*>(sm + kV + buf * 4096);
+        const float4* tkk = reinterpret_cast<const float4*>(tab + kTabKK);
+        // delta_t = r_t - sum_{s<t} c[t][s] delta_s  with  r_t = beta_t v_t - beta_t G_t (S0 k_t)  (beta folded into c).
+        // Steps are taken four at a time; a group in which no step runs costs nothing.
+        float r[kT];
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+          const float4 bg4 = reinterpret_cast<const float4*>(tab + kTabBG)[q4], be4 = reinterpret_cast<const float4*>(sc + 16)[q4];
+          const float bgv[4] = {bg4.x, bg4.y, bg4.z, bg4.w}, bev[4] = {be4.x, be4.y, be4.z, be4.w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int t = 4 * q4 + e;
+            r[t] = fmaf(-bgv[e], __uint_as_float(wr[t]), bev[e] * __bfloat162float(vt[t * kD + row]));
+          }
+        }
+#pragma unroll
+        for (int g4 = 0; g4 < 4; ++g4) {
+          if ((bits >> (4 * g4)) & 0xFu) {   // uniform over the CTA
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const int t = 4 * g4 + e;
+              float ckk[kT];
+#pragma unroll
+              for (int q4 = 0; q4 < 4; ++q4)
+                if (4 * q4 < t) {
+                  const float4 c = tkk[t * 4 + q4];
+                  ckk[4 * q4] = c.x; ckk[4 * q4 + 1] = c.y; ckk[4 * q4 + 2] = c.z; ckk[4 * q4 + 3] = c.w;
+                }
+              // two partial sums keep the chain through the freshest delta short; a step that does not
+              // run has beta' = 0, hence r = 0 and a zero row of c: its delta is exactly 0
+              float acc0 = r[t], acc1 = 0.f;
+#pragma unroll
+              for (int s = 0; s < t; ++s) {
+                if (s & 1) acc1 = fmaf(-d[s], ckk[s], acc1);
+                else acc0 = fmaf(-d[s], ckk[s], acc0);
+              }
+              d[t] = acc0 + acc1;
+            }
+          } else {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) d[4 * g4 + e] = 0.f;
+          }
+        }
+#pragma unroll
+        for (int t = 0; t < kT; ++t) dx[t * kD + row] = d[t];
+      }
+      asm volatile("bar.sync 2, %0;" ::"n"(kComputeThreads) : "memory");
+      PH(4);
+      if (w < 4) {
+        // E = Gam[s,T] delta_s, split exactly into three bf16 terms, as the A operand (pairs of steps per column)
+        const float* ge = reinterpret_cast<const float*>(tab + kTabGe);
+        uint32_t er[32];
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          const float e0 = ge[2 * c] * d[2 * c], e1 = ge[2 * c + 1] * d[2 * c + 1];
+          const float r0 = e0 - trunc16(e0), r1 = e1 - trunc16(e1);
+          er[c] = pack_trunc(e0, e1);
+          er[8 + c] = pack_trunc(r0, r1);
+          er[16 + c] = pack_rn(r0 - trunc16(r0), r1 - trunc16(r1));
+          er[24 + c] = 0u;
+        }
+        ptx::tmem_st32(tmem + lane_addr + kColE, er);
+        if (a.tape) {
+#pragma unroll
+          for (int t = 0; t < kT; ++t)
+            if (t < T) a.tape[obase + t * ostep] = d[t];
+        }
+        ptx::tmem_st_wait();
+        ptx::tc_fence_before();
+      } else {
+        // y_t = G_t (S0 q_t) + sum_{s<=t} c'[t][s] delta_s
+        const float4* tkq = reinterpret_cast<const float4*>(tab + kTabKQ);
+        const float* gp = reinterpret_cast<const float*>(tab + kTabGp);
+        __nv_bfloat16* yout = reinterpret_cast<__nv_bfloat16*>(a.y);
+#pragma unroll
+        for (int t = 0; t < kT; ++t) d[t] = dx[t * kD + row];
+        float gpv[kT];
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+          const float4 g4 = reinterpret_cast<const float4*>(gp)[q4];
+          gpv[4 * q4] = g4.x; gpv[4 * q4 + 1] = g4.y; gpv[4 * q4 + 2] = g4.z; gpv[4 * q4 + 3] = g4.w;
+        }
+#pragma unroll
+        for (int g4 = 0; g4 < 4; ++g4) {
+          float y[4] = {0.f, 0.f, 0.f, 0.f};
+          if ((bits >> (4 * g4)) & 0xFu) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const int t = 4 * g4 + e;
+              float ckq[kT];
+#pragma unroll
+              for (int q4 = 0; q4 < 4; ++q4)
+                if (4 * q4 <= t) {
+                  const float4 c = tkq[t * 4 + q4];
+                  ckq[4 * q4] = c.x; ckq[4 * q4 + 1] = c.y; ckq[4 * q4 + 2] = c.z; ckq[4 * q4 + 3] = c.w;
+                }
+              float y0 = gpv[t] * __uint_as_float(wr[16 + t]), y1 = 0.f;
+#pragma unroll
+              for (int s = 0; s <= t; ++s) {
+                if (s & 1) y1 = fmaf(d[s], ckq[s], y1);
+                else y0 = fmaf(d[s], ckq[s], y0);
+              }
+              y[e] = ((bits >> t) & 1u) ? y0 + y1 : 0.f;
+            }
+          }
+#pragma unroll
+          for (int e = 0; e < 4; ++e)
+            if (4 * g4 + e < T) yout[obase + (4 * g4 + e) * ostep] = __float2bfloat16_rn(y[e]);
+        }
+      }
+    }
+    PH(5);
+    if (__syncthreads_or(failed)) { failed = true; break; }
+    PH(6);
+
+    // ---- issuing warp: accumulator += E K, then the next item's Gram products; scalar warp: its tables ----
+    if (mma) {
+      if (lane == 0) {
+        ptx::tc_fence_after();
+        // k rows 0-15 of both chunks as an MN-major operand: 64-column atoms 4096 bytes apart, 8-step groups 1024 apart
+        const uint64_t db = make_desc(ptx::smem_u32(KQ), 4096, 1024);
+        const uint32_t dcol = tmem + kColD + 128 * buf;
+        ptx::umma_ts_acc(dcol, tmem + kColE, db, kIdescD);
+        ptx::umma_ts_acc(dcol, tmem + kColE + 8, db, kIdescD);
+        ptx::umma_ts_acc(dcol, tmem + kColE + 16, db, kIdescD);
+        ptx::umma_commit(&bars[4]);
+      }
+      __syncwarp();
+      if (has_next) {
+        failed = !ptx::mbar_wait(&bars[5 + (buf ^ 1)], (uint32_t)((it + 1) >> 1) & 1u);
+        if (lane == 0) { ptx::tc_fence_after(); issue_gram(tmem, buf ^ 1); }
+        __syncwarp();
+      }
+    } else if (aux && has_next) {
+      failed = !ptx::mbar_wait(&bars[2], gram_uses & 1u);
+      ++gram_uses;
+      ptx::tc_fence_after();
+      build_tables(tmem, buf ^ 1);
+      __threadfence_block();
+      asm volatile("bar.arrive 4, %0;" ::"n"(kPairThreads) : "memory");
+    }
+    PH(7);
+    b_prev = b_cur;
+    hv_prev = hv_cur;
+    b_cur = b_nxt;
+    hv_cur = hv_nxt;
+  }
+  // the last item's state
+  if (!failed && it > 0 && !helper) {
+    if (!flush_state((it - 1) & 1, b_prev, hv_prev, (uint32_t)(it - 1) & 1u)) failed = true;
+  }
+
+  PH_FLUSH();
+  if (failed && lane == 0) atomicExch(status, 1);
+  if (tid == 0) ptx::bulk_wait_all();   // shared memory must outlive the last store
+  ptx::tc_fence_before();
+  __syncthreads();
+  if (aux) {
+    ptx::tc_fence_after();
+    ptx::tmem_dealloc(tmem, kTmemCols);
+  }
+}
+
+}  // namespace
+
+bool gdn_tc_supported(const GdnArgs& a) {
+  if (a.replay || a.Dk != kD || a.Dv != kD || a.g_is_vector || a.T > kT || a.T < 1) return false;
+  if (a.in_dtype != DFLASH_BF16) return false;
+  if ((long long)a.B * a.Hv > (1LL << 24) - 1024) return false;
+  if (a.Hv % a.Hk != 0) return false;
+  // TMA needs 16-byte aligned bases
+  const uintptr_t al = (uintptr_t)a.q | (uintptr_t)a.k | (uintptr_t)a.v | (uintptr_t)a.state_in | (uintptr_t)a.state_out;
+  return (al & 15u) == 0;
+}
+
+int32_t launch_gdn_tc(const GdnArgs& a, cudaStream_t stream) {
+  EncodeTiledFn encode = tensor_map_encoder();
+  if (!encode) { set_error("cuTensorMapEncodeTiled is not available from this driver"); return DFLASH_ERR_CUDA; }
+  int* status = device_status_word();
+  if (!status) { set_error("no CUDA device"); return DFLASH_ERR_CUDA; }
+  TcMaps maps;
+  const cuuint32_t ones[4] = {1, 1, 1, 1};
+  auto state_map = [&](CUtensorMap* m, const float* base) {
+    const cuuint64_t dims[2] = {(cuuint64_t)kD, (cuuint64_t)a.B * a.Hv * kD};
+    const cuuint64_t strides[1] = {(cuuint64_t)kD * 4};
+    const cuuint32_t box[2] = {32, (cuuint32_t)kD};
+    return encode(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(base), dims, strides, box, ones,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  };
+  // per-token tensors [B, T, H, 128] as (d, h, t, b); one box = the 16 steps of one head (rows past T read as zeros)
+  auto token_map = [&](CUtensorMap* m, const void* base, int H, int box_d, CUtensorMapSwizzle sw) {
+    const cuuint64_t dims[4] = {(cuuint64_t)kD, (cuuint64_t)H, (cuuint64_t)a.T, (cuuint64_t)a.B};
+    const cuuint64_t strides[3] = {(cuuint64_t)kD * 2, (cuuint64_t)H * kD * 2, (cuuint64_t)a.T * H * kD * 2};
+    const cuuint32_t box[4] = {(cuuint32_t)box_d, 1, (cuuint32_t)kT, 1};
+    return encode(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, ones,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  };
+  CUresult r = state_map(&maps.state_in, a.state_in);
+  if (r == CUDA_SUCCESS) r = state_map(&maps.state_out, a.state_out);
+  if (r == CUDA_SUCCESS) r = token_map(&maps.k, a.k, a.Hk, 64, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (r == CUDA_SUCCESS) r = token_map(&maps.q, a.q, a.Hk, 64, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (r == CUDA_SUCCESS) r = token_map(&maps.v, a.v, a.Hv, 128, CU_TENSOR_MAP_SWIZZLE_NONE);
+  if (r != CUDA_SUCCESS) { set_error("cuTensorMapEncodeTiled failed with CUresult %d", (int)r); return DFLASH_ERR_CUDA; }
+  DFLASH_CUDA_CHECK(cudaFuncSetAttribute(gdn_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes));
+  const long long items = (long long)a.B * a.Hv;
+  const long long grid = items < (long long)sm_count() ? items : (long long)sm_count();
+  gdn_tc_kernel<<<(unsigned)grid, kThreads, kSmemBytes, stream>>>(maps, a, status);
+  DFLASH_LAUNCH_CHECK();
+  count_launch();
+  return DFLASH_OK;
+}
+
+}  // namespace dflash
