@@ -50,9 +50,9 @@ def measured_peaks():
 # DRAM bytes moved per algorithmic byte, from the committed ncu captures (dram__bytes_read.sum +
 # dram__bytes_write.sum of one launch on a smaller case of the same kernel; traffic grows in
 # proportion to the units processed):
-#   profiles/gdn_fast_forward_replay_small.md   2.5559 GB moved / 2.5627 GB algorithmic
-#   profiles/sdpa_tc_sdpa_small.md              284.4 MB (main kernel) + 27.0 MB (merge) / 277.9 MB
-TRAFFIC_PER_ALGORITHMIC_BYTE = {"gdn_fast_forward": 0.9974, "sdpa_tc": 1.1205}
+#   profiles/gdn_tc_forward_replay_small.md     2.6157 GB moved / 2.5627 GB algorithmic
+#   profiles/sdpa_tc_sdpa_small.md              277.6 MB moved / 277.9 MB algorithmic (no merge kernel for configs[2])
+TRAFFIC_PER_ALGORITHMIC_BYTE = {"gdn_tc_forward": 1.0207, "sdpa_tc": 0.9990}
 
 
 class ClockSampler:
@@ -275,7 +275,7 @@ def run_gpu(args):
     ms_per_step = total_ms / args.steps
     value = world * heads / (ms_per_step * 1e-3)
     achieved_gbs = alg_bytes / (kernel_ms * 1e-3) / 1e9
-    traffic = TRAFFIC_PER_ALGORITHMIC_BYTE["gdn_fast_forward"]
+    traffic = TRAFFIC_PER_ALGORITHMIC_BYTE["gdn_tc_forward"]
 
     # ---- end to end through the host-buffer API (rank-local pinned buffers) ----
     e2e_steps = max(1, min(args.steps, 3))
@@ -319,7 +319,7 @@ def run_gpu(args):
                    "global_batch": f"{64 * world} sequences", "parallelism": f"sequence-sharded x{world}, no collective",
                    "l2": "inputs (5.4 GB) and outputs (5.1 GB) per step exceed the 126 MB L2; no flush needed",
                    "seed": SEED + 1000},
-        "roofline": {"bound": "hbm", "kernel": "gdn_fast_kernel<bf16, forward>", "achieved": achieved_gbs,
+        "roofline": {"bound": "hbm", "kernel": "gdn_tc_kernel (bf16 inputs, forward with tape)", "achieved": achieved_gbs,
                      "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved_gbs / peaks["hbm_gbs"],
                      "peak_source": peaks["source"], "algorithmic_bytes_per_launch": alg_bytes,
                      "kernel_ms": kernel_ms,
@@ -354,19 +354,25 @@ def run_sdpa(torch, kernels, device, args, peaks):
         q, k, v = sets[i % 3]
         kernels.batched_sdpa_2pass(q, k, v, scale, out=out)
     torch.cuda.synchronize()
-    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
-    for i, (e0, e1) in enumerate(evs):
-        q, k, v = sets[i % 3]
+    # bursts of `steps` back-to-back calls between one pair of events (a call is ~60 us: an event
+    # pair around every single call would mostly time the gaps between launches)
+    bursts = []
+    for _ in range(5):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        kernels.batched_sdpa_2pass(q, k, v, scale, out=out)
+        for i in range(steps):
+            q, k, v = sets[i % 3]
+            kernels.batched_sdpa_2pass(q, k, v, scale, out=out)
         e1.record()
-    torch.cuda.synchronize()
+        torch.cuda.synchronize()
+        bursts.append(e0.elapsed_time(e1) / steps)
     kernels.device_status()
-    ms = statistics.median(e0.elapsed_time(e1) for e0, e1 in evs)
+    ms = statistics.median(bursts)
     tflops = sdpa_flops() / (ms * 1e-3) / 1e12
     gbs = sdpa_bytes() / (ms * 1e-3) / 1e9
     return {"metric": "verify_sdpa_tflops", "value": tflops, "unit": "TFLOP/s", "ms_per_call": ms,
-            "config": "configs[2]: B=32, Hq=16, Hkv=2, T=16, D=256, N=4096+16, bf16, scale 1/16; 3 rotating K/V sets",
+            "config": "configs[2]: B=32, Hq=16, Hkv=2, T=16, D=256, N=4096+16, bf16, scale 1/16; 3 rotating K/V sets; "
+                      "median of 5 bursts of back-to-back calls",
             "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                          "frac": gbs / peaks["hbm_gbs"], "algorithmic_bytes_per_launch": sdpa_bytes(),
                          "traffic": TRAFFIC_PER_ALGORITHMIC_BYTE["sdpa_tc"] * sdpa_bytes(),

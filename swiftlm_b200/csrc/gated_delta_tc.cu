@@ -20,20 +20,24 @@
 // fp32: S_T = G_T * S0 + (E K) with S0 read from the fp32 tile, and E is split exactly (24 bits).
 // For a sequence with no running step the output state equals the input bit for bit.
 //
-// One persistent CTA per SM: eight compute warps and one helper warp.  Per work item
-// (sequence, v-head), with the phases of neighbouring items interleaved:
-//   load    TMA: the fp32 state tile (four 128-byte-swizzled boxes), K and Q rows of the block
-//           (swizzled, they are tensor-core operands as they land), V rows.  The state tile has
-//           one landing buffer, refilled for the next item as soon as the split has read it.
+// One persistent CTA per SM: eight compute warps, a scalar warp and an issuing warp.  Per work
+// item (sequence, v-head), with the phases of neighbouring items interleaved:
+//   load    issuing warp, TMA: the fp32 state tile (four 128-byte-swizzled boxes; one landing tile,
+//           refilled for the next item as soon as the split has read it), and K, Q rows of the block
+//           (swizzled, they are tensor-core operands as they land) and V rows on a barrier of their own
 //   split   compute warps, two threads per state row: S0 -> two bf16 operand tiles in the tensor
 //           cores' K-major layout, and G_T * S0 in fp32 -> the item's accumulator in tensor memory
-//   mma     helper lane: [S0 K^T | S0 Q^T] into tensor memory; under it the compute warps move
+//   mma     issuing warp: [S0 K^T | S0 Q^T] into tensor memory; under it the compute warps move
 //           the PREVIOUS item's finished state from tensor memory to a staging tile, which a TMA
 //           store sends out
-//   solve   warps 0-3, one thread per state row: the recurrence; delta (tape) and y leave for
-//           global memory; E goes to tensor memory as the A operand of the last product
-//   mma     helper lane: the accumulator += E K; then, under the next split, the next item's Gram
-//           products, which the helper warp scales by the gate products into the other table slot
+//   solve   two threads per state row: warps 0-3 run the recurrence for delta four steps at a time,
+//           hand the deltas over through shared memory, write the tape and put E into tensor memory
+//           as the A operand of the last product; warps 4-7 form y from the deltas
+//   mma     issuing warp: the accumulator += E K, then the next item's Gram products
+//   tables  scalar warp: gates and betas of the item after the next fetched into registers, those of
+//           the next item published; the next item's Gram rows out of tensor memory, scaled by the
+//           gate products (and beta) into the other table slot
+// Hand-offs that only one side waits for use named barriers (bar.arrive on the other side).
 // Every wait is bounded; a wait that gives up sets the device status word and the CTA leaves.
 //
 // Reference semantics: Sources/DFlash/DFlashKernels.swift:122-199 (kernel), :409-466 (CPU statement).

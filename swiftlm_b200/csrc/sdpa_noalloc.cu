@@ -14,7 +14,8 @@
 //     and lets the CUDA runtime load the kernels; make that first call before any stream
 //     capture starts;
 //   * the array keeps whatever the previous call left in it; nothing in it has to start at
-//     zero, because every launch rewrites the slot table entries and partials it later reads;
+//     zero, because every launch rewrites the slot table entries and partials it later reads,
+//     and the arrival flags carry a tag that is new for every launch;
 //   * two calls that overlap on the GPU (different streams, or different threads) race on the
 //     array: serialise them, or give the second caller dflash_verify_sdpa with its own buffer.
 // The entry point allocates nothing: no cudaMalloc / cudaFree, no library routine that
