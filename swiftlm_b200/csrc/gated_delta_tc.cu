@@ -356,8 +356,8 @@ gdn_tc_kernel(const __grid_constant__ TcMaps maps, const GdnArgs a, int* status)
 #pragma unroll
       for (int t = 0; t < kT; ++t) g_T *= sc[t];
 #pragma unroll
-      for (int bb = 0; bb < 2; ++bb) {
-        const int box = 2 * half + bb;                  // 32 state columns
+      for (int pass = 0; pass < 2; ++pass) {
+        const int box = 2 * pass + half;                // 32 state columns; pass = operand chunk (64 columns)
         float4 x4[8];
 #pragma unroll
         for (int g = 0; g < 8; ++g)
@@ -371,7 +371,7 @@ gdn_tc_kernel(const __grid_constant__ TcMaps maps, const GdnArgs a, int* status)
           acc[4 * g + 3] = __float_as_uint(g_T * x4[g].w);
         }
         ptx::tmem_st32(tmem + lane_addr + kColD + 128 * buf + 32 * box, acc);
-        // operand tiles: chunk = box / 2 (64 columns), 16-byte granule = 8 columns
+        // operand tiles: 16-byte granule = 8 columns
 #pragma unroll
         for (int gg8 = 0; gg8 < 4; ++gg8) {
           const float x[8] = {x4[2 * gg8].x, x4[2 * gg8].y, x4[2 * gg8].z, x4[2 * gg8].w,
@@ -382,14 +382,35 @@ gdn_tc_kernel(const __grid_constant__ TcMaps maps, const GdnArgs a, int* status)
             hi[i] = pack_trunc(x[2 * i], x[2 * i + 1]);
             lo[i] = pack_rn(x[2 * i] - trunc16(x[2 * i]), x[2 * i + 1] - trunc16(x[2 * i + 1]));
           }
-          const int gran = (box & 1) * 4 + gg8;
-          uint8_t* dst = sm + kX + (box >> 1) * 16384 + row * 128 + ((gran ^ (row & 7)) << 4);
+          const int gran = half * 4 + gg8;
+          uint8_t* dst = sm + kX + pass * 16384 + row * 128 + ((gran ^ (row & 7)) << 4);
           *reinterpret_cast<uint4*>(dst) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
           *reinterpret_cast<uint4*>(dst + 32768) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+        }
+        if (pass == 0) {
+          // the first chunk is complete: its eight products can run under the second pass (named barrier 5)
+          ptx::fence_proxy_async();
+          asm volatile("bar.arrive 5, %0;" ::"n"(kPairThreads) : "memory");
         }
       }
       ptx::fence_proxy_async();
       ptx::tmem_st_wait();
+    } else if (mma) {
+      asm volatile("bar.sync 5, %0;" ::"n"(kPairThreads) : "memory");
+      if (lane == 0) {
+        ptx::tc_fence_after();
+        const uint32_t kq_addr = ptx::smem_u32(KQ), x_addr = ptx::smem_u32(sm + kX);
+#pragma unroll
+        for (int sp = 0; sp < 2; ++sp)
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk) {
+            const uint64_t da = make_desc(x_addr + sp * 32768, 16, 1024) + 2 * kk;
+            const uint64_t db = make_desc(kq_addr, 16, 1024) + 2 * kk;
+            if (sp == 0 && kk == 0) ptx::umma_ss_first(tmem + kColW, da, db, kIdescW);
+            else ptx::umma_ss_acc(tmem + kColW, da, db, kIdescW);
+          }
+      }
+      __syncwarp();
     }
     ptx::tc_fence_before();
     PH(1);
@@ -399,8 +420,8 @@ gdn_tc_kernel(const __grid_constant__ TcMaps maps, const GdnArgs a, int* status)
     PH(2);
 
     if (mma) {
-      // ---- issuing warp: the next item's state load (its landing tile is free again), this item's
-      //      [S0 K^T | S0 Q^T], then the next item's K, Q, V loads ----
+      // ---- issuing warp: the next item's state load (its landing tile is free again), the second
+      //      chunk's products, then the next item's K, Q, V loads ----
       if (has_next) issue_state_load(b_nxt, hv_nxt, buf ^ 1);
       if (lane == 0) {
         ptx::tc_fence_after();
@@ -408,11 +429,10 @@ gdn_tc_kernel(const __grid_constant__ TcMaps maps, const GdnArgs a, int* status)
 #pragma unroll
         for (int sp = 0; sp < 2; ++sp)
 #pragma unroll
-          for (int kk = 0; kk < 8; ++kk) {
-            const uint64_t da = make_desc(x_addr + sp * 32768 + (kk >> 2) * 16384, 16, 1024) + 2 * (kk & 3);
-            const uint64_t db = make_desc(kq_addr + (kk >> 2) * 4096, 16, 1024) + 2 * (kk & 3);
-            if (sp == 0 && kk == 0) ptx::umma_ss_first(tmem + kColW, da, db, kIdescW);
-            else ptx::umma_ss_acc(tmem + kColW, da, db, kIdescW);
+          for (int kk = 0; kk < 4; ++kk) {
+            const uint64_t da = make_desc(x_addr + sp * 32768 + 16384, 16, 1024) + 2 * kk;
+            const uint64_t db = make_desc(kq_addr + 4096, 16, 1024) + 2 * kk;
+            ptx::umma_ss_acc(tmem + kColW, da, db, kIdescW);
           }
         ptx::umma_commit(&bars[3]);
       }
@@ -501,11 +521,16 @@ gdn_tc_kernel(const __grid_constant__ TcMaps maps, const GdnArgs a, int* status)
 #pragma unroll
             for (int e = 0; e < 4; ++e) d[4 * g4 + e] = 0.f;
           }
-        }
+          // hand the group over to the y threads (named barriers 6-9: this side only signals)
 #pragma unroll
-        for (int t = 0; t < kT; ++t) dx[t * kD + row] = d[t];
+          for (int e = 0; e < 4; ++e) dx[(4 * g4 + e) * kD + row] = d[4 * g4 + e];
+          __threadfence_block();
+          if (g4 == 0) asm volatile("bar.arrive 6, %0;" ::"n"(kComputeThreads) : "memory");
+          else if (g4 == 1) asm volatile("bar.arrive 7, %0;" ::"n"(kComputeThreads) : "memory");
+          else if (g4 == 2) asm volatile("bar.arrive 8, %0;" ::"n"(kComputeThreads) : "memory");
+          else asm volatile("bar.arrive 9, %0;" ::"n"(kComputeThreads) : "memory");
+        }
       }
-      asm volatile("bar.sync 2, %0;" ::"n"(kComputeThreads) : "memory");
       PH(4);
       if (w < 4) {
         // E = Gam[s,T] delta_s, split exactly into three bf16 terms, as the A operand (pairs of steps per column)
@@ -533,8 +558,6 @@ gdn_tc_kernel(const __grid_constant__ TcMaps maps, const GdnArgs a, int* status)
         const float4* tkq = reinterpret_cast<const float4*>(tab + kTabKQ);
         const float* gp = reinterpret_cast<const float*>(tab + kTabGp);
         __nv_bfloat16* yout = reinterpret_cast<__nv_bfloat16*>(a.y);
-#pragma unroll
-        for (int t = 0; t < kT; ++t) d[t] = dx[t * kD + row];
         float gpv[kT];
 #pragma unroll
         for (int q4 = 0; q4 < 4; ++q4) {
@@ -543,6 +566,12 @@ gdn_tc_kernel(const __grid_constant__ TcMaps maps, const GdnArgs a, int* status)
         }
 #pragma unroll
         for (int g4 = 0; g4 < 4; ++g4) {
+          if (g4 == 0) asm volatile("bar.sync 6, %0;" ::"n"(kComputeThreads) : "memory");
+          else if (g4 == 1) asm volatile("bar.sync 7, %0;" ::"n"(kComputeThreads) : "memory");
+          else if (g4 == 2) asm volatile("bar.sync 8, %0;" ::"n"(kComputeThreads) : "memory");
+          else asm volatile("bar.sync 9, %0;" ::"n"(kComputeThreads) : "memory");
+#pragma unroll
+          for (int e = 0; e < 4; ++e) d[4 * g4 + e] = dx[(4 * g4 + e) * kD + row];
           float y[4] = {0.f, 0.f, 0.f, 0.f};
           if ((bits >> (4 * g4)) & 0xFu) {
 #pragma unroll
