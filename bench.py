@@ -296,6 +296,8 @@ def run_gpu(args):
 
     # ---- verify attention, configs[2] (rank-local, same on every rank) ----
     sd = run_sdpa(torch, kernels, device, args, peaks)
+    # ---- long-context verify attention, configs[3]: the 16 (sequence, KV head) pairs sharded over the ranks ----
+    sd_long = run_sdpa_long(torch, kernels, device, rank, world, peaks, max_over_ranks)
 
     if world > 1:
         dist.barrier()
@@ -332,6 +334,7 @@ def run_gpu(args):
         "gpu_launches": launches,
         "clocks": clocks,
         "sdpa": sd,
+        "sdpa_long": sd_long,
     }
     print(json.dumps(line))
     if world > 1:
@@ -379,6 +382,55 @@ def run_sdpa(torch, kernels, device, args, peaks):
                          "frac_of_bf16_peak": tflops / peaks["bf16_tflops"],
                          "note": "arithmetic intensity 128 FLOP/B is below the ridge (~252): the HBM roofline "
                                  "caps this shape at ~49% of dense bf16 peak"}}
+
+
+def run_sdpa_long(torch, kernels, device, rank, world, peaks, max_over_ranks):
+    """configs[3]: batch 8, 16 q / 2 KV heads, D = 256, KV lengths 40960 and 102400 (+16 block tokens), KV in pages of 256
+    tokens behind a seeded random page table.  The 16 (sequence, KV head) pairs are dealt to the ranks
+    (swiftlm_b200.partition); a rank sees its pairs as a batch of single-KV-head sequences.  Strong scaling."""
+    from swiftlm_b200 import partition
+    B, Hq, Hkv, D, page = 8, 16, 2, 256, 256
+    G = Hq // Hkv
+    lo, hi = partition.plan(B * Hkv, world)[rank]
+    pairs = hi - lo
+    out = []
+    for n_ctx in (40960, 102400):
+        N = n_ctx + 16
+        pages_per_seq = (N + page - 1) // page
+        g = torch.Generator(device=device).manual_seed(SEED + 3000 + rank)
+        ms = 0.0
+        if pairs > 0:
+            pool_pages = pairs * pages_per_seq
+            q = torch.randn(pairs, G, 16, D, device=device, generator=g).bfloat16()
+            kp = torch.randn(pool_pages, 1, page, D, device=device, generator=g).bfloat16()
+            vp = torch.randn(pool_pages, 1, page, D, device=device, generator=g).bfloat16()
+            table = torch.randperm(pool_pages, device=device, generator=g).to(torch.int32).reshape(pairs, pages_per_seq)
+            lens = torch.full((pairs,), N, dtype=torch.int32, device=device)
+            o = torch.empty_like(q)
+            call = lambda: kernels.batched_sdpa_2pass(q, kp, vp, 1.0 / 16.0, kv_len=lens, page_table=table, n_max=N, out=o)  # noqa: E731
+            for _ in range(3):
+                call()
+            torch.cuda.synchronize()
+            reps = []
+            for _ in range(5):
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                for _ in range(4):
+                    call()
+                e1.record()
+                torch.cuda.synchronize()
+                reps.append(e0.elapsed_time(e1) / 4)
+            kernels.device_status()
+            ms = statistics.median(reps)
+            del q, kp, vp, o
+        ms = max_over_ranks(ms)
+        byts = 2.0 * B * Hkv * N * D * 2 + 2.0 * B * Hq * 16 * D * 2
+        flops = 4.0 * B * Hq * 16 * N * D
+        out.append({"kv_len": N, "ms_per_call": ms, "tflops": flops / (ms * 1e-3) / 1e12, "gbs": byts / (ms * 1e-3) / 1e9,
+                    "frac_of_hbm_peak_per_gpu": byts / (ms * 1e-3) / 1e9 / (peaks["hbm_gbs"] * world)})
+    return {"config": "configs[3]: B=8, Hq=16, Hkv=2, T=16, D=256, paged KV (256-token pages, random page table), "
+                      f"16 (sequence, KV head) pairs over {world} GPU(s); K/V per call exceed L2; 4 calls per timed burst",
+            "scaling": "strong", "results": out}
 
 
 def run_case(args):

@@ -153,3 +153,33 @@ def test_full_size_properties_benchmark_config():
     assert float((c.float() - 0.5).abs().max()) < 1e-2
     want = CO.verify_sdpa(q[:1].float().cpu().numpy(), k[:1].float().cpu().numpy(), v[:1].float().cpu().numpy(), 1.0 / 16)
     assert np.abs(out[:1].float().cpu().numpy() - want).max() < ATOL
+
+
+def test_long_context_paged_matches_oracle_and_dense():
+    """configs[3] scale on one (sequence, KV head) pair per batch row: 40 960 committed keys + the block, 256-token
+    pages behind a random page table.  Paged and dense runs must agree bit for bit, and both with the oracle."""
+    B, Hq, Hkv, D, pt = 2, 8, 1, 256, 256
+    N = 40960 + 16
+    x = O.make_sdpa_inputs(B, Hq, Hkv, N, D, 1200, "bf16")
+    dt = torch.bfloat16
+    dense = run(x, "bf16")
+    pages = (N + pt - 1) // pt
+    rng = np.random.default_rng(11)
+    perm = rng.permutation(B * pages).reshape(B, pages).astype(np.int32)
+    kp = np.zeros((B * pages, Hkv, pt, D), np.float32)
+    vp = np.zeros_like(kp)
+    for b in range(B):
+        for pg in range(pages):
+            lo, hi = pg * pt, min(N, (pg + 1) * pt)
+            kp[perm[b, pg], :, :hi - lo] = x["k"][b, :, lo:hi]
+            vp[perm[b, pg], :, :hi - lo] = x["v"][b, :, lo:hi]
+    lens = np.full((B,), N, np.int32)
+    paged = K().batched_sdpa_2pass(dev(x["q"], dt), dev(kp, dt), dev(vp, dt), float(x["scale"]), kv_len=lens,
+                                   page_table=dev(perm), n_max=N)
+    torch.cuda.synchronize()
+    K().device_status()
+    dense_len = run(x, "bf16", kv_len=lens)
+    assert torch.equal(paged, dense_len)
+    want = CO.verify_sdpa(x["q"], x["k"], x["v"], float(x["scale"]))
+    assert np.abs(dense.float().cpu().numpy() - want).max() < ATOL
+    assert np.abs(paged.float().cpu().numpy() - want).max() < ATOL
