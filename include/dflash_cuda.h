@@ -136,6 +136,20 @@ int32_t dflash_accept_lengths(const uint32_t* posterior, const int32_t* verify_i
                               void* stream);
 
 /* ---------------------------------------------------------------------------------------------
+ * Conv-window rebuild of the rollback cache: replaces RecurrentRollbackCache.rebuildConvState,
+ * Sources/DFlash/RecurrentRollbackCache.swift:139-158.
+ *   out = concat(conv_snapshot [B,keep,C], qkv [B,T,C])[:, steps : min(steps + keep, keep + T)]
+ * conv_snapshot may be NULL (zeros, :150-153).  Rows are row_bytes bytes each (a multiple of 16).
+ * steps_per_seq == NULL: every sequence uses steps_all and *rows_out (host) receives the window
+ * length, which is shorter than keep when steps_all + keep runs past the end, as in the reference.
+ * steps_per_seq != NULL (device int32[B], e.g. replay_len of dflash_accept_lengths): per-sequence
+ * starts, clamped to T, keep rows each; out is [B,keep,C].
+ */
+int32_t dflash_rebuild_conv_state(const void* conv_snapshot, const void* qkv, const int32_t* steps_per_seq,
+                                  int32_t steps_all, void* out, int32_t B, int32_t T, int32_t keep,
+                                  int64_t row_bytes, int32_t* rows_out, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
  * TurboQuant 3-bit KV codec, 128-dimension blocks (a 256-dimension head vector is two blocks).
  * Follows the codec as stated in the reference's tests/test_turbo_quant.cpp: V path :69-75, K path
  * with residual sign bits :85-98, primitives :14-22 (the production encoder lives in a dependency

@@ -25,6 +25,7 @@ SIGNATURES = {
     "dflash_verify_sdpa_noalloc": (_i32, [_vp] * 7 + [_i32] * 8 + [_f32, _i32, _i32, _vp]),
     "dflash_greedy_tokens": (_i32, [_vp, _vp, _vp, _i32, _i32, _i32, _vp]),
     "dflash_accept_lengths": (_i32, [_vp] * 5 + [_i32, _i32, _vp]),
+    "dflash_rebuild_conv_state": (_i32, [_vp, _vp, _vp, _i32, _vp, _i32, _i32, _i32, C.c_int64, C.POINTER(_i32), _vp]),
     "dflash_turbo_encode": (_i32, [_vp] * 5 + [C.c_int64, _i32, _i32, _vp]),
     "dflash_turbo_decode": (_i32, [_vp] * 5 + [C.c_int64, _i32, _i32, _vp]),
     "dflash_partition_plan": (_i32, [_i32, _i32, C.POINTER(_i32)]),

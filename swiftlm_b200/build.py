@@ -85,6 +85,17 @@ def build(force: bool = False, verbose: bool = False) -> str:
         if r.returncode != 0:
             sys.stderr.write(r.stdout + r.stderr)
             raise RuntimeError("building dflash_kernel_bench failed")
+    # host program: self-test of the C++ host layer (dflash_host.hpp)
+    st_src = os.path.join(PKG, "host", "dflash_host_selftest.cu")
+    st_hdr = os.path.join(PKG, "host", "dflash_host.hpp")
+    st_bin = os.path.join(PKG, "bin", "dflash_host_selftest")
+    if force or _newer(st_bin, [st_src, st_hdr, LIB] + headers):
+        cmd = [nvcc, "-std=c++17", "-O2", "-gencode", "arch=compute_100a,code=sm_100a", st_src, "-o", st_bin,
+               "-L" + LIBDIR, "-ldflash_cuda", "-Xlinker", "-rpath", "-Xlinker", "$ORIGIN/../lib"]
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode != 0:
+            sys.stderr.write(r.stdout + r.stderr)
+            raise RuntimeError("building dflash_host_selftest failed")
     return LIB
 
 

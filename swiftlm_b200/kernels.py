@@ -11,6 +11,8 @@ from __future__ import annotations
 
 from typing import Optional, Tuple
 
+import ctypes as C
+
 import torch
 
 from . import _lib
@@ -222,6 +224,32 @@ def gated_delta_into(q, k, v, g, beta, state, n_per_seq, y, state_out, tape=None
         _ptr(q), _ptr(k), _ptr(v), _ptr(g), _ptr(beta), _ptr(state), _ptr(mask_t), _ptr(n_per_seq),
         _ptr(y), _ptr(state_out), _ptr(tape), B, T, Hk, Hv, Dk, Dv, int(g.dim() == 4), _DT[q.dtype], mdt,
         _stream()))
+
+
+def rebuild_conv_state(conv_snapshot: Optional[torch.Tensor], qkv: torch.Tensor, steps, keep: int) -> torch.Tensor:
+    """RecurrentRollbackCache.rebuildConvState (Sources/DFlash/RecurrentRollbackCache.swift:139-158) on the device:
+    concat(conv_snapshot [B,keep,C], qkv [B,T,C])[:, steps : min(steps + keep, keep + T)].  `steps` is an int
+    (the reference's accepted_steps) or a device int32 tensor [B] of per-sequence step counts (keep rows each)."""
+    _need_cuda(qkv)
+    qkv = qkv.contiguous()
+    B, T, Cdim = qkv.shape
+    row_bytes = Cdim * qkv.element_size()
+    snap = None if conv_snapshot is None else conv_snapshot.to(qkv.dtype).contiguous()
+    rows = C.c_int32(0)
+    out = torch.empty(B, keep, Cdim, dtype=qkv.dtype, device=qkv.device)
+    if isinstance(steps, torch.Tensor):
+        st = steps.to(torch.int32).contiguous()
+        _lib.check(_lib.lib().dflash_rebuild_conv_state(_ptr(snap), _ptr(qkv), _ptr(st), 0, _ptr(out), B, T, keep,
+                                                       row_bytes, C.byref(rows), _stream()))
+        return out
+    # scalar count: the window is [B, rows, C] with rows <= keep, written densely at the front of `out`
+    end = min(int(steps) + keep, keep + T)
+    n_rows = max(end - int(steps), 0)
+    out = torch.empty(B, n_rows, Cdim, dtype=qkv.dtype, device=qkv.device)
+    if n_rows:
+        _lib.check(_lib.lib().dflash_rebuild_conv_state(_ptr(snap), _ptr(qkv), None, int(steps), _ptr(out), B, T, keep,
+                                                       row_bytes, C.byref(rows), _stream()))
+    return out
 
 
 def turbo_encode(x: torch.Tensor, is_key: bool):

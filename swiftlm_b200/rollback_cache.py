@@ -72,7 +72,8 @@ class RecurrentRollbackCache:
         self.clear_transients()
 
     def rebuild_conv_state(self, accepted_steps: Union[int, torch.Tensor]) -> Optional[torch.Tensor]:
-        """:139-158.  With a tensor of per-sequence step counts the window is gathered per row."""
+        """:139-158 through dflash_rebuild_conv_state.  With a tensor of per-sequence step counts every
+        sequence gets its own window start (keep rows each)."""
         qkv = self._tape_qkv
         if qkv is None:
             return self.state[0]
@@ -80,16 +81,7 @@ class RecurrentRollbackCache:
         if keep <= 0:
             return None
         snap = self._snapshot[0] if self._snapshot else None
-        prefix = snap if snap is not None else torch.zeros(qkv.shape[0], keep, qkv.shape[-1], dtype=qkv.dtype,
-                                                           device=qkv.device)
-        conv_input = torch.cat([prefix, qkv], dim=1)                        # :154
-        if isinstance(accepted_steps, torch.Tensor):
-            idx = accepted_steps.to(torch.long).view(-1, 1) + torch.arange(keep, device=qkv.device).view(1, -1)
-            idx = idx.clamp_(max=conv_input.shape[1] - 1)
-            return torch.gather(conv_input, 1, idx.unsqueeze(-1).expand(-1, -1, conv_input.shape[-1]))
-        start = int(accepted_steps)
-        end = min(start + keep, conv_input.shape[1])                        # :156
-        return conv_input[:, start:end]
+        return kernels.rebuild_conv_state(snap, qkv, accepted_steps, keep)   # :148-157 on the device
 
     def clear_transients(self) -> None:                                     # :163-170
         self._armed = False

@@ -15,34 +15,6 @@ from swiftlm_b200 import partition
 from swiftlm_b200.rollback_cache import RecurrentRollbackCache, restore_after_acceptance
 
 
-def test_conv_window_rebuild_matches_oracle_exactly():
-    c = RecurrentRollbackCache(conv_kernel_size=4)
-    snap = torch.arange(2 * 3 * 5).reshape(2, 3, 5).float()
-    qkv = 100 + torch.arange(2 * 16 * 5).reshape(2, 16, 5).float()
-    c.state = [snap, None]
-    c.arm_rollback()
-    c.record_tape(None, None, None, qkv)
-    for steps in (1, 2, 7, 16):
-        got = c.rebuild_conv_state(steps)
-        want = O.rebuild_conv_state(snap.numpy(), qkv.numpy(), steps, 4)
-        np.testing.assert_array_equal(got.numpy(), want)
-    # per-sequence step counts: each row equals the scalar rule for its own count
-    steps = torch.tensor([3, 12])
-    got = c.rebuild_conv_state(steps)
-    for b in range(2):
-        want = O.rebuild_conv_state(snap.numpy()[b:b + 1], qkv.numpy()[b:b + 1], int(steps[b]), 4)
-        np.testing.assert_array_equal(got[b:b + 1].numpy(), want)
-    # no snapshot -> zero prefix; kernel size 1 -> no window
-    c2 = RecurrentRollbackCache(conv_kernel_size=4)
-    c2.arm_rollback()
-    c2.record_tape(None, None, None, qkv)
-    np.testing.assert_array_equal(c2.rebuild_conv_state(1).numpy(), O.rebuild_conv_state(None, qkv.numpy(), 1, 4))
-    c3 = RecurrentRollbackCache(conv_kernel_size=1)
-    c3.arm_rollback()
-    c3.record_tape(None, None, None, qkv)
-    assert c3.rebuild_conv_state(1) is None
-
-
 def test_arm_record_clear_and_full_accept_shortcut():
     c = RecurrentRollbackCache()
     assert not c.is_armed

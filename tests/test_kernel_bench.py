@@ -30,3 +30,20 @@ def test_bench_runs_every_section():
         med, mn, mx = float(m.group(1)), float(m.group(2)), float(m.group(3))
         assert 0 < mn <= med <= mx
     assert r.stdout.rstrip().endswith("Done.")
+
+
+SELFTEST = os.path.join(os.path.dirname(build.__file__), "bin", "dflash_host_selftest")
+
+
+def test_host_selftest_binary_is_built():
+    build.build()
+    assert os.access(SELFTEST, os.X_OK)
+
+
+@pytest.mark.gpu
+def test_cpp_host_layer_selftest():
+    """The C++ mirror of DFlashKernels / RecurrentRollbackCache (swiftlm_b200/host/dflash_host.hpp) on the GPU."""
+    build.build()
+    r = subprocess.run([SELFTEST], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stdout + r.stderr
+    assert "all checks passed" in r.stdout and "FAIL" not in r.stdout
