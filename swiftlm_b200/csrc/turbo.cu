@@ -10,8 +10,9 @@
 //
 // The codec is integer/byte work whose results must match the reference bit for bit, so every
 // floating-point operation is performed in the reference's order with explicitly rounded
-// adds and multiplies (no fused multiply-add): one thread owns one 128-block and walks it
-// sequentially in shared memory (element i of thread t at [i][t]: conflict-free).
+// adds and multiplies (no fused multiply-add).  One thread owns one 128-block.  The encoder walks
+// it sequentially in shared memory (element i of thread t at [i][t]: conflict-free); the decoder,
+// which sits on the attention read path, keeps the block in registers.
 #include "common.cuh"
 #include "turbo_tables.cuh"
 
@@ -128,34 +129,115 @@ turbo_encode_kernel(const InT* __restrict__ x, uint8_t* __restrict__ packed, uin
   rnorm[v] = to_f16_trunc(__fsqrt_rn(rns));
 }
 
-template <typename OutT>
-__global__ void __launch_bounds__(kThreadsPerCta)
+// ---- decode: one thread per 128-block, the block lives in registers ----------------------------
+// The Walsh-Hadamard butterflies of one stage are independent of each other, so running them from
+// registers in any order gives the same bits as the reference's loops; the stages keep their order.
+constexpr int kDecThreads = 64;
+
+__device__ __forceinline__ float flip(float x, unsigned int neg_word, int bit) {   // x * (+-1), exactly
+  return __uint_as_float(__float_as_uint(x) ^ (((neg_word >> bit) & 1u) << 31));
+}
+template <int H> __device__ __forceinline__ void wht_stage(float (&x)[kBlock]) {
+#pragma unroll
+  for (int p = 0; p < kBlock / 2; ++p) {
+    const int j = (p / H) * 2 * H + (p % H);   // the p-th butterfly of the stage
+    const float a = x[j], b = x[j + H];
+    x[j] = __fadd_rn(a, b);
+    x[j + H] = __fsub_rn(a, b);
+  }
+}
+__device__ __forceinline__ void rot_regs(float (&x)[kBlock], const unsigned int* first, const unsigned int* second) {
+  unsigned int f[4], s[4];
+#pragma unroll
+  for (int w = 0; w < 4; ++w) { f[w] = first[w]; s[w] = second[w]; }
+#pragma unroll
+  for (int i = 0; i < kBlock; ++i) x[i] = flip(x[i], f[i >> 5], i & 31);
+  wht_stage<1>(x); wht_stage<2>(x); wht_stage<4>(x); wht_stage<8>(x); wht_stage<16>(x); wht_stage<32>(x); wht_stage<64>(x);
+#pragma unroll
+  for (int i = 0; i < kBlock; ++i) x[i] = flip(__fmul_rn(x[i], 0.08838834764831845f), s[i >> 5], i & 31);
+}
+
+template <typename OutT> __device__ __forceinline__ void store8_out(OutT* dst, const float (&v)[8]);
+template <> __device__ __forceinline__ void store8_out<float>(float* dst, const float (&v)[8]) {
+  *reinterpret_cast<float4*>(dst) = make_float4(v[0], v[1], v[2], v[3]);
+  *reinterpret_cast<float4*>(dst + 4) = make_float4(v[4], v[5], v[6], v[7]);
+}
+template <> __device__ __forceinline__ void store8_out<__nv_bfloat16>(__nv_bfloat16* dst, const float (&v)[8]) {
+  __nv_bfloat162 p[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) p[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+  *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(p);
+}
+template <> __device__ __forceinline__ void store8_out<__half>(__half* dst, const float (&v)[8]) {
+  __half2 p[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) p[i] = __floats2half2_rn(v[2 * i], v[2 * i + 1]);
+  *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(p);
+}
+
+template <typename OutT, bool IS_KEY>
+__global__ void __launch_bounds__(kDecThreads)
 turbo_decode_kernel(const uint8_t* __restrict__ packed, const uint8_t* __restrict__ signs,
                     const uint16_t* __restrict__ norm, const uint16_t* __restrict__ rnorm, OutT* __restrict__ out,
-                    long long n, int is_key) {
-  extern __shared__ float sh[];
-  const long long v = (long long)blockIdx.x * kThreadsPerCta + threadIdx.x;
+                    long long n) {
+  extern __shared__ float sh[];                      // [8][kDecThreads] centroid table, then (keys) [128][kDecThreads]
+  float* c3 = sh;                                    // one copy of the 8 centroids per thread column: no bank conflicts
+  for (int i = threadIdx.x; i < 8 * kDecThreads; i += kDecThreads) c3[i] = TURBO_C3[i / kDecThreads];
+  __syncthreads();
+  const long long v = (long long)blockIdx.x * kDecThreads + threadIdx.x;
   if (v >= n) return;
-  const Vec dec{sh + threadIdx.x};
-  const Vec sf{sh + kBlock * kThreadsPerCta + threadIdx.x};
-  const uint8_t* pk = packed + v * 48;
-  for (int g8 = 0; g8 < 16; ++g8) {
-    const uint32_t bits = pk[3 * g8] | ((uint32_t)pk[3 * g8 + 1] << 8) | ((uint32_t)pk[3 * g8 + 2] << 16);
-    for (int e = 0; e < 8; ++e) dec[g8 * 8 + e] = TURBO_C3[(bits >> (3 * e)) & 7u];
+  float* stash = sh + 8 * kDecThreads + threadIdx.x;   // element i at stash[i * kDecThreads]
+  float x[kBlock];
+  if (IS_KEY) {
+    // residual term first: qrot(signs) * (QJL_C / 128 * rnorm), parked in shared memory (:96-98)
+    const uint4 sg = *reinterpret_cast<const uint4*>(signs + v * 16);
+    const unsigned int sw[4] = {sg.x, sg.y, sg.z, sg.w};
+#pragma unroll
+    for (int i = 0; i < kBlock; ++i) x[i] = (sw[i >> 5] >> (i & 31)) & 1u ? 1.f : -1.f;
+    rot_regs(x, TURBO_Q1_NEG, TURBO_Q2_NEG);
+    const float qs = __fmul_rn(__fdiv_rn(TURBO_QJL_C, 128.f), from_f16_bits(rnorm[v]));
+#pragma unroll
+    for (int i = 0; i < kBlock; ++i) stash[i * kDecThreads] = __fmul_rn(x[i], qs);
   }
-  rot(dec, TURBO_S2_NEG, TURBO_S1_NEG);
+  {
+    const uint4* pk = reinterpret_cast<const uint4*>(packed + v * 48);
+    const uint4 p0 = pk[0], p1 = pk[1], p2 = pk[2];
+    const unsigned int w[13] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w, p2.x, p2.y, p2.z, p2.w, 0u};
+#pragma unroll
+    for (int i = 0; i < kBlock; ++i) {
+      const int bit = 3 * i, word = bit >> 5, off = bit & 31;
+      unsigned int idx = w[word] >> off;
+      if (off > 29) idx |= w[word + 1] << (32 - off);
+      x[i] = c3[(idx & 7u) * kDecThreads + threadIdx.x];
+    }
+  }
+  rot_regs(x, TURBO_S2_NEG, TURBO_S1_NEG);
   const float sc = from_f16_bits(norm[v]);
   OutT* dst = out + v * kBlock;
-  if (!is_key) {
-    for (int i = 0; i < kBlock; ++i) dst[i] = from_f32<OutT>(__fmul_rn(dec[i], sc));           // :75
-    return;
+#pragma unroll
+  for (int g8 = 0; g8 < kBlock / 8; ++g8) {
+    float o[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const int i = g8 * 8 + e;
+      o[e] = IS_KEY ? __fmul_rn(__fadd_rn(x[i], stash[i * kDecThreads]), sc) : __fmul_rn(x[i], sc);
+    }
+    store8_out<OutT>(dst + g8 * 8, o);
   }
-  const uint8_t* sg = signs + v * 16;
-  for (int i = 0; i < kBlock; ++i) sf[i] = (sg[i >> 3] >> (i & 7)) & 1u ? 1.f : -1.f;
-  rot(sf, TURBO_Q1_NEG, TURBO_Q2_NEG);
-  const float qs = __fmul_rn(__fdiv_rn(TURBO_QJL_C, 128.f), from_f16_bits(rnorm[v]));           // :98
-  for (int i = 0; i < kBlock; ++i)
-    dst[i] = from_f32<OutT>(__fmul_rn(__fadd_rn(dec[i], __fmul_rn(sf[i], qs)), sc));
+}
+
+template <typename OutT>
+int32_t launch_decode_typed(const uint8_t* packed, const uint8_t* signs, const uint16_t* norm, const uint16_t* rnorm, void* out,
+                            long long n, int is_key, cudaStream_t stream) {
+  const unsigned grid = (unsigned)((n + kDecThreads - 1) / kDecThreads);
+  const size_t smem = (8 + (is_key ? kBlock : 0)) * kDecThreads * sizeof(float);
+  if (is_key) {
+    DFLASH_CUDA_CHECK(cudaFuncSetAttribute(turbo_decode_kernel<OutT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    turbo_decode_kernel<OutT, true><<<grid, kDecThreads, smem, stream>>>(packed, signs, norm, rnorm, (OutT*)out, n);
+  } else {
+    turbo_decode_kernel<OutT, false><<<grid, kDecThreads, smem, stream>>>(packed, signs, norm, rnorm, (OutT*)out, n);
+  }
+  return DFLASH_OK;
 }
 
 }  // namespace
@@ -188,25 +270,20 @@ int32_t launch_turbo_encode(const void* x, uint8_t* packed, uint8_t* signs, uint
 
 int32_t launch_turbo_decode(const uint8_t* packed, const uint8_t* signs, const uint16_t* norm, const uint16_t* rnorm,
                             void* out, long long n, int is_key, int out_dtype, cudaStream_t stream) {
-  const unsigned grid = (unsigned)((n + kThreadsPerCta - 1) / kThreadsPerCta);
-  const size_t smem = 2 * kBlock * kThreadsPerCta * sizeof(float);
+  if (((uintptr_t)packed & 15) || (is_key && ((uintptr_t)signs & 15)) || ((uintptr_t)out & 15)) {
+    set_error("turbo_decode: packed, signs and out must be 16-byte aligned");
+    return DFLASH_ERR_INVALID_ARG;
+  }
+  int32_t st;
   switch (out_dtype) {
-    case DFLASH_F32:
-      DFLASH_CUDA_CHECK(cudaFuncSetAttribute(turbo_decode_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-      turbo_decode_kernel<float><<<grid, kThreadsPerCta, smem, stream>>>(packed, signs, norm, rnorm, (float*)out, n, is_key);
-      break;
-    case DFLASH_BF16:
-      DFLASH_CUDA_CHECK(cudaFuncSetAttribute(turbo_decode_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-      turbo_decode_kernel<__nv_bfloat16><<<grid, kThreadsPerCta, smem, stream>>>(packed, signs, norm, rnorm, (__nv_bfloat16*)out, n, is_key);
-      break;
-    case DFLASH_F16:
-      DFLASH_CUDA_CHECK(cudaFuncSetAttribute(turbo_decode_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-      turbo_decode_kernel<__half><<<grid, kThreadsPerCta, smem, stream>>>(packed, signs, norm, rnorm, (__half*)out, n, is_key);
-      break;
+    case DFLASH_F32: st = launch_decode_typed<float>(packed, signs, norm, rnorm, out, n, is_key, stream); break;
+    case DFLASH_BF16: st = launch_decode_typed<__nv_bfloat16>(packed, signs, norm, rnorm, out, n, is_key, stream); break;
+    case DFLASH_F16: st = launch_decode_typed<__half>(packed, signs, norm, rnorm, out, n, is_key, stream); break;
     default:
       set_error("turbo_decode: unsupported dtype %d", out_dtype);
       return DFLASH_ERR_UNSUPPORTED;
   }
+  if (st != DFLASH_OK) return st;
   DFLASH_LAUNCH_CHECK();
   count_launch();
   return DFLASH_OK;
