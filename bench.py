@@ -298,6 +298,10 @@ def run_gpu(args):
     sd = run_sdpa(torch, kernels, device, args, peaks)
     # ---- long-context verify attention, configs[3]: the 16 (sequence, KV head) pairs sharded over the ranks ----
     sd_long = run_sdpa_long(torch, kernels, device, rank, world, peaks, max_over_ranks)
+    # ---- the composed verify step, configs[4]: 64 sequences sharded by sequence over the ranks ----
+    del x
+    torch.cuda.empty_cache()
+    vstep = run_verify_step(torch, device, rank, world, peaks, max_over_ranks, barrier)
 
     if world > 1:
         dist.barrier()
@@ -335,6 +339,7 @@ def run_gpu(args):
         "clocks": clocks,
         "sdpa": sd,
         "sdpa_long": sd_long,
+        "verify_step": vstep,
     }
     print(json.dumps(line))
     if world > 1:
@@ -431,6 +436,44 @@ def run_sdpa_long(torch, kernels, device, rank, world, peaks, max_over_ranks):
     return {"config": "configs[3]: B=8, Hq=16, Hkv=2, T=16, D=256, paged KV (256-token pages, random page table), "
                       f"16 (sequence, KV head) pairs over {world} GPU(s); K/V per call exceed L2; 4 calls per timed burst",
             "scaling": "strong", "results": out}
+
+
+def run_verify_step(torch, device, rank, world, peaks, max_over_ranks, barrier):
+    """configs[4]: hybrid stack of 36 gated-delta and 12 full-attention layers, 64 sequences in all (sharded by
+    sequence), T = 16, context 8192, KV in the TurboQuant 3-bit format, per-sequence acceptance, all-gather of the
+    acceptance results.  Composition of the library's kernels (swiftlm_b200/verify_step.py), not a fused step."""
+    from swiftlm_b200 import partition
+    from swiftlm_b200.verify_step import StepConfig, VerifyStep
+    total = 64
+    lo, hi = partition.plan(total, world)[rank]
+    cfg = StepConfig(batch=hi - lo)
+    step = VerifyStep(cfg, device)
+    for _ in range(2):
+        step.run(world, total)
+    barrier()
+    times, parts = [], []
+    for _ in range(3):
+        ev = {}
+        barrier()
+        step.run(world, total, events=ev)
+        torch.cuda.synchronize()
+        names = ["start", "layers", "acceptance", "rollback", "gather"]
+        t = [ev[n][0] for n in names]
+        times.append(t[0].elapsed_time(t[-1]))
+        parts.append([t[i].elapsed_time(t[i + 1]) for i in range(4)])
+    from swiftlm_b200 import kernels
+    kernels.device_status()
+    i = sorted(range(3), key=lambda j: times[j])[1]
+    ms = max_over_ranks(times[i])
+    accepted = float(step.run(world, total)["accept"].float().mean().item()) + 1.0
+    byts = step.bytes_per_step() * world
+    return {"config": f"configs[4]: 36 gated-delta + 12 attention layers, 64 sequences over {world} GPU(s), T=16, context 8192, "
+                      "TurboQuant 3-bit KV decoded per layer, vocabulary 151936, per-sequence acceptance",
+            "ms_per_step": ms, "steps_per_s": 1e3 / ms, "sequences": total,
+            "committed_tokens_per_step_per_sequence": accepted,
+            "ms_layers_acceptance_rollback_gather": parts[i],
+            "algorithmic_gb_per_step": byts / 1e9, "gbs": byts / (ms * 1e-3) / 1e9,
+            "frac_of_hbm_peak_per_gpu": byts / (ms * 1e-3) / 1e9 / (peaks["hbm_gbs"] * world), "scaling": "strong"}
 
 
 def run_case(args):

@@ -204,6 +204,16 @@ def accept_lengths(posterior: torch.Tensor, verify_ids: torch.Tensor):
     return acc, nxt, rep
 
 
+def turbo_decode_into(packed, signs, norm, rnorm, out: torch.Tensor) -> None:
+    """turbo_decode into a caller-owned tensor (any shape holding norm.numel() * 128 values)."""
+    _need_cuda(packed, norm, out)
+    n = norm.numel()
+    if out.numel() != n * 128 or not out.is_contiguous():
+        raise _lib.DFlashError(_lib.ERR_INVALID_ARG, "turbo_decode_into: out must be contiguous with 128 values per block")
+    _lib.check(_lib.lib().dflash_turbo_decode(_ptr(packed.contiguous()), _ptr(signs), _ptr(norm.contiguous()),
+                                             _ptr(rnorm), _ptr(out), n, int(signs is not None), _DT[out.dtype], _stream()))
+
+
 def device_status() -> None:
     """Raises if a kernel's bounded device-side wait gave up since the last check."""
     _lib.check(_lib.lib().dflash_device_status(_stream()))
