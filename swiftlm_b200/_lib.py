@@ -8,7 +8,8 @@ import ctypes as C
 import os
 
 _PKG = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_PKG, "lib", "libdflash_cuda.so")
+# DFLASH_CUDA_LIB points at a library built elsewhere (for instance an instrumented build)
+LIB_PATH = os.environ.get("DFLASH_CUDA_LIB") or os.path.join(_PKG, "lib", "libdflash_cuda.so")
 
 F32, BF16, F16, U8 = 0, 1, 2, 3
 KV_DENSE, KV_TURBO3 = 0, 1
