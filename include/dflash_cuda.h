@@ -38,6 +38,18 @@ typedef enum { DFLASH_F32 = 0, DFLASH_BF16 = 1, DFLASH_F16 = 2, DFLASH_U8 = 3 } 
 /* KV storage formats of dflash_verify_sdpa. */
 typedef enum { DFLASH_KV_DENSE = 0, DFLASH_KV_TURBO3 = 1 } dflash_kv_format;
 
+/* KV held in the TurboQuant 3-bit format (see dflash_turbo_encode below): device arrays over
+ * [B,Hkv,N, D/128 blocks].  With kv_format == DFLASH_KV_TURBO3 the `k` argument of
+ * dflash_verify_sdpa points at one of these (in host memory) and `v` is ignored. */
+typedef struct {
+  const uint8_t* k_packed;   /* [blocks,48] */
+  const uint8_t* k_signs;    /* [blocks,16] */
+  const uint16_t* k_norm;    /* [blocks] fp16 bits */
+  const uint16_t* k_rnorm;   /* [blocks] fp16 bits */
+  const uint8_t* v_packed;   /* [blocks,48] */
+  const uint16_t* v_norm;    /* [blocks] fp16 bits */
+} dflash_turbo_kv;
+
 /* ---------------------------------------------------------------------------------------------
  * Gated-delta forward that records the innovation tape; with n_per_seq it is the replay of a
  * recorded (q,k,v,beta,g) block from the last committed state to the accepted length.
@@ -101,6 +113,10 @@ int32_t dflash_verify_sdpa(const void* q, const void* k, const void* v, const in
                            void* stream);
 
 size_t dflash_verify_sdpa_workspace_bytes(int32_t B, int32_t Hq, int32_t Hkv, int32_t D, int32_t N);
+/* The same for a given kv_format: DFLASH_KV_TURBO3 adds room for K and V expanded to `dtype`
+ * (2 * B*Hkv*N*D elements of 2 bytes), which the call decodes into before attending (dense KV
+ * only, no page table).  The expanded KV makes a round trip through HBM: correct, not yet fused. */
+size_t dflash_verify_sdpa_workspace_bytes_ex(int32_t B, int32_t Hq, int32_t Hkv, int32_t D, int32_t N, int32_t kv_format);
 
 /* Same computation as dflash_verify_sdpa for a caller that cannot supply scratch memory (a host
  * whose device-memory budget is fixed and whose allocator is closed to plug-ins, or a request path

@@ -22,6 +22,7 @@ SIGNATURES = {
     "dflash_gated_delta_tape": (_i32, [_vp] * 11 + [_i32] * 9 + [_vp]),
     "dflash_tape_replay": (_i32, [_vp] * 7 + [_i32] * 9 + [_vp]),
     "dflash_verify_sdpa": (_i32, [_vp] * 8 + [_sz] + [_i32] * 8 + [_f32, _i32, _i32, _vp]),
+    "dflash_verify_sdpa_workspace_bytes_ex": (_sz, [_i32] * 6),
     "dflash_verify_sdpa_workspace_bytes": (_sz, [_i32] * 5),
     "dflash_verify_sdpa_noalloc": (_i32, [_vp] * 7 + [_i32] * 8 + [_f32, _i32, _i32, _vp]),
     "dflash_greedy_tokens": (_i32, [_vp, _vp, _vp, _i32, _i32, _i32, _vp]),
@@ -36,6 +37,12 @@ SIGNATURES = {
     "dflash_launch_count": (_u64, []),
     "dflash_version": (C.c_char_p, []),
 }
+
+
+class TurboKV(C.Structure):
+    """dflash_turbo_kv of include/dflash_cuda.h."""
+    _fields_ = [("k_packed", C.c_void_p), ("k_signs", C.c_void_p), ("k_norm", C.c_void_p), ("k_rnorm", C.c_void_p),
+                ("v_packed", C.c_void_p), ("v_norm", C.c_void_p)]
 
 
 class DFlashError(RuntimeError):

@@ -147,7 +147,7 @@ int32_t dflash_verify_sdpa(const void* q, const void* k, const void* v, const in
                            size_t workspace_bytes, int32_t B, int32_t Hq, int32_t Hkv, int32_t T,
                            int32_t D, int32_t N, int32_t page_tokens, int32_t max_pages, float scale,
                            int32_t dtype, int32_t kv_format, void* stream) {
-  if (!q || !k || !v || !out) return bad("null tensor pointer");
+  if (!q || !k || (!v && kv_format == DFLASH_KV_DENSE) || !out) return bad("null tensor pointer");
   if (B <= 0 || Hq <= 0 || Hkv <= 0 || N <= 0) return bad("non-positive dimension");
   // eligibility of the reference's kernel, Sources/DFlash/DFlashKernels.swift:755-758
   if (T != 16) { set_error("unsupported query length %d (the verify block has 16 rows)", T); return DFLASH_ERR_UNSUPPORTED; }
@@ -155,7 +155,27 @@ int32_t dflash_verify_sdpa(const void* q, const void* k, const void* v, const in
   if (D != 128 && D != 256) { set_error("unsupported head_dim %d (128 or 256)", D); return DFLASH_ERR_UNSUPPORTED; }
   if (Hq % Hkv != 0) { set_error("unsupported heads: Hq=%d not a multiple of Hkv=%d", Hq, Hkv); return DFLASH_ERR_UNSUPPORTED; }
   if (N < 16) { set_error("unsupported N=%d: the 16 block keys are part of the KV", N); return DFLASH_ERR_UNSUPPORTED; }
-  if (kv_format != DFLASH_KV_DENSE) { set_error("unsupported kv_format %d in dflash_verify_sdpa", kv_format); return DFLASH_ERR_UNSUPPORTED; }
+  if (kv_format != DFLASH_KV_DENSE && kv_format != DFLASH_KV_TURBO3) { set_error("unsupported kv_format %d in dflash_verify_sdpa", kv_format); return DFLASH_ERR_UNSUPPORTED; }
+  if (kv_format == DFLASH_KV_TURBO3) {
+    // expand K and V into the front of the workspace, then attend over the expanded copy
+    if (page_table) { set_error("TurboQuant KV behind a page table is not supported"); return DFLASH_ERR_UNSUPPORTED; }
+    const dflash_turbo_kv* t = reinterpret_cast<const dflash_turbo_kv*>(k);
+    if (!t->k_packed || !t->k_signs || !t->k_norm || !t->k_rnorm || !t->v_packed || !t->v_norm) return bad("null TurboQuant array");
+    const size_t kv_elems = (size_t)B * Hkv * N * D, kv_bytes = (kv_elems * 2 + 255) / 256 * 256;
+    const size_t need = 2 * kv_bytes + sdpa_workspace_bytes(B, Hq, Hkv, D, N);
+    if (!workspace || workspace_bytes < need) {
+      set_error("verify_sdpa (TurboQuant KV): workspace of %zu bytes needed, %zu given", need, workspace_bytes);
+      return DFLASH_ERR_WORKSPACE;
+    }
+    if (!aligned16(workspace)) return bad("tensor base pointers must be 16-byte aligned");
+    uint8_t* ws = reinterpret_cast<uint8_t*>(workspace);
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+    const long long blocks = (long long)(kv_elems / 128);
+    if (int32_t st = launch_turbo_decode(t->k_packed, t->k_signs, t->k_norm, t->k_rnorm, ws, blocks, 1, dtype, s)) return st;
+    if (int32_t st = launch_turbo_decode(t->v_packed, nullptr, t->v_norm, nullptr, ws + kv_bytes, blocks, 0, dtype, s)) return st;
+    return dflash_verify_sdpa(q, ws, ws + kv_bytes, nullptr, kv_len_per_seq, mask, out, ws + 2 * kv_bytes, workspace_bytes - 2 * kv_bytes,
+                              B, Hq, Hkv, T, D, N, 0, 0, scale, dtype, DFLASH_KV_DENSE, stream);
+  }
   if (page_table && (page_tokens <= 0 || page_tokens % 128 != 0 || max_pages <= 0 ||
                      (long long)max_pages * page_tokens < N))
     return bad("paged KV needs page_tokens % 128 == 0 and max_pages * page_tokens >= N");
@@ -171,6 +191,13 @@ int32_t dflash_verify_sdpa(const void* q, const void* k, const void* v, const in
 size_t dflash_verify_sdpa_workspace_bytes(int32_t B, int32_t Hq, int32_t Hkv, int32_t D, int32_t N) {
   if (B <= 0 || Hq <= 0 || Hkv <= 0 || D <= 0 || N <= 0) return 0;
   return sdpa_workspace_bytes(B, Hq, Hkv, D, N);
+}
+
+size_t dflash_verify_sdpa_workspace_bytes_ex(int32_t B, int32_t Hq, int32_t Hkv, int32_t D, int32_t N, int32_t kv_format) {
+  const size_t base = dflash_verify_sdpa_workspace_bytes(B, Hq, Hkv, D, N);
+  if (!base || kv_format != DFLASH_KV_TURBO3) return base;
+  const size_t kv_bytes = ((size_t)B * Hkv * N * D * 2 + 255) / 256 * 256;
+  return base + 2 * kv_bytes;
 }
 
 int32_t dflash_greedy_tokens(const void* logits, const uint8_t* suppress, uint32_t* posterior,

@@ -236,6 +236,33 @@ def gated_delta_into(q, k, v, g, beta, state, n_per_seq, y, state_out, tape=None
         _stream()))
 
 
+def batched_sdpa_turbo_kv(queries, k_enc, v_enc, n_keys: int, scale: float, out=None) -> Optional[torch.Tensor]:
+    """Block-verify attention over KV held in the TurboQuant 3-bit format: k_enc = (packed, signs, norm, rnorm)
+    and v_enc = (packed, norm) as returned by turbo_encode for tensors [B,Hkv,N,D].  The library expands K and V
+    into its workspace and attends over the copy (dflash_verify_sdpa with DFLASH_KV_TURBO3)."""
+    _need_cuda(queries, k_enc[0], v_enc[0])
+    B, Hq, T, D = queries.shape
+    dt = queries.dtype
+    Hkv = k_enc[2].shape[1]
+    if T != 16 or dt not in (torch.bfloat16, torch.float16) or D not in (128, 256) or Hq % Hkv != 0:
+        return None
+    q = queries.contiguous()
+    if out is None:
+        out = torch.empty_like(q)
+    L = _lib.lib()
+    ws = _workspace(q.device, L.dflash_verify_sdpa_workspace_bytes_ex(B, Hq, Hkv, D, n_keys, _lib.KV_TURBO3))
+    kp, ks, kn, kr = (t.contiguous() for t in k_enc)
+    vp, vn = (t.contiguous() for t in v_enc)
+    desc = _lib.TurboKV(_ptr(kp), _ptr(ks), _ptr(kn), _ptr(kr), _ptr(vp), _ptr(vn))
+    try:
+        _lib.check(L.dflash_verify_sdpa(_ptr(q), C.cast(C.pointer(desc), C.c_void_p), None, None, None, None, _ptr(out),
+                                        _ptr(ws), ws.numel(), B, Hq, Hkv, T, D, n_keys, 0, 0, float(scale), _DT[dt],
+                                        _lib.KV_TURBO3, _stream()))
+    except _lib.DFlashUnsupported:
+        return None
+    return out
+
+
 def rebuild_conv_state(conv_snapshot: Optional[torch.Tensor], qkv: torch.Tensor, steps, keep: int) -> torch.Tensor:
     """RecurrentRollbackCache.rebuildConvState (Sources/DFlash/RecurrentRollbackCache.swift:139-158) on the device:
     concat(conv_snapshot [B,keep,C], qkv [B,T,C])[:, steps : min(steps + keep, keep + T)].  `steps` is an int

@@ -5,8 +5,8 @@ greedy posterior :118-128, acceptance :133-142, commit arithmetic :523-547, cach
 Sources/DFlash/RecurrentRollbackCache.swift:95-131 for the per-layer rollback).
 
 Layer weights are omitted: the per-layer q/k/v/beta/g of the gated-delta layers, the queries of the
-attention layers, the KV cache (held in the TurboQuant 3-bit format and expanded per layer into a
-reused bf16 scratch pair) and the logits are seeded synthetic tensors.  What runs per step:
+attention layers, the KV cache (held in the TurboQuant 3-bit format and expanded per layer inside the
+library's workspace) and the logits are seeded synthetic tensors.  What runs per step:
   * every gated-delta layer: forward over the whole block with tape (the verify pass);
   * every attention layer: TurboQuant decode of K and V, then block-verify attention;
   * greedy posterior tokens over the vocabulary, accepted length, next token, replay length;
@@ -81,8 +81,6 @@ class VerifyStep:
         wrong = torch.arange(T - 1, device=device).view(1, -1) >= agree.view(-1, 1)
         ids[:, 1:][wrong] = (ids[:, 1:][wrong] + 1) % c.vocab
         self.verify_ids = ids.to(torch.int32)
-        self.k_scratch = torch.empty(B, c.Hkv, N, c.D, dtype=bf, device=device)
-        self.v_scratch = torch.empty_like(self.k_scratch)
         self.attn_out = [torch.empty_like(a["q"]) for a in self.attn]
         self.scale = 1.0 / float(c.D) ** 0.5
 
@@ -121,9 +119,8 @@ class VerifyStep:
 
     def _attention(self, i: int) -> None:
         a = self.attn[i]
-        kernels.turbo_decode_into(a["kp"], a["ks"], a["kn"], a["kr"], self.k_scratch)
-        kernels.turbo_decode_into(a["vp"], None, a["vn"], None, self.v_scratch)
-        kernels.batched_sdpa_2pass(a["q"], self.k_scratch, self.v_scratch, self.scale, out=self.attn_out[i])
+        kernels.batched_sdpa_turbo_kv(a["q"], (a["kp"], a["ks"], a["kn"], a["kr"]), (a["vp"], a["vn"]), self.N, self.scale,
+                                      out=self.attn_out[i])
 
     def bytes_per_step(self) -> float:
         """Algorithmic HBM bytes of one step (what a fused implementation would have to move at least)."""

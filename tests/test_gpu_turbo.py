@@ -81,3 +81,22 @@ def test_attention_over_turbo_compressed_kv():
     v_ref = O.round_bf16(CO.turbo_decode_v(p, n)).reshape(x["v"].shape)
     want = CO.verify_sdpa(x["q"], k_ref, v_ref, float(x["scale"]))
     assert np.abs(out.float().cpu().numpy() - want).max() < 2e-2
+
+
+def test_turbo_kv_format_of_the_attention_entry_point():
+    """dflash_verify_sdpa with DFLASH_KV_TURBO3 expands K and V inside the library: same bits as decoding first."""
+    from oracle import dflash_oracle as O
+    B, Hq, Hkv, N, D = 2, 16, 2, 16 + 900, 256
+    x = O.make_sdpa_inputs(B, Hq, Hkv, N, D, 4343, "bf16")
+    k = torch.from_numpy(x["k"]).cuda().bfloat16()
+    v = torch.from_numpy(x["v"]).cuda().bfloat16()
+    q = torch.from_numpy(x["q"]).cuda().bfloat16()
+    k_enc = K().turbo_encode(k, True)
+    vp, _, vn, _ = K().turbo_encode(v, False)
+    fused = K().batched_sdpa_turbo_kv(q, k_enc, (vp, vn), N, float(x["scale"]))
+    k_hat = K().turbo_decode(*k_enc, dtype=torch.bfloat16)
+    v_hat = K().turbo_decode(vp, None, vn, None, dtype=torch.bfloat16)
+    two_step = K().batched_sdpa_2pass(q, k_hat, v_hat, float(x["scale"]))
+    torch.cuda.synchronize()
+    K().device_status()
+    assert fused is not None and torch.equal(fused, two_step)
