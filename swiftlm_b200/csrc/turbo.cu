@@ -184,8 +184,8 @@ turbo_decode_kernel(const uint8_t* __restrict__ packed, const uint8_t* __restric
   float* c3 = sh;                                    // one copy of the 8 centroids per thread column: no bank conflicts
   for (int i = threadIdx.x; i < 8 * kDecThreads; i += kDecThreads) c3[i] = TURBO_C3[i / kDecThreads];
   __syncthreads();
-  const long long v = (long long)blockIdx.x * kDecThreads + threadIdx.x;
-  if (v >= n) return;
+  long long v = (long long)blockIdx.x * kDecThreads + threadIdx.x;
+  if (v >= n) v = n - 1;                               // the tail threads redo the last block; their copy is not written out
   float* stash = sh + 8 * kDecThreads + threadIdx.x;   // element i at stash[i * kDecThreads]
   float x[kBlock];
   if (IS_KEY) {
@@ -213,7 +213,10 @@ turbo_decode_kernel(const uint8_t* __restrict__ packed, const uint8_t* __restric
   }
   rot_regs(x, TURBO_S2_NEG, TURBO_S1_NEG);
   const float sc = from_f16_bits(norm[v]);
-  OutT* dst = out + v * kBlock;
+  // Outputs leave through a staging area so that a warp writes whole lines: thread t parks its block at
+  // t * (block bytes + 16) (the pad keeps the 16-byte pieces of neighbouring threads on different banks).
+  constexpr int kRowBytes = kBlock * (int)sizeof(OutT) + 16;
+  uint8_t* stage = reinterpret_cast<uint8_t*>(sh + (8 + (IS_KEY ? kBlock : 0)) * kDecThreads);
 #pragma unroll
   for (int g8 = 0; g8 < kBlock / 8; ++g8) {
     float o[8];
@@ -222,7 +225,16 @@ turbo_decode_kernel(const uint8_t* __restrict__ packed, const uint8_t* __restric
       const int i = g8 * 8 + e;
       o[e] = IS_KEY ? __fmul_rn(__fadd_rn(x[i], stash[i * kDecThreads]), sc) : __fmul_rn(x[i], sc);
     }
-    store8_out<OutT>(dst + g8 * 8, o);
+    store8_out<OutT>(reinterpret_cast<OutT*>(stage + threadIdx.x * kRowBytes) + g8 * 8, o);
+  }
+  __syncthreads();
+  constexpr int kPieces = kBlock * (int)sizeof(OutT) / 16;            // 16-byte pieces per block
+  const long long first = (long long)blockIdx.x * kDecThreads;        // first block of this CTA
+  const long long here = n - first < kDecThreads ? n - first : kDecThreads;
+  uint8_t* gbase = reinterpret_cast<uint8_t*>(out + first * kBlock);
+  for (int p = threadIdx.x; p < (int)here * kPieces; p += kDecThreads) {
+    const int t = p / kPieces, off = p % kPieces;
+    *reinterpret_cast<uint4*>(gbase + (long long)p * 16) = *reinterpret_cast<const uint4*>(stage + t * kRowBytes + off * 16);
   }
 }
 
@@ -230,7 +242,8 @@ template <typename OutT>
 int32_t launch_decode_typed(const uint8_t* packed, const uint8_t* signs, const uint16_t* norm, const uint16_t* rnorm, void* out,
                             long long n, int is_key, cudaStream_t stream) {
   const unsigned grid = (unsigned)((n + kDecThreads - 1) / kDecThreads);
-  const size_t smem = (8 + (is_key ? kBlock : 0)) * kDecThreads * sizeof(float);
+  const size_t smem = (8 + (is_key ? kBlock : 0)) * kDecThreads * sizeof(float) + kDecThreads * (kBlock * sizeof(OutT) + 16);
+  DFLASH_CUDA_CHECK(cudaFuncSetAttribute(turbo_decode_kernel<OutT, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   if (is_key) {
     DFLASH_CUDA_CHECK(cudaFuncSetAttribute(turbo_decode_kernel<OutT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     turbo_decode_kernel<OutT, true><<<grid, kDecThreads, smem, stream>>>(packed, signs, norm, rnorm, (OutT*)out, n);
