@@ -196,3 +196,33 @@ def test_full_size_properties_replay_config():
     idle = (n == 0)
     if idle.any():
         assert torch.equal(s1[idle], s0[idle])
+
+
+@pytest.mark.parametrize("variant", ["large_state", "correlated_keys", "tiny_gates", "ones"])
+def test_tensor_core_path_under_stress(variant):
+    """The bf16 / 128 x 128 / scalar-gate path (three tensor-core products plus a triangular recurrence) on inputs
+    that stress its two-term split of the state and the recurrence: O(1) states, nearly parallel keys, gates down to
+    1e-3 (and exactly 0 and 1), betas of exactly 1."""
+    rng = np.random.default_rng(77)
+    x = O.make_gdn_inputs(4, 16, 2, 4, 128, 128, 950, False, "bf16")
+    if variant == "large_state":
+        x["state"] = rng.standard_normal(x["state"].shape).astype(np.float32)
+    elif variant == "correlated_keys":
+        base = rng.standard_normal((4, 1, 2, 128)).astype(np.float32)
+        k = base + 0.15 * rng.standard_normal((4, 16, 2, 128)).astype(np.float32)
+        x["k"] = O.round_bf16(k / np.linalg.norm(k, axis=-1, keepdims=True))
+        x["beta"] = O.round_bf16(np.full_like(x["beta"], 0.98))
+    elif variant == "tiny_gates":
+        g = 10.0 ** rng.uniform(-3, 0, x["g"].shape)
+        g[0, 3] = 0.0
+        g[1, 5] = 1.0
+        x["g"] = O.round_bf16(g.astype(np.float32))
+    else:
+        x["beta"] = np.ones_like(x["beta"])
+        x["g"] = np.ones_like(x["g"])
+    x["n"] = np.array([16, 9, 16, 3], np.int32)
+    y, s, tape = run_fwd(x, "bf16")
+    yo, so, to = CO.gated_delta(x["q"], x["k"], x["v"], x["g"], x["beta"], x["state"], n=x["n"])
+    assert rel(s, so) < STATE_RTOL
+    assert rel(tape, to) < 1e-4
+    assert rel(y, yo) < y_tol("bf16")
