@@ -38,8 +38,12 @@ typedef enum { DFLASH_F32 = 0, DFLASH_BF16 = 1, DFLASH_F16 = 2, DFLASH_U8 = 3 } 
 /* KV storage formats of dflash_verify_sdpa. */
 typedef enum { DFLASH_KV_DENSE = 0, DFLASH_KV_TURBO3 = 1 } dflash_kv_format;
 
-/* KV held in the TurboQuant 3-bit format (see dflash_turbo_encode below): device arrays over
- * [B,Hkv,N, D/128 blocks].  With kv_format == DFLASH_KV_TURBO3 the `k` argument of
+/* KV held in the TurboQuant 3-bit format (see dflash_turbo_encode below) with the reference's hot
+ * window (docs/turboquant_hybrid_architecture.md:49-53 of the SwiftLM tree): the oldest n_cold
+ * tokens of every (sequence, KV head) are compressed, the newest n_hot tokens (the verify block
+ * among them) stay in the attention dtype; attention sees [decoded cold | hot], N = n_cold + n_hot.
+ * Compressed arrays are device arrays over [B,Hkv,n_cold, D/128 blocks]; hot arrays are
+ * [B,Hkv,n_hot,D] (NULL when n_hot == 0).  With kv_format == DFLASH_KV_TURBO3 the `k` argument of
  * dflash_verify_sdpa points at one of these (in host memory) and `v` is ignored. */
 typedef struct {
   const uint8_t* k_packed;   /* [blocks,48] */
@@ -48,6 +52,10 @@ typedef struct {
   const uint16_t* k_rnorm;   /* [blocks] fp16 bits */
   const uint8_t* v_packed;   /* [blocks,48] */
   const uint16_t* v_norm;    /* [blocks] fp16 bits */
+  const void* k_hot;         /* [B,Hkv,n_hot,D] or NULL */
+  const void* v_hot;
+  int32_t n_cold;
+  int32_t n_hot;
 } dflash_turbo_kv;
 
 /* ---------------------------------------------------------------------------------------------

@@ -42,7 +42,8 @@ SIGNATURES = {
 class TurboKV(C.Structure):
     """dflash_turbo_kv of include/dflash_cuda.h."""
     _fields_ = [("k_packed", C.c_void_p), ("k_signs", C.c_void_p), ("k_norm", C.c_void_p), ("k_rnorm", C.c_void_p),
-                ("v_packed", C.c_void_p), ("v_norm", C.c_void_p)]
+                ("v_packed", C.c_void_p), ("v_norm", C.c_void_p), ("k_hot", C.c_void_p), ("v_hot", C.c_void_p),
+                ("n_cold", C.c_int32), ("n_hot", C.c_int32)]
 
 
 class DFlashError(RuntimeError):

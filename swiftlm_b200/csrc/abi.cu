@@ -160,7 +160,9 @@ int32_t dflash_verify_sdpa(const void* q, const void* k, const void* v, const in
     // expand K and V into the front of the workspace, then attend over the expanded copy
     if (page_table) { set_error("TurboQuant KV behind a page table is not supported"); return DFLASH_ERR_UNSUPPORTED; }
     const dflash_turbo_kv* t = reinterpret_cast<const dflash_turbo_kv*>(k);
-    if (!t->k_packed || !t->k_signs || !t->k_norm || !t->k_rnorm || !t->v_packed || !t->v_norm) return bad("null TurboQuant array");
+    if (t->n_cold < 0 || t->n_hot < 0 || t->n_cold + t->n_hot != N) return bad("TurboQuant KV: n_cold + n_hot must equal N");
+    if (t->n_cold > 0 && (!t->k_packed || !t->k_signs || !t->k_norm || !t->k_rnorm || !t->v_packed || !t->v_norm)) return bad("null TurboQuant array");
+    if (t->n_hot > 0 && (!t->k_hot || !t->v_hot || !aligned16(t->k_hot) || !aligned16(t->v_hot))) return bad("TurboQuant KV: hot window arrays missing or misaligned");
     const size_t kv_elems = (size_t)B * Hkv * N * D, kv_bytes = (kv_elems * 2 + 255) / 256 * 256;
     const size_t need = 2 * kv_bytes + sdpa_workspace_bytes(B, Hq, Hkv, D, N);
     if (!workspace || workspace_bytes < need) {
@@ -170,9 +172,18 @@ int32_t dflash_verify_sdpa(const void* q, const void* k, const void* v, const in
     if (!aligned16(workspace)) return bad("tensor base pointers must be 16-byte aligned");
     uint8_t* ws = reinterpret_cast<uint8_t*>(workspace);
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-    const long long blocks = (long long)(kv_elems / 128);
-    if (int32_t st = launch_turbo_decode(t->k_packed, t->k_signs, t->k_norm, t->k_rnorm, ws, blocks, 1, dtype, s)) return st;
-    if (int32_t st = launch_turbo_decode(t->v_packed, nullptr, t->v_norm, nullptr, ws + kv_bytes, blocks, 0, dtype, s)) return st;
+    const long long pairs = (long long)B * Hkv, blocks_per_pair = (long long)t->n_cold * (D / 128);
+    if (t->n_cold > 0) {   // cold history: every pair's run of blocks goes to the front of its N x D slab
+      if (int32_t st = launch_turbo_decode(t->k_packed, t->k_signs, t->k_norm, t->k_rnorm, ws, pairs * blocks_per_pair, 1, dtype, s,
+                                           blocks_per_pair, (long long)N * D)) return st;
+      if (int32_t st = launch_turbo_decode(t->v_packed, nullptr, t->v_norm, nullptr, ws + kv_bytes, pairs * blocks_per_pair, 0, dtype, s,
+                                           blocks_per_pair, (long long)N * D)) return st;
+    }
+    if (t->n_hot > 0) {    // hot window: copied behind the cold history
+      const size_t row = (size_t)t->n_hot * D * 2, pitch = (size_t)N * D * 2, off = (size_t)t->n_cold * D * 2;
+      DFLASH_CUDA_CHECK(cudaMemcpy2DAsync(ws + off, pitch, t->k_hot, row, row, (size_t)pairs, cudaMemcpyDeviceToDevice, s));
+      DFLASH_CUDA_CHECK(cudaMemcpy2DAsync(ws + kv_bytes + off, pitch, t->v_hot, row, row, (size_t)pairs, cudaMemcpyDeviceToDevice, s));
+    }
     return dflash_verify_sdpa(q, ws, ws + kv_bytes, nullptr, kv_len_per_seq, mask, out, ws + 2 * kv_bytes, workspace_bytes - 2 * kv_bytes,
                               B, Hq, Hkv, T, D, N, 0, 0, scale, dtype, DFLASH_KV_DENSE, stream);
   }

@@ -124,7 +124,9 @@ int32_t launch_accept_lengths(const uint32_t* posterior, const int32_t* verify_i
 
 int32_t launch_turbo_encode(const void* x, uint8_t* packed, uint8_t* signs, uint16_t* norm, uint16_t* rnorm,
                             long long n, int is_key, int in_dtype, cudaStream_t stream);
+// group_blocks > 0: output block v goes to out + (v / group_blocks) * group_stride + (v % group_blocks) * 128 elements
 int32_t launch_turbo_decode(const uint8_t* packed, const uint8_t* signs, const uint16_t* norm, const uint16_t* rnorm,
-                            void* out, long long n, int is_key, int out_dtype, cudaStream_t stream);
+                            void* out, long long n, int is_key, int out_dtype, cudaStream_t stream,
+                            long long group_blocks = 0, long long group_stride = 0);
 
 }  // namespace dflash

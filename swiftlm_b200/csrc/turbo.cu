@@ -179,7 +179,8 @@ template <typename OutT, bool IS_KEY>
 __global__ void __launch_bounds__(kDecThreads)
 turbo_decode_kernel(const uint8_t* __restrict__ packed, const uint8_t* __restrict__ signs,
                     const uint16_t* __restrict__ norm, const uint16_t* __restrict__ rnorm, OutT* __restrict__ out,
-                    long long n) {
+                    long long n, long long group_blocks, long long group_stride) {
+  // output block v lands at out + (v / group_blocks) * group_stride + (v % group_blocks) * 128 elements
   extern __shared__ float sh[];                      // [8][kDecThreads] centroid table, then (keys) [128][kDecThreads]
   float* c3 = sh;                                    // one copy of the 8 centroids per thread column: no bank conflicts
   for (int i = threadIdx.x; i < 8 * kDecThreads; i += kDecThreads) c3[i] = TURBO_C3[i / kDecThreads];
@@ -231,24 +232,25 @@ turbo_decode_kernel(const uint8_t* __restrict__ packed, const uint8_t* __restric
   constexpr int kPieces = kBlock * (int)sizeof(OutT) / 16;            // 16-byte pieces per block
   const long long first = (long long)blockIdx.x * kDecThreads;        // first block of this CTA
   const long long here = n - first < kDecThreads ? n - first : kDecThreads;
-  uint8_t* gbase = reinterpret_cast<uint8_t*>(out + first * kBlock);
   for (int p = threadIdx.x; p < (int)here * kPieces; p += kDecThreads) {
     const int t = p / kPieces, off = p % kPieces;
-    *reinterpret_cast<uint4*>(gbase + (long long)p * 16) = *reinterpret_cast<const uint4*>(stage + t * kRowBytes + off * 16);
+    const long long blk = first + t;
+    uint8_t* g = reinterpret_cast<uint8_t*>(out + (blk / group_blocks) * group_stride + (blk % group_blocks) * kBlock);
+    *reinterpret_cast<uint4*>(g + off * 16) = *reinterpret_cast<const uint4*>(stage + t * kRowBytes + off * 16);
   }
 }
 
 template <typename OutT>
 int32_t launch_decode_typed(const uint8_t* packed, const uint8_t* signs, const uint16_t* norm, const uint16_t* rnorm, void* out,
-                            long long n, int is_key, cudaStream_t stream) {
+                            long long n, int is_key, long long group_blocks, long long group_stride, cudaStream_t stream) {
   const unsigned grid = (unsigned)((n + kDecThreads - 1) / kDecThreads);
   const size_t smem = (8 + (is_key ? kBlock : 0)) * kDecThreads * sizeof(float) + kDecThreads * (kBlock * sizeof(OutT) + 16);
   DFLASH_CUDA_CHECK(cudaFuncSetAttribute(turbo_decode_kernel<OutT, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   if (is_key) {
     DFLASH_CUDA_CHECK(cudaFuncSetAttribute(turbo_decode_kernel<OutT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    turbo_decode_kernel<OutT, true><<<grid, kDecThreads, smem, stream>>>(packed, signs, norm, rnorm, (OutT*)out, n);
+    turbo_decode_kernel<OutT, true><<<grid, kDecThreads, smem, stream>>>(packed, signs, norm, rnorm, (OutT*)out, n, group_blocks, group_stride);
   } else {
-    turbo_decode_kernel<OutT, false><<<grid, kDecThreads, smem, stream>>>(packed, signs, norm, rnorm, (OutT*)out, n);
+    turbo_decode_kernel<OutT, false><<<grid, kDecThreads, smem, stream>>>(packed, signs, norm, rnorm, (OutT*)out, n, group_blocks, group_stride);
   }
   return DFLASH_OK;
 }
@@ -282,16 +284,18 @@ int32_t launch_turbo_encode(const void* x, uint8_t* packed, uint8_t* signs, uint
 }
 
 int32_t launch_turbo_decode(const uint8_t* packed, const uint8_t* signs, const uint16_t* norm, const uint16_t* rnorm,
-                            void* out, long long n, int is_key, int out_dtype, cudaStream_t stream) {
+                            void* out, long long n, int is_key, int out_dtype, cudaStream_t stream,
+                            long long group_blocks, long long group_stride) {
+  if (group_blocks <= 0) { group_blocks = n; group_stride = n * kBlock; }   // one dense run
   if (((uintptr_t)packed & 15) || (is_key && ((uintptr_t)signs & 15)) || ((uintptr_t)out & 15)) {
     set_error("turbo_decode: packed, signs and out must be 16-byte aligned");
     return DFLASH_ERR_INVALID_ARG;
   }
   int32_t st;
   switch (out_dtype) {
-    case DFLASH_F32: st = launch_decode_typed<float>(packed, signs, norm, rnorm, out, n, is_key, stream); break;
-    case DFLASH_BF16: st = launch_decode_typed<__nv_bfloat16>(packed, signs, norm, rnorm, out, n, is_key, stream); break;
-    case DFLASH_F16: st = launch_decode_typed<__half>(packed, signs, norm, rnorm, out, n, is_key, stream); break;
+    case DFLASH_F32: st = launch_decode_typed<float>(packed, signs, norm, rnorm, out, n, is_key, group_blocks, group_stride, stream); break;
+    case DFLASH_BF16: st = launch_decode_typed<__nv_bfloat16>(packed, signs, norm, rnorm, out, n, is_key, group_blocks, group_stride, stream); break;
+    case DFLASH_F16: st = launch_decode_typed<__half>(packed, signs, norm, rnorm, out, n, is_key, group_blocks, group_stride, stream); break;
     default:
       set_error("turbo_decode: unsupported dtype %d", out_dtype);
       return DFLASH_ERR_UNSUPPORTED;

@@ -236,10 +236,12 @@ def gated_delta_into(q, k, v, g, beta, state, n_per_seq, y, state_out, tape=None
         _stream()))
 
 
-def batched_sdpa_turbo_kv(queries, k_enc, v_enc, n_keys: int, scale: float, out=None) -> Optional[torch.Tensor]:
-    """Block-verify attention over KV held in the TurboQuant 3-bit format: k_enc = (packed, signs, norm, rnorm)
-    and v_enc = (packed, norm) as returned by turbo_encode for tensors [B,Hkv,N,D].  The library expands K and V
-    into its workspace and attends over the copy (dflash_verify_sdpa with DFLASH_KV_TURBO3)."""
+def batched_sdpa_turbo_kv(queries, k_enc, v_enc, n_cold: int, scale: float, k_hot=None, v_hot=None, out=None) -> Optional[torch.Tensor]:
+    """Block-verify attention over KV held in the TurboQuant 3-bit format with a hot window: k_enc = (packed, signs,
+    norm, rnorm) and v_enc = (packed, norm) as returned by turbo_encode for the cold history [B,Hkv,n_cold,D]; k_hot,
+    v_hot [B,Hkv,n_hot,D] in the attention dtype are the newest tokens (the verify block among them).  The library
+    expands the cold history into its workspace, appends the hot window and attends over the copy (dflash_verify_sdpa
+    with DFLASH_KV_TURBO3)."""
     _need_cuda(queries, k_enc[0], v_enc[0])
     B, Hq, T, D = queries.shape
     dt = queries.dtype
@@ -249,11 +251,15 @@ def batched_sdpa_turbo_kv(queries, k_enc, v_enc, n_keys: int, scale: float, out=
     q = queries.contiguous()
     if out is None:
         out = torch.empty_like(q)
+    n_hot = 0 if k_hot is None else k_hot.shape[2]
+    n_keys = n_cold + n_hot
     L = _lib.lib()
     ws = _workspace(q.device, L.dflash_verify_sdpa_workspace_bytes_ex(B, Hq, Hkv, D, n_keys, _lib.KV_TURBO3))
     kp, ks, kn, kr = (t.contiguous() for t in k_enc)
     vp, vn = (t.contiguous() for t in v_enc)
-    desc = _lib.TurboKV(_ptr(kp), _ptr(ks), _ptr(kn), _ptr(kr), _ptr(vp), _ptr(vn))
+    kh = None if k_hot is None else k_hot.to(dt).contiguous()
+    vh = None if v_hot is None else v_hot.to(dt).contiguous()
+    desc = _lib.TurboKV(_ptr(kp), _ptr(ks), _ptr(kn), _ptr(kr), _ptr(vp), _ptr(vn), _ptr(kh), _ptr(vh), n_cold, n_hot)
     try:
         _lib.check(L.dflash_verify_sdpa(_ptr(q), C.cast(C.pointer(desc), C.c_void_p), None, None, None, None, _ptr(out),
                                         _ptr(ws), ws.numel(), B, Hq, Hkv, T, D, n_keys, 0, 0, float(scale), _DT[dt],

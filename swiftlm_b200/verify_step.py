@@ -68,10 +68,12 @@ class VerifyStep:
         for _ in range(c.attn_layers):
             k = rn(B, c.Hkv, N, c.D).to(bf)
             v = rn(B, c.Hkv, N, c.D).to(bf)
-            kp, ks, kn, kr = kernels.turbo_encode(k, True)
-            vp, _, vn, _ = kernels.turbo_encode(v, False)
+            # the committed context is compressed; the block's own T tokens stay dense (the hot window)
+            kp, ks, kn, kr = kernels.turbo_encode(k[:, :, :c.context].contiguous(), True)
+            vp, _, vn, _ = kernels.turbo_encode(v[:, :, :c.context].contiguous(), False)
+            self.attn.append(dict(q=rn(B, c.Hq, T, c.D).to(bf), kp=kp, ks=ks, kn=kn, kr=kr, vp=vp, vn=vn,
+                                  k_hot=k[:, :, c.context:].contiguous(), v_hot=v[:, :, c.context:].contiguous()))
             del k, v
-            self.attn.append(dict(q=rn(B, c.Hq, T, c.D).to(bf), kp=kp, ks=ks, kn=kn, kr=kr, vp=vp, vn=vn))
         self.logits = rn(B, T, c.vocab).to(bf)
         # draft ids: the staged token, then drafted tokens that agree with the posterior for a random prefix
         post = kernels.greedy_tokens_with_mask(self.logits).to(torch.int64)
@@ -119,16 +121,16 @@ class VerifyStep:
 
     def _attention(self, i: int) -> None:
         a = self.attn[i]
-        kernels.batched_sdpa_turbo_kv(a["q"], (a["kp"], a["ks"], a["kn"], a["kr"]), (a["vp"], a["vn"]), self.N, self.scale,
-                                      out=self.attn_out[i])
+        kernels.batched_sdpa_turbo_kv(a["q"], (a["kp"], a["ks"], a["kn"], a["kr"]), (a["vp"], a["vn"]), self.cfg.context,
+                                      self.scale, k_hot=a["k_hot"], v_hot=a["v_hot"], out=self.attn_out[i])
 
     def bytes_per_step(self) -> float:
         """Algorithmic HBM bytes of one step (what a fused implementation would have to move at least)."""
         c = self.cfg
         heads = c.batch * c.Hv
         gdn = c.gdn_layers * (heads * (131072 + 772 * c.T) + heads * (131072 + 642 * 8))          # verify + mean rollback
-        blocks = c.batch * c.Hkv * self.N * (c.D // 128)
-        attn = c.attn_layers * blocks * (48 + 16 + 4 + 48 + 2)
+        blocks = c.batch * c.Hkv * c.context * (c.D // 128)
+        attn = c.attn_layers * (blocks * (48 + 16 + 4 + 48 + 2) + 2 * c.batch * c.Hkv * c.T * c.D * 2)
         return float(gdn + attn + self.logits.numel() * 2)
 
 

@@ -83,20 +83,38 @@ def test_attention_over_turbo_compressed_kv():
     assert np.abs(out.float().cpu().numpy() - want).max() < 2e-2
 
 
-def test_turbo_kv_format_of_the_attention_entry_point():
-    """dflash_verify_sdpa with DFLASH_KV_TURBO3 expands K and V inside the library: same bits as decoding first."""
+@pytest.mark.parametrize("n_hot", [0, 16, 256])
+def test_turbo_kv_format_of_the_attention_entry_point(n_hot):
+    """dflash_verify_sdpa with DFLASH_KV_TURBO3: the cold history is expanded inside the library, the hot window
+    (the reference keeps the newest tokens uncompressed) is appended: same bits as decoding and concatenating first."""
     from oracle import dflash_oracle as O
-    B, Hq, Hkv, N, D = 2, 16, 2, 16 + 900, 256
-    x = O.make_sdpa_inputs(B, Hq, Hkv, N, D, 4343, "bf16")
+    B, Hq, Hkv, D = 2, 16, 2, 256
+    n_cold = 768
+    N = n_cold + n_hot if n_hot else n_cold + 16
+    x = O.make_sdpa_inputs(B, Hq, Hkv, N, D, 4343 + n_hot, "bf16")
     k = torch.from_numpy(x["k"]).cuda().bfloat16()
     v = torch.from_numpy(x["v"]).cuda().bfloat16()
     q = torch.from_numpy(x["q"]).cuda().bfloat16()
-    k_enc = K().turbo_encode(k, True)
-    vp, _, vn, _ = K().turbo_encode(v, False)
-    fused = K().batched_sdpa_turbo_kv(q, k_enc, (vp, vn), N, float(x["scale"]))
+    cold = N - n_hot
+    k_enc = K().turbo_encode(k[:, :, :cold].contiguous(), True)
+    vp, _, vn, _ = K().turbo_encode(v[:, :, :cold].contiguous(), False)
+    k_hot = k[:, :, cold:].contiguous() if n_hot else None
+    v_hot = v[:, :, cold:].contiguous() if n_hot else None
+    fused = K().batched_sdpa_turbo_kv(q, k_enc, (vp, vn), cold, float(x["scale"]), k_hot=k_hot, v_hot=v_hot)
     k_hat = K().turbo_decode(*k_enc, dtype=torch.bfloat16)
     v_hat = K().turbo_decode(vp, None, vn, None, dtype=torch.bfloat16)
+    if n_hot:
+        k_hat, v_hat = torch.cat([k_hat, k_hot], dim=2), torch.cat([v_hat, v_hot], dim=2)
     two_step = K().batched_sdpa_2pass(q, k_hat, v_hat, float(x["scale"]))
     torch.cuda.synchronize()
     K().device_status()
     assert fused is not None and torch.equal(fused, two_step)
+    # against the oracle: its decode of its own encode for the cold part, the hot part as given
+    p, s_, n_, r_ = CO.turbo_encode_k(x["k"][:, :, :cold].reshape(-1, 128))
+    k_ref = O.round_bf16(CO.turbo_decode_k(p, s_, n_, r_)).reshape(B, Hkv, cold, D)
+    p, n_ = CO.turbo_encode_v(x["v"][:, :, :cold].reshape(-1, 128))
+    v_ref = O.round_bf16(CO.turbo_decode_v(p, n_)).reshape(B, Hkv, cold, D)
+    k_ref = np.concatenate([k_ref, x["k"][:, :, cold:]], axis=2)
+    v_ref = np.concatenate([v_ref, x["v"][:, :, cold:]], axis=2)
+    want = CO.verify_sdpa(x["q"], k_ref, v_ref, float(x["scale"]))
+    assert np.abs(fused.float().cpu().numpy() - want).max() < 2e-2

@@ -14,7 +14,7 @@ pytestmark = pytest.mark.gpu
 def test_small_step_matches_oracle_composition():
     from swiftlm_b200 import kernels
     from swiftlm_b200.verify_step import StepConfig, VerifyStep
-    cfg = StepConfig(batch=3, gdn_layers=3, attn_layers=1, Hk=2, Hv=4, Hq=16, Hkv=2, D=256, context=300, vocab=4096,
+    cfg = StepConfig(batch=3, gdn_layers=3, attn_layers=1, Hk=2, Hv=4, Hq=16, Hkv=2, D=256, context=384, vocab=4096,
                      conv_dim=64)
     step = VerifyStep(cfg, torch.device("cuda", 0))
     r = step.run()
@@ -39,10 +39,13 @@ def test_small_step_matches_oracle_composition():
         for b in range(cfg.batch):
             assert torch.equal(conv[b], full[b, int(replay[b]):int(replay[b]) + cfg.conv_kernel - 1])
     a = step.attn[0]
-    kq = a["kp"].cpu().numpy().reshape(-1, 48)
-    k_ref = O.round_bf16(CO.turbo_decode_k(kq, a["ks"].cpu().numpy().reshape(-1, 16), a["kn"].cpu().numpy().reshape(-1).view(np.uint16),
-                                           a["kr"].cpu().numpy().reshape(-1).view(np.uint16))).reshape(cfg.batch, cfg.Hkv, step.N, cfg.D)
-    v_ref = O.round_bf16(CO.turbo_decode_v(a["vp"].cpu().numpy().reshape(-1, 48),
-                                           a["vn"].cpu().numpy().reshape(-1).view(np.uint16))).reshape(cfg.batch, cfg.Hkv, step.N, cfg.D)
+    cold = cfg.context
+    k_cold = O.round_bf16(CO.turbo_decode_k(a["kp"].cpu().numpy().reshape(-1, 48), a["ks"].cpu().numpy().reshape(-1, 16),
+                                            a["kn"].cpu().numpy().reshape(-1).view(np.uint16),
+                                            a["kr"].cpu().numpy().reshape(-1).view(np.uint16))).reshape(cfg.batch, cfg.Hkv, cold, cfg.D)
+    v_cold = O.round_bf16(CO.turbo_decode_v(a["vp"].cpu().numpy().reshape(-1, 48),
+                                            a["vn"].cpu().numpy().reshape(-1).view(np.uint16))).reshape(cfg.batch, cfg.Hkv, cold, cfg.D)
+    k_ref = np.concatenate([k_cold, f(a["k_hot"])], axis=2)
+    v_ref = np.concatenate([v_cold, f(a["v_hot"])], axis=2)
     want = CO.verify_sdpa(f(a["q"]), k_ref, v_ref, step.scale)
     assert np.abs(f(r["attn_out"][0]) - want).max() < 2e-2
