@@ -171,6 +171,31 @@ def cpu_replay_sample(seqs: int, repeats: int = 1):
     return heads / best, best, CO.num_threads(), heads
 
 
+def cpu_ops_sample(seqs: int = 2):
+    """Times the op-for-op Torch-CPU statement of the reference's CPU path (five full-state passes per token,
+    all intra-op threads) on `seqs` sequences x 36 layers of configs[1]."""
+    import torch
+    from oracle import dflash_oracle as O
+    from oracle.torch_ops_oracle import gated_delta_ops_torch
+    cfg = CFG1
+    B = seqs * cfg["L"]
+    x = O.make_gdn_inputs(B, cfg["T"], cfg["Hk"], cfg["Hv"], cfg["D"], cfg["D"], SEED + 1000, False, "bf16")
+    rng = np.random.default_rng(SEED + 1001)
+    n = np.repeat(rng.integers(0, cfg["T"] + 1, seqs), cfg["L"]).astype(np.int32)
+    mask = (np.arange(cfg["T"])[None, :] < n[:, None]).astype(np.float32)
+    t = {k_: torch.from_numpy(np.ascontiguousarray(v_)) for k_, v_ in x.items() if k_ != "n"}
+    best = None
+    for _ in range(2):
+        t0 = time.perf_counter()
+        gated_delta_ops_torch(t["q"], t["k"], t["v"], t["g"], t["beta"], t["state"], torch.from_numpy(mask))
+        dt = time.perf_counter() - t0
+        best = dt if best is None else min(best, dt)
+    heads = B * cfg["Hv"]
+    return {"value": heads / best, "unit": "head-states/s", "threads": torch.get_num_threads(),
+            "sample": f"{seqs} of 64 sequences x 36 layers x 32 heads ({heads} head-states, best of 2 passes, {best:.2f} s each), "
+                      "Torch-CPU op-for-op statement of gatedDeltaOpsWithTape (all T steps computed, arithmetic masking)"}
+
+
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -315,7 +340,8 @@ def run_gpu(args):
         v, dt, threads, sample_heads = cpu_replay_sample(16, repeats=6)
         cpu = {"value": v, "unit": "head-states/s", "cores": threads, "kind": "port",
                "sample": f"16 of 64 sequences x 36 layers x 32 heads ({sample_heads} head-states, best of 6 passes, {dt:.2f} s each), OpenMP "
-                         f"row-wise C restatement of the reference's ops path"}
+                         f"row-wise C restatement of the reference's ops path",
+               "ops_path": cpu_ops_sample(2)}
 
     line = {
         "metric": "replayed_head_states_per_s", "value": value, "unit": "head-states/s", "n_gpus": world,

@@ -214,3 +214,16 @@ def test_rollback_indexing_contract():
     z = O.rebuild_conv_state(None, qkv, 1, 4)
     assert (z[:, :2] == 0).all() and (z[:, 2] == qkv[:, 0]).all()
     assert O.rebuild_conv_state(snap, qkv, 2, 1) is None
+
+
+def test_torch_ops_restatement_matches_numpy_oracle():
+    """The op-for-op Torch-CPU statement (timed by bench.py as the reference's CPU structure) against the NumPy one."""
+    from oracle.torch_ops_oracle import gated_delta_ops_torch
+    for vec in (False, True):
+        x = O.make_gdn_inputs(2, 16, 2, 4, 64, 32, 77 + vec, vec)
+        mask = (np.arange(16)[None, :] < x["n"][:, None]).astype(np.float32)
+        y, s, tape = gated_delta_ops_torch(x["q"], x["k"], x["v"], x["g"], x["beta"], x["state"], mask)
+        yo, so, to = O.gated_delta_ops_with_tape(x["q"], x["k"], x["v"], x["g"], x["beta"], x["state"], n_per_seq=x["n"])
+        assert np.abs(s.numpy() - so).max() <= 1e-5 * np.abs(so).max()
+        assert np.abs(y.numpy() - yo).max() <= 1e-5 * max(np.abs(yo).max(), 1e-30)
+        assert np.abs(tape.numpy() - to).max() <= 1e-5 * max(np.abs(to).max(), 1e-30)
