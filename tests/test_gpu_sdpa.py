@@ -51,6 +51,12 @@ CASES = [
     (2, 4, 4, 16 + 300, 256, "bf16"),         # no grouping (GQA 1)
     (1, 16, 1, 16 + 2100, 256, "bf16"),       # GQA 16: two 128-row query tiles per KV head
     (8, 16, 2, 16 + 4096, 256, "bf16"),       # a slice of the benchmark configuration
+    (32, 16, 2, 16 + 600, 256, "bf16"),       # 64 units: cluster pairs (two CTAs per unit, swap through distributed shared memory)
+    (8, 32, 8, 16 + 1000, 128, "bf16"),       # 64 units at D 128: cluster pairs with 32-column quarters
+    (20, 16, 2, 16 + 700, 256, "bf16"),       # 40 units: three equal cuts per unit, last finisher merges
+    (16, 16, 2, 16 + 900, 256, "fp16"),       # 32 units: four equal cuts per unit
+    (80, 16, 2, 16 + 300, 256, "bf16"),       # 160 units on 148 SMs: stream-K ranges that cover whole units and pieces
+    (37, 16, 2, 16 + 130, 256, "bf16"),       # 74 units of two tiles: one tile per CTA of a pair
 ]
 
 
