@@ -76,6 +76,9 @@ CASES = [
     (2, 8, 8, 16, 128, 128, False, "bf16"),       # the reference's consistency-check shape
     (2, 16, 1, 3, 32, 48, True, "fp32"),          # odd head ratio, Dv not a power of two
     (2, 20, 2, 4, 256, 64, False, "bf16"),        # T > 16, Dk = 256
+    (1, 1, 1, 4, 128, 128, False, "bf16"),        # a single step, four v-heads per qk-head (tensor-core path)
+    (3, 13, 4, 4, 128, 128, False, "bf16"),       # Hk == Hv, odd T (tensor-core path, rows of K/Q/V beyond T read as zeros)
+    (40, 16, 2, 4, 128, 128, False, "bf16"),      # more head-states than SMs (tensor-core path, several items per CTA)
 ]
 
 
