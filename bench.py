@@ -322,11 +322,23 @@ def run_gpu(args):
     # ---- verify attention, configs[2] (rank-local, same on every rank) ----
     sd = run_sdpa(torch, kernels, device, args, peaks)
     # ---- long-context verify attention, configs[3]: the 16 (sequence, KV head) pairs sharded over the ranks ----
-    sd_long = run_sdpa_long(torch, kernels, device, rank, world, peaks, max_over_ranks)
+    # The two sections below are additional reporting: a failure in one of them (say, memory on a shared box) is
+    # recorded in its place and does not take the headline with it.  Every rank reaches the same collectives or none:
+    # the failure flag is agreed on before the next section starts.
+    def guarded(fn):
+        try:
+            out, bad = fn(), 0.0
+        except Exception as e:  # noqa: BLE001
+            out, bad = {"error": f"{type(e).__name__}: {e}"[:300]}, 1.0
+        if max_over_ranks(bad) > 0 and "error" not in out:
+            out = {"error": "failed on another rank"}
+        return out
+
+    sd_long = guarded(lambda: run_sdpa_long(torch, kernels, device, rank, world, peaks, max_over_ranks))
     # ---- the composed verify step, configs[4]: 64 sequences sharded by sequence over the ranks ----
     del x
     torch.cuda.empty_cache()
-    vstep = run_verify_step(torch, device, rank, world, peaks, max_over_ranks, barrier)
+    vstep = guarded(lambda: run_verify_step(torch, device, rank, world, peaks, max_over_ranks, barrier))
 
     if world > 1:
         dist.barrier()
