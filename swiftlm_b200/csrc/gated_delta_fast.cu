@@ -1,5 +1,5 @@
 // Gated-delta forward with tape / tape replay for the production shape: Dk = Dv = 128,
-// scalar gate, T <= 16 (one DFlash verify block).  HBM-bound by design: the 64 KiB fp32 state of
+// scalar or per-channel gate, T <= 16 (one DFlash verify block).  HBM-bound by design: the 64 KiB fp32 state of
 // every (sequence, v-head) is read once and written once; everything else is small.
 //
 // Structure (persistent CTAs of 256 threads, two resident per SM for 16-bit inputs so that one
@@ -15,7 +15,9 @@
 //   * the state is carried as S = G * U with a running scalar G (product of the gates so far):
 //       kv = G <U_row, k>,  delta = (v - kv) beta,  U_row += (delta / G) k,  y = G <U_row, q>
 //     i.e. 3 packed fp32x2 fused multiply-adds per state element per step instead of 4; G is
-//     folded back into U when it gets small (or a gate is exactly 0);
+//     folded back into U when it gets small (or a gate is exactly 0); with a per-channel gate
+//     (a [Dk] vector per step, kept in its input type in shared memory and widened as it is read)
+//     the state is decayed column by column in the reference's own order, 4 operations per element;
 //   * the new state leaves as full 128-byte lines; y and the tape are staged per warp and written
 //     as 16-byte pieces.
 // Work items are ordered so that consecutive items come from different sequences: accepted
@@ -36,7 +38,7 @@ constexpr int kTmax = 16;
 constexpr int kThreads = 256;
 constexpr uint32_t kStateBytes = kD * kD * 4;
 
-template <typename InT, bool REPLAY>
+template <typename InT, bool REPLAY, bool VEC>
 struct Layout {
   static constexpr uint32_t in_row = kD * sizeof(InT);
   static constexpr uint32_t f32_tile = kTmax * kD * 4;
@@ -44,12 +46,14 @@ struct Layout {
   static constexpr uint32_t raw_k = kStateBytes;
   static constexpr uint32_t raw_q = raw_k + kTmax * in_row;                       // forward only
   static constexpr uint32_t raw_v = REPLAY ? raw_q : raw_q + kTmax * in_row;      // v (InT) or recorded delta (fp32)
-  static constexpr uint32_t raw_end = raw_v + kTmax * (REPLAY ? kD * 4 : in_row);
+  // per-channel gate only: two buffers, because the gate is read during the recurrence while the next item's inputs land
+  static constexpr uint32_t raw_g = raw_v + kTmax * (REPLAY ? kD * 4 : in_row);
+  static constexpr uint32_t raw_end = raw_g + (VEC ? 2 * kTmax * in_row : 0);
   static constexpr uint32_t k32 = raw_end;                                        // [16][128] fp32
   static constexpr uint32_t q32 = k32 + f32_tile;                                 // forward only
   static constexpr uint32_t d32 = REPLAY ? q32 : q32 + f32_tile;                  // [8 warps][16 steps][16 rows]: v / delta in; y out
-  static constexpr uint32_t dout = d32 + f32_tile;                                // forward only: delta out
-  static constexpr uint32_t scal = REPLAY ? dout : dout + f32_tile;
+  static constexpr uint32_t dout = d32 + f32_tile;                                // forward with a scalar gate only: delta out
+  static constexpr uint32_t scal = (REPLAY || VEC) ? dout : dout + f32_tile;
   static constexpr uint32_t s_beta = scal;               // [3][16]
   static constexpr uint32_t s_g = s_beta + 3 * 16 * 4;   // [3][16]
   static constexpr uint32_t s_bits = s_g + 3 * 16 * 4;   // [4]
@@ -84,6 +88,23 @@ template <> __device__ __forceinline__ void load8_as_f32<__half>(const __half* s
     o[2 * i + 1] = f.y;
   }
 }
+// four consecutive elements widened to two fp32 pairs
+template <typename InT> __device__ __forceinline__ void load4_as_f32x2(const InT* src, float2 (&o)[2]);
+template <> __device__ __forceinline__ void load4_as_f32x2<float>(const float* src, float2 (&o)[2]) {
+  const float4 a = *reinterpret_cast<const float4*>(src);
+  o[0] = make_float2(a.x, a.y);
+  o[1] = make_float2(a.z, a.w);
+}
+template <> __device__ __forceinline__ void load4_as_f32x2<__nv_bfloat16>(const __nv_bfloat16* src, float2 (&o)[2]) {
+  const uint2 u = *reinterpret_cast<const uint2*>(src);
+  o[0] = make_float2(__uint_as_float(u.x << 16), __uint_as_float(u.x & 0xffff0000u));
+  o[1] = make_float2(__uint_as_float(u.y << 16), __uint_as_float(u.y & 0xffff0000u));
+}
+template <> __device__ __forceinline__ void load4_as_f32x2<__half>(const __half* src, float2 (&o)[2]) {
+  const uint2 u = *reinterpret_cast<const uint2*>(src);
+  o[0] = __half22float2(*reinterpret_cast<const __half2*>(&u.x));
+  o[1] = __half22float2(*reinterpret_cast<const __half2*>(&u.y));
+}
 template <typename OutT> __device__ __forceinline__ void store8(OutT* dst, const float (&v)[8]);
 template <> __device__ __forceinline__ void store8<float>(float* dst, const float (&v)[8]) {
   *reinterpret_cast<float4*>(dst) = make_float4(v[0], v[1], v[2], v[3]);
@@ -115,10 +136,10 @@ __device__ __forceinline__ float reduce4_over8(const float (&v)[4], int lane) {
   return x;
 }
 
-template <typename InT, bool REPLAY>
+template <typename InT, bool REPLAY, bool VEC>
 __global__ void __launch_bounds__(kThreads, sizeof(InT) == 2 ? 2 : 1)
 gdn_fast_kernel(const __grid_constant__ CUtensorMap state_map, const GdnArgs a, int* status) {
-  using L = Layout<InT, REPLAY>;
+  using L = Layout<InT, REPLAY, VEC>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* sm = smem_raw + ((1024u - (ptx::smem_u32(smem_raw) & 1023u)) & 1023u);
 
@@ -160,7 +181,7 @@ gdn_fast_kernel(const __grid_constant__ CUtensorMap state_map, const GdnArgs a, 
     return on;
   };
   // cp.async of the per-token inputs of item (b, hv) for the steps in `bits`
-  auto issue_inputs = [&](int b, int hv, uint32_t bits) {
+  auto issue_inputs = [&](int b, int hv, uint32_t bits, int gbuf) {
     const int hk = hv / rep;
     constexpr int cpr = L::in_row / 16;  // 16-byte chunks per k/q/v row
     for (int c = tid; c < kTmax * cpr; c += kThreads) {
@@ -168,6 +189,8 @@ gdn_fast_kernel(const __grid_constant__ CUtensorMap state_map, const GdnArgs a, 
       if (t < T && ((bits >> t) & 1u)) {
         const long long bt = (long long)b * T + t;
         ptx::cp_async16(sm + L::raw_k + t * L::in_row + off, reinterpret_cast<const uint8_t*>(gk + (bt * a.Hk + hk) * kD) + off);
+        if (VEC)
+          ptx::cp_async16(sm + L::raw_g + (gbuf * kTmax + t) * L::in_row + off, reinterpret_cast<const uint8_t*>(gg + (bt * a.Hv + hv) * kD) + off);
         if (!REPLAY) {
           ptx::cp_async16(sm + L::raw_q + t * L::in_row + off, reinterpret_cast<const uint8_t*>(gq + (bt * a.Hk + hk) * kD) + off);
           ptx::cp_async16(sm + L::raw_v + t * L::in_row + off, reinterpret_cast<const uint8_t*>(gv + (bt * a.Hv + hv) * kD) + off);
@@ -216,12 +239,12 @@ gdn_fast_kernel(const __grid_constant__ CUtensorMap state_map, const GdnArgs a, 
     if (lane == 0) { s_bits[0] = m0; s_bits[1] = m1; }
   } else if (w == 1 && lane < T) {
     const long long bt = (long long)b_cur * T + lane;
-    s_g[lane] = to_f32(gg[bt * a.Hv + hv_cur]);
+    if (!VEC) s_g[lane] = to_f32(gg[bt * a.Hv + hv_cur]);
     if (!REPLAY) s_beta[lane] = to_f32(gbeta[bt * a.Hv + hv_cur]);
   }
   __syncthreads();
   if (tid == 0) issue_state(b_cur, hv_cur);
-  issue_inputs(b_cur, hv_cur, s_bits[0]);
+  issue_inputs(b_cur, hv_cur, s_bits[0], 0);
   ptx::cp_async_commit();
 
   const int col = 4 * c_sub;                                  // this thread's 4 columns inside each 32-column box
@@ -246,7 +269,7 @@ gdn_fast_kernel(const __grid_constant__ CUtensorMap state_map, const GdnArgs a, 
       }
     } else if (w == 1 && has_next && lane < T) {
       const long long bt = (long long)b_nxt * T + lane;
-      g_next = to_f32(gg[bt * a.Hv + hv_nxt]);
+      if (!VEC) g_next = to_f32(gg[bt * a.Hv + hv_nxt]);
       if (!REPLAY) beta_next = to_f32(gbeta[bt * a.Hv + hv_nxt]);
     }
 
@@ -299,7 +322,7 @@ gdn_fast_kernel(const __grid_constant__ CUtensorMap state_map, const GdnArgs a, 
 
     if (has_next) {
       if (tid == 0) issue_state(b_nxt, hv_nxt);
-      issue_inputs(b_nxt, hv_nxt, s_bits[(it + 1) % 3]);
+      issue_inputs(b_nxt, hv_nxt, s_bits[(it + 1) % 3], (it + 1) & 1);
     }
     ptx::cp_async_commit();
 
@@ -314,8 +337,15 @@ gdn_fast_kernel(const __grid_constant__ CUtensorMap state_map, const GdnArgs a, 
         kk[box][0] = f2(k4.x, k4.y);
         kk[box][1] = f2(k4.z, k4.w);
       }
-      Gd *= s_g[slot * 16 + t];
-      if (Gd < 1e-12f) {  // uniform per work item: U <- Gd * U, Gd <- 1
+      float2 gg2[4][2];   // per-channel gate of this thread's 16 columns
+      if (VEC) {
+        const InT* grow = reinterpret_cast<const InT*>(sm + L::raw_g) + ((it & 1) * kTmax + t) * kD;
+#pragma unroll
+        for (int box = 0; box < 4; ++box) load4_as_f32x2<InT>(grow + 32 * box + col, gg2[box]);
+      } else {
+        Gd *= s_g[slot * 16 + t];
+      }
+      if (!VEC && Gd < 1e-12f) {  // uniform per work item: U <- Gd * U, Gd <- 1
         const float2 G2 = f2(Gd, Gd);
 #pragma unroll
         for (int i = 0; i < 4; ++i)
@@ -336,13 +366,20 @@ gdn_fast_kernel(const __grid_constant__ CUtensorMap state_map, const GdnArgs a, 
           for (int i = 0; i < 4; ++i) {
             const float2 dd = f2(d[i], d[i]);
 #pragma unroll
-            for (int j = 0; j < 2; ++j) S[i][box][j] = __ffma2_rn(dd, kk[box][j], S[i][box][j]);
+            for (int j = 0; j < 2; ++j)
+              S[i][box][j] = __ffma2_rn(dd, kk[box][j], VEC ? __fmul2_rn(S[i][box][j], gg2[box][j]) : S[i][box][j]);
           }
       } else {
         const float beta = s_beta[slot * 16 + t];
         float part[4];
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
+          if (VEC) {
+#pragma unroll
+            for (int box = 0; box < 4; ++box)
+#pragma unroll
+              for (int j = 0; j < 2; ++j) S[i][box][j] = __fmul2_rn(S[i][box][j], gg2[box][j]);
+          }
           float2 acc0 = __fmul2_rn(S[i][0][0], kk[0][0]), acc1 = __fmul2_rn(S[i][0][1], kk[0][1]);
 #pragma unroll
           for (int box = 1; box < 4; ++box) {
@@ -378,7 +415,9 @@ gdn_fast_kernel(const __grid_constant__ CUtensorMap state_map, const GdnArgs a, 
         const float y_mine = Gd * reduce4_over8(y_part, lane);
         if (!(lane & 4)) {  // lanes 0-3 of each 8-lane group hold the four rows' results
           d32[t * 16 + my_r] = y_mine;   // y takes the slot v was read from
-          dout[t * 16 + my_r] = d_mine;
+          if (!VEC) dout[t * 16 + my_r] = d_mine;
+          else if (a.tape)   // no staging tile in this variant: 16 lanes write the warp's 64 contiguous bytes of the step
+            a.tape[(((long long)b_cur * T + t) * a.Hv + hv_cur) * kD + 16 * w + my_r] = d_mine;
         }
       }
     }
@@ -411,11 +450,11 @@ gdn_fast_kernel(const __grid_constant__ CUtensorMap state_map, const GdnArgs a, 
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
           yv[i] = on ? d32[t * 16 + 8 * half + i] : 0.f;
-          dv[i] = on ? dout[t * 16 + 8 * half + i] : 0.f;
+          dv[i] = (on && !VEC) ? dout[t * 16 + 8 * half + i] : 0.f;
         }
         const long long o = (((long long)b_cur * T + t) * a.Hv + hv_cur) * kD + 16 * w + 8 * half;
         store8<InT>(reinterpret_cast<InT*>(a.y) + o, yv);
-        if (a.tape) store8<float>(a.tape + o, dv);
+        if (a.tape && (!VEC || !on)) store8<float>(a.tape + o, dv);
       }
     }
 
@@ -424,7 +463,7 @@ gdn_fast_kernel(const __grid_constant__ CUtensorMap state_map, const GdnArgs a, 
       const uint32_t m = __ballot_sync(0xffffffffu, on2);
       if (lane == 0) s_bits[(it + 2) % 3] = m;
     } else if (w == 1 && lane < T) {
-      s_g[((it + 1) % 3) * 16 + lane] = g_next;
+      if (!VEC) s_g[((it + 1) % 3) * 16 + lane] = g_next;
       if (!REPLAY) s_beta[((it + 1) % 3) * 16 + lane] = beta_next;
     }
     if (!has_next) break;
@@ -433,9 +472,10 @@ gdn_fast_kernel(const __grid_constant__ CUtensorMap state_map, const GdnArgs a, 
   }
 }
 
-template <typename InT, bool REPLAY>
-int32_t launch_typed(const GdnArgs& a, cudaStream_t stream) {
-  using L = Layout<InT, REPLAY>;
+template <typename InT, bool REPLAY, bool VEC>
+int32_t launch_variant(const GdnArgs& a, cudaStream_t stream) {
+  using L = Layout<InT, REPLAY, VEC>;
+  static_assert(sizeof(InT) != 2 || 2 * (L::alloc + 1024) <= 228 * 1024, "two CTAs of a 16-bit variant must fit one SM");
   EncodeTiledFn encode = tensor_map_encoder();
   if (!encode) {
     set_error("cuTensorMapEncodeTiled is not available from this driver");
@@ -459,7 +499,7 @@ int32_t launch_typed(const GdnArgs& a, cudaStream_t stream) {
     set_error("cuTensorMapEncodeTiled(state) failed with CUresult %d", (int)r);
     return DFLASH_ERR_CUDA;
   }
-  auto kernel = gdn_fast_kernel<InT, REPLAY>;
+  auto kernel = gdn_fast_kernel<InT, REPLAY, VEC>;
   DFLASH_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)L::alloc));
   const long long items = (long long)a.B * a.Hv;
   const int per_sm = sizeof(InT) == 2 ? 2 : 1;
@@ -470,10 +510,15 @@ int32_t launch_typed(const GdnArgs& a, cudaStream_t stream) {
   return DFLASH_OK;
 }
 
+template <typename InT, bool REPLAY>
+int32_t launch_typed(const GdnArgs& a, cudaStream_t stream) {
+  return a.g_is_vector ? launch_variant<InT, REPLAY, true>(a, stream) : launch_variant<InT, REPLAY, false>(a, stream);
+}
+
 }  // namespace
 
 bool gdn_fast_supported(const GdnArgs& a) {
-  if (a.Dk != kD || a.Dv != kD || a.g_is_vector || a.T > kTmax) return false;
+  if (a.Dk != kD || a.Dv != kD || a.T > kTmax) return false;
   if ((long long)a.B * a.Hv > (1LL << 24) - 1024) return false;   // 32-bit item and TMA row arithmetic
   return a.in_dtype == DFLASH_F32 || a.in_dtype == DFLASH_BF16 || a.in_dtype == DFLASH_F16;
 }

@@ -8,7 +8,8 @@
 // counts for the GB/s column (main.swift:119-124, 164-166, 220-222) and the same
 // median / min / max report (main.swift:42-66).  Wall-clock around a lazy-graph evaluation
 // (main.swift:33-39) becomes a pair of CUDA events on the launching stream.  --batch B scales
-// the batch dimension (not in the reference).  The reference's "variants" and "ops" sections
+// the batch dimension and --cold rotates the large inputs among copies that together exceed the L2 cache (neither is in
+// the reference).  The reference's "variants" and "ops" sections
 // compare Metal source variants and its CPU fallback; neither exists here.
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
@@ -29,6 +30,7 @@ struct Args {
   int iterations = 200, warmup = 20, batch = 1;
   std::string kernels = "tape,gdelta,sdpa";
   bool long_ctx = false;
+  bool cold = false;   // rotate among copies of the inputs that together exceed the L2 cache
   bool has(const char* k) const { return ("," + kernels + ",").find(std::string(",") + k + ",") != std::string::npos; }
 };
 
@@ -55,17 +57,24 @@ static float* rand_f32(size_t n) {
 }
 
 struct Result { double med, mn, mx; };
+// how many copies of a working set of `bytes` exceed the L2 cache comfortably (1 when warm)
+static int copies_for(const Args& a, double bytes) {
+  if (!a.cold) return 1;
+  const double target = 400e6;   // the L2 of a B200 holds 126 MB
+  int n = (int)(target / bytes) + 1;
+  return n < 2 ? 2 : (n > 256 ? 256 : n);
+}
 template <typename F>
 static Result measure(const Args& a, F&& body) {
   cudaEvent_t e0, e1;
   CK(cudaEventCreate(&e0));
   CK(cudaEventCreate(&e1));
-  for (int i = 0; i < a.warmup; ++i) body();
+  for (int i = 0; i < a.warmup; ++i) body(i);
   CK(cudaDeviceSynchronize());
   std::vector<double> s;
   for (int i = 0; i < a.iterations; ++i) {
     CK(cudaEventRecord(e0, 0));
-    body();
+    body(a.warmup + i);
     CK(cudaEventRecord(e1, 0));
     CK(cudaEventSynchronize(e1));
     float ms;
@@ -89,22 +98,26 @@ static void bench_tape(const Args& a) {
   __nv_bfloat16* k = rand_bf16((size_t)B * T * Hk * Dk);
   __nv_bfloat16* g = rand_bf16((size_t)B * T * Hv, 0.5f);
   __nv_bfloat16* gvec = rand_bf16((size_t)B * T * Hv * Dk, 0.5f);
-  float* state = rand_f32((size_t)B * Hv * Dv * Dk);
-  float* out;
-  CK(cudaMalloc(&out, (size_t)B * Hv * Dv * Dk * 4));
+  const double state_bytes = (double)B * Hv * Dv * Dk * 4;   // fp32 state here (bf16 in the reference)
+  const int nc = copies_for(a, state_bytes * 2);
+  std::vector<float*> state(nc), out(nc);
+  for (int c = 0; c < nc; ++c) {
+    state[c] = rand_f32((size_t)B * Hv * Dv * Dk);
+    CK(cudaMalloc(&out[c], (size_t)B * Hv * Dv * Dk * 4));
+  }
   std::vector<__nv_bfloat16> hm((size_t)B * T);
   for (auto& m : hm) m = __float2bfloat16(urand() >= 0.f ? 1.f : 0.f);
   __nv_bfloat16* mask;
   CK(cudaMalloc(&mask, hm.size() * 2));
   CK(cudaMemcpy(mask, hm.data(), hm.size() * 2, cudaMemcpyHostToDevice));
-  const double state_bytes = (double)B * Hv * Dv * Dk * 4;   // fp32 state here (bf16 in the reference)
-  auto run = [&](const void* gate, int vec, const void* m) {
-    DF(dflash_tape_replay(tape, k, gate, state, m, nullptr, out, B, T, Hk, Hv, Dk, Dv, vec, DFLASH_BF16, DFLASH_BF16, nullptr));
+  auto run = [&](int i, const void* gate, int vec, const void* m) {
+    DF(dflash_tape_replay(tape, k, gate, state[i % nc], m, nullptr, out[i % nc], B, T, Hk, Hv, Dk, Dv, vec, DFLASH_BF16, DFLASH_BF16, nullptr));
   };
-  print_result("scalar-g, no mask", measure(a, [&] { run(g, 0, nullptr); }), state_bytes * 2);
-  print_result("scalar-g, mask", measure(a, [&] { run(g, 0, mask); }), state_bytes * 2);
-  print_result("vec-g, no mask", measure(a, [&] { run(gvec, 1, nullptr); }), state_bytes * 2);
-  print_result("vec-g, mask", measure(a, [&] { run(gvec, 1, mask); }), state_bytes * 2);
+  print_result("scalar-g, no mask", measure(a, [&](int i) { run(i, g, 0, nullptr); }), state_bytes * 2);
+  print_result("scalar-g, mask", measure(a, [&](int i) { run(i, g, 0, mask); }), state_bytes * 2);
+  print_result("vec-g, no mask", measure(a, [&](int i) { run(i, gvec, 1, nullptr); }), state_bytes * 2);
+  print_result("vec-g, mask", measure(a, [&](int i) { run(i, gvec, 1, mask); }), state_bytes * 2);
+  for (int c = 0; c < nc; ++c) { CK(cudaFree(state[c])); CK(cudaFree(out[c])); }
 }
 
 static void bench_gdelta(const Args& a) {
@@ -115,10 +128,14 @@ static void bench_gdelta(const Args& a) {
   __nv_bfloat16* g = rand_bf16((size_t)B * T * Hv, 0.5f);
   __nv_bfloat16* gvec = rand_bf16((size_t)B * T * Hv * Dk, 0.5f);
   __nv_bfloat16* beta = rand_bf16((size_t)B * T * Hv, 0.5f);
-  float* state = rand_f32((size_t)B * Hv * Dv * Dk);
-  float *out, *tape;
+  const int nc = copies_for(a, (double)B * Hv * Dv * Dk * 4 * 2);
+  std::vector<float*> state(nc), out(nc);
+  for (int c = 0; c < nc; ++c) {
+    state[c] = rand_f32((size_t)B * Hv * Dv * Dk);
+    CK(cudaMalloc(&out[c], (size_t)B * Hv * Dv * Dk * 4));
+  }
+  float* tape;
   __nv_bfloat16* y;
-  CK(cudaMalloc(&out, (size_t)B * Hv * Dv * Dk * 4));
   CK(cudaMalloc(&tape, (size_t)B * T * Hv * Dv * 4));
   CK(cudaMalloc(&y, (size_t)B * T * Hv * Dv * 2));
   std::vector<__nv_bfloat16> hm((size_t)B * T);
@@ -129,14 +146,15 @@ static void bench_gdelta(const Args& a) {
   // q + k + v inputs, state in + out (fp32 here), tape out (main.swift:164-166)
   const double bytes = ((double)B * T * Hk * Dk * 2 + (double)B * T * Hv * Dv) * 2 + (double)B * Hv * Dv * Dk * 4 * 2 +
                        (double)B * T * Hv * Dv * 4;
-  auto run = [&](const void* gate, int vec, const void* m) {
-    DF(dflash_gated_delta_tape(q, k, v, gate, beta, state, m, nullptr, y, out, tape, B, T, Hk, Hv, Dk, Dv, vec, DFLASH_BF16,
+  auto run = [&](int i, const void* gate, int vec, const void* m) {
+    DF(dflash_gated_delta_tape(q, k, v, gate, beta, state[i % nc], m, nullptr, y, out[i % nc], tape, B, T, Hk, Hv, Dk, Dv, vec, DFLASH_BF16,
                                DFLASH_BF16, nullptr));
   };
-  print_result("scalar-g, no mask", measure(a, [&] { run(g, 0, nullptr); }), bytes);
-  print_result("scalar-g, mask", measure(a, [&] { run(g, 0, mask); }), bytes);
-  print_result("vec-g, no mask", measure(a, [&] { run(gvec, 1, nullptr); }), bytes);
-  print_result("vec-g, mask", measure(a, [&] { run(gvec, 1, mask); }), bytes);
+  print_result("scalar-g, no mask", measure(a, [&](int i) { run(i, g, 0, nullptr); }), bytes);
+  print_result("scalar-g, mask", measure(a, [&](int i) { run(i, g, 0, mask); }), bytes);
+  print_result("vec-g, no mask", measure(a, [&](int i) { run(i, gvec, 1, nullptr); }), bytes);
+  print_result("vec-g, mask", measure(a, [&](int i) { run(i, gvec, 1, mask); }), bytes);
+  for (int c = 0; c < nc; ++c) { CK(cudaFree(state[c])); CK(cudaFree(out[c])); }
 }
 
 static void bench_sdpa(const Args& a) {
@@ -149,18 +167,22 @@ static void bench_sdpa(const Args& a) {
   __nv_bfloat16* out;
   CK(cudaMalloc(&out, (size_t)B * Hq * T * D * 2));
   for (int n : sizes) {
-    __nv_bfloat16 *k = rand_bf16((size_t)B * Hk * n * D), *v = rand_bf16((size_t)B * Hk * n * D);
+    const double kv_bytes = 2.0 * B * Hk * n * D * 2;
+    const int nc = copies_for(a, kv_bytes);
+    std::vector<__nv_bfloat16*> k(nc), v(nc);
+    for (int c = 0; c < nc; ++c) { k[c] = rand_bf16((size_t)B * Hk * n * D); v[c] = rand_bf16((size_t)B * Hk * n * D); }
     const size_t ws_bytes = dflash_verify_sdpa_workspace_bytes(B, Hq, Hk, D, n);
     void* ws;
     CK(cudaMalloc(&ws, ws_bytes));
     const double bytes = ((double)B * Hq * T * D + 2.0 * B * Hk * n * D) * 2 + (double)B * Hq * T * D * 2;   // main.swift:220-222
     char label[64];
     snprintf(label, sizeof label, "nKV=%d", n);
-    print_result(label, measure(a, [&] {
-                   DF(dflash_verify_sdpa(q, k, v, nullptr, nullptr, nullptr, out, ws, ws_bytes, B, Hq, Hk, T, D, n, 0, 0, scale,
+    print_result(label, measure(a, [&](int i) {
+                   DF(dflash_verify_sdpa(q, k[i % nc], v[i % nc], nullptr, nullptr, nullptr, out, ws, ws_bytes, B, Hq, Hk, T, D, n, 0, 0, scale,
                                          DFLASH_BF16, DFLASH_KV_DENSE, nullptr));
                  }), bytes);
-    CK(cudaFree(k)); CK(cudaFree(v)); CK(cudaFree(ws));
+    for (int c = 0; c < nc; ++c) { CK(cudaFree(k[c])); CK(cudaFree(v[c])); }
+    CK(cudaFree(ws));
   }
 }
 
@@ -172,13 +194,15 @@ int main(int argc, char** argv) {
     else if (!strcmp(argv[i], "--batch") && i + 1 < argc) a.batch = atoi(argv[++i]);
     else if (!strcmp(argv[i], "--kernels") && i + 1 < argc) a.kernels = argv[++i];
     else if (!strcmp(argv[i], "--long-ctx")) a.long_ctx = true;
+    else if (!strcmp(argv[i], "--cold")) a.cold = true;
   }
   if (dflash_device_count() < 1) { fprintf(stderr, "no CUDA device (there is no CPU fallback)\n"); return 1; }
   cudaDeviceProp p;
   CK(cudaGetDeviceProperties(&p, 0));
   printf("DFlash Kernel Micro-Benchmark (%s)\n", dflash_version());
-  printf("  Device:     %s, %d SMs\n  Iterations: %d  Warmup: %d  Batch: %d\n  Kernels:    %s\n  Long-ctx:   %s\n", p.name,
-         p.multiProcessorCount, a.iterations, a.warmup, a.batch, a.kernels.c_str(), a.long_ctx ? "true" : "false");
+  printf("  Device:     %s, %d SMs\n  Iterations: %d  Warmup: %d  Batch: %d\n  Kernels:    %s\n  Long-ctx:   %s\n  L2:         %s\n", p.name,
+         p.multiProcessorCount, a.iterations, a.warmup, a.batch, a.kernels.c_str(), a.long_ctx ? "true" : "false",
+         a.cold ? "cold (inputs rotate among copies that exceed the cache)" : "warm (same buffers every iteration)");
   if (a.has("tape")) bench_tape(a);
   if (a.has("gdelta")) bench_gdelta(a);
   if (a.has("sdpa")) bench_sdpa(a);

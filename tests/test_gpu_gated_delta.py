@@ -79,6 +79,9 @@ CASES = [
     (1, 1, 1, 4, 128, 128, False, "bf16"),        # a single step, four v-heads per qk-head (tensor-core path)
     (3, 13, 4, 4, 128, 128, False, "bf16"),       # Hk == Hv, odd T (tensor-core path, rows of K/Q/V beyond T read as zeros)
     (40, 16, 2, 4, 128, 128, False, "bf16"),      # more head-states than SMs (tensor-core path, several items per CTA)
+    (3, 16, 2, 6, 128, 128, True, "fp16"),        # vector gate, three v-heads per qk-head
+    (2, 11, 4, 4, 128, 128, True, "fp32"),        # vector gate, fp32 inputs, odd T
+    (160, 16, 2, 4, 128, 128, True, "bf16"),      # vector gate, three items per CTA (both gate buffers reused)
 ]
 
 
@@ -125,8 +128,9 @@ def test_tape_replay_matches_oracle_and_forward(case):
     assert rel(s_all.cpu().numpy(), s_full.cpu().numpy()) < STATE_RTOL
 
 
-def test_edge_lengths_and_determinism():
-    x = O.make_gdn_inputs(4, 16, 2, 4, 128, 128, 900, False, "bf16")
+@pytest.mark.parametrize("vec", [False, True], ids=["scalar_gate", "vector_gate"])
+def test_edge_lengths_and_determinism(vec):
+    x = O.make_gdn_inputs(4, 16, 2, 4, 128, 128, 900, vec, "bf16")
     x["n"] = np.array([0, 16, 1, 15], np.int32)
     y, s, tape = run_fwd(x, "bf16")
     np.testing.assert_array_equal(s[0], x["state"][0])          # n = 0: identity

@@ -32,6 +32,18 @@ def test_bench_runs_every_section():
     assert r.stdout.rstrip().endswith("Done.")
 
 
+@pytest.mark.gpu
+def test_bench_cold_cache_mode():
+    """--cold rotates the large inputs among copies that exceed the L2 cache; same sections, same line format."""
+    build.build()
+    r = subprocess.run([BIN, "--iterations", "6", "--warmup", "2", "--kernels", "tape,sdpa", "--cold"],
+                       capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stdout + r.stderr
+    assert re.search(r"L2:\s+cold", r.stdout), r.stdout
+    assert len([l for l in r.stdout.splitlines() if " med " in l]) == 7, r.stdout
+    assert r.stdout.rstrip().endswith("Done.")
+
+
 SELFTEST = os.path.join(os.path.dirname(build.__file__), "bin", "dflash_host_selftest")
 
 
