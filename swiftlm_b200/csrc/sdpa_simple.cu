@@ -1,7 +1,7 @@
 // Block-verify attention on CUDA cores: the general path of dflash_verify_sdpa.
 //
-// Serves what the tensor-core kernel (sdpa_tc.cu) does not take — an additive mask, or a
-// device where the fast path is not eligible — with the exact semantics of the reference's
+// Serves what the tensor-core kernel (sdpa_tc.cu) does not take — a call without the tensor-core
+// kernel's workspace, a non-positive scale, more than 4096 ragged sequences — with the exact semantics of the reference's
 // two-pass kernel (Sources/DFlash/DFlashKernels.swift:563-649, :661-720): q pre-scaled,
 // fp32 online softmax one key at a time, visibility n <= N_b - 16 + r, optional additive mask
 // whose entries below the dtype's finite minimum hide the key, log-sum-exp merge of the

@@ -14,7 +14,10 @@
 //              tensor memory (bf16, aliasing the S buffer) and V MN-major from shared memory.
 //              Owns the tensor-memory allocation.
 //   warps 2-9  softmax: two threads per query row (64 key columns each).  Loads its part of S,
-//              applies the block-causal rule on the last tiles, keeps a running reference
+//              adds the additive mask if there is one (a second instantiation of the kernel; the
+//              thread's 64 mask values of a tile are fetched before it waits for S, rows read
+//              16 bytes at a time when N is a multiple of 8; an entry below the dtype's lowest
+//              finite value hides the key), applies the block-causal rule on the last tiles, keeps a running reference
 //              maximum and sum, writes P (bf16) back to tensor memory, rescales O only when the
 //              maximum grew by more than 2^8, and at the end of a segment normalises and stores.
 // KV is split across CTAs stream-K style: the (unit, 128-key tile) pairs of the whole batch
@@ -84,6 +87,8 @@ struct TcParams {
   int units;               // B * Hkv * MT
   long long total_tiles;   // only valid when kv_len == nullptr
   float scale_log2;
+  float inv_scale;         // additive mask values are brought to raw-score units: mask / scale
+  int mask_vec;            // 1: mask rows can be read 16 bytes at a time (base 16-byte aligned, N a multiple of 8)
   int split;               // 0: stream-K ranges; c > 0: every unit cut into c equal ranges (uniform N only)
   int pair;                // 1: split == 2 and the two CTAs of a unit form a cluster that merges through
                            //    distributed shared memory (no partials in global memory)
@@ -277,7 +282,40 @@ template <> __device__ __forceinline__ uint32_t pack2<__half>(float a, float b) 
   return *reinterpret_cast<const uint32_t*>(&v);
 }
 
-template <typename InT, int D>
+// This thread's 64 additive-mask values of one key tile (row `mrow`, keys n0 .. n0+63), as 32 packed pairs.
+// Keys at or beyond N, and rows outside the group (mrow == nullptr), read as 0: the visibility rule hides them anyway.
+template <typename InT>
+__device__ __forceinline__ void load_mask64(const InT* mrow, int n0, int N, bool vec, uint32_t (&mk)[32]) {
+  if (mrow && vec && n0 + 64 <= N) {
+    const uint4* src = reinterpret_cast<const uint4*>(mrow + n0);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const uint4 u = __ldg(src + i);
+      mk[4 * i] = u.x; mk[4 * i + 1] = u.y; mk[4 * i + 2] = u.z; mk[4 * i + 3] = u.w;
+    }
+  } else {
+    const unsigned short* src = reinterpret_cast<const unsigned short*>(mrow);
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      const uint32_t lo = (mrow && n0 + 2 * i < N) ? (uint32_t)__ldg(src + n0 + 2 * i) : 0u;
+      const uint32_t hi = (mrow && n0 + 2 * i + 1 < N) ? (uint32_t)__ldg(src + n0 + 2 * i + 1) : 0u;
+      mk[i] = lo | (hi << 16);
+    }
+  }
+}
+template <typename InT> __device__ __forceinline__ float2 unpack2(uint32_t u);
+template <> __device__ __forceinline__ float2 unpack2<__nv_bfloat16>(uint32_t u) {
+  return make_float2(__uint_as_float(u << 16), __uint_as_float(u & 0xffff0000u));
+}
+template <> __device__ __forceinline__ float2 unpack2<__half>(uint32_t u) {
+  return __half22float2(*reinterpret_cast<const __half2*>(&u));
+}
+// Lowest finite value of the attention dtype: a mask entry below it (or a NaN) hides the key.
+template <typename InT> __device__ __forceinline__ float mask_floor();
+template <> __device__ __forceinline__ float mask_floor<__nv_bfloat16>() { return -3.3895313892515355e38f; }
+template <> __device__ __forceinline__ float mask_floor<__half>() { return -65504.f; }
+
+template <typename InT, int D, bool MASK>
 __global__ void __launch_bounds__(kThreads, 1)
 sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                const __grid_constant__ CUtensorMap map_v, const TcParams p) {
@@ -592,11 +630,16 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         const int rr = s.mt * kRowsM + row;          // row inside the (b, kvh) group
         const int tok = rr & 15;                     // draft token index of this row
         const int last_visible = s.n_keys - 16 + tok;
+        const InT* mrow = nullptr;                   // this row of the additive mask [B, Hq, 16, N]
+        if (MASK && rr < p.R)
+          mrow = reinterpret_cast<const InT*>(a.mask) + ((((long long)s.b * a.Hq + (long long)s.kvh * p.G + (rr >> 4)) * 16) + tok) * (long long)a.N;
         float m_ref = -INFINITY;                     // reference maximum (raw score units), same in both halves
         float l_sum = 0.f;                           // this half's share of the row sum
         for (int jj = 0; ok && jj < ntiles; ++jj) {
           const uint32_t t = tile_ctr + jj, buf = t & 1;
           const int j = s.tile_lo + jj;
+          uint32_t mk[32];
+          if constexpr (MASK) load_mask64<InT>(mrow, j * kBlockN + half * 64, a.N, p.mask_vec != 0, mk);   // in flight while S is computed
           {
             TR_T0();
             ok = wait_or_abort(&bars[SL::b_s_full + buf], (t >> 1) & 1, abort_flag, p.status);
@@ -611,6 +654,18 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
           ptx::tmem_ld32(s_addr + half * 64 + 32, sr[1]);
           ptx::tmem_ld_wait();
           const int n_base = j * kBlockN + half * 64;
+          if constexpr (MASK) {
+            // softmax(scale * (s + mask / scale)): the mask joins the raw scores; an entry below the dtype's
+            // lowest finite value (or a NaN) hides the key
+#pragma unroll
+            for (int q2 = 0; q2 < 2; ++q2)
+#pragma unroll
+              for (int i = 0; i < 32; i += 2) {
+                const float2 mv = unpack2<InT>(mk[q2 * 16 + (i >> 1)]);
+                sr[q2][i] = __float_as_uint(mv.x >= mask_floor<InT>() ? fmaf(mv.x, p.inv_scale, __uint_as_float(sr[q2][i])) : -INFINITY);
+                sr[q2][i + 1] = __float_as_uint(mv.y >= mask_floor<InT>() ? fmaf(mv.y, p.inv_scale, __uint_as_float(sr[q2][i + 1])) : -INFINITY);
+              }
+          }
           if (n_base + 63 > s.n_keys - 16) {        // this half touches the block keys or the end
 #pragma unroll
             for (int q2 = 0; q2 < 2; ++q2)
@@ -1041,7 +1096,7 @@ unsigned long long next_epoch() {
   return e ? e : counter.fetch_add(1);
 }
 
-template <typename InT, int D>
+template <typename InT, int D, bool MASK>
 int32_t launch_typed(const SdpaArgs& a, cudaStream_t stream) {
   using SL = Smem<D>;
   EncodeTiledFn encode = tensor_map_encoder();
@@ -1062,6 +1117,8 @@ int32_t launch_typed(const SdpaArgs& a, cudaStream_t stream) {
   const long long tiles_per_unit = (a.N + kBlockN - 1) / kBlockN;
   p.total_tiles = tiles_per_unit * p.units;
   p.scale_log2 = a.scale * 1.4426950408889634f;
+  p.inv_scale = 1.f / a.scale;
+  p.mask_vec = (a.mask && (reinterpret_cast<uintptr_t>(a.mask) & 15u) == 0 && a.N % 8 == 0) ? 1 : 0;
   p.status = status;
   const int n_sm = sm_count();
   long long grid = p.total_tiles < n_sm ? p.total_tiles : n_sm;   // upper bound also for ragged lengths
@@ -1129,7 +1186,7 @@ int32_t launch_typed(const SdpaArgs& a, cudaStream_t stream) {
   if (r == CUDA_SUCCESS) r = encode_kv(&mv, a.v);
   if (r != CUDA_SUCCESS) { set_error("cuTensorMapEncodeTiled(k/v) failed with CUresult %d", (int)r); return DFLASH_ERR_CUDA; }
 
-  auto kernel = sdpa_tc_kernel<InT, D>;
+  auto kernel = sdpa_tc_kernel<InT, D, MASK>;
   DFLASH_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SL::alloc));
   if (p.pair) {
     cudaLaunchConfig_t cfg = {};
@@ -1168,7 +1225,6 @@ size_t sdpa_workspace_bytes(int B, int Hq, int Hkv, int D, int N) {
 }
 
 bool sdpa_tc_supported(const SdpaArgs& a) {
-  if (a.mask) return false;                          // additive masks take the general path
   if (a.D != 128 && a.D != 256) return false;
   if (a.dtype != DFLASH_BF16 && a.dtype != DFLASH_F16) return false;
   if (a.kv_len && a.B > 4096) return false;
@@ -1177,9 +1233,14 @@ bool sdpa_tc_supported(const SdpaArgs& a) {
   return true;
 }
 
+template <typename InT, int D>
+static int32_t launch_dims(const SdpaArgs& a, cudaStream_t stream) {
+  return a.mask ? launch_typed<InT, D, true>(a, stream) : launch_typed<InT, D, false>(a, stream);
+}
+
 int32_t launch_sdpa_tc(const SdpaArgs& a, cudaStream_t stream) {
-  if (a.dtype == DFLASH_BF16) return a.D == 256 ? launch_typed<__nv_bfloat16, 256>(a, stream) : launch_typed<__nv_bfloat16, 128>(a, stream);
-  return a.D == 256 ? launch_typed<__half, 256>(a, stream) : launch_typed<__half, 128>(a, stream);
+  if (a.dtype == DFLASH_BF16) return a.D == 256 ? launch_dims<__nv_bfloat16, 256>(a, stream) : launch_dims<__nv_bfloat16, 128>(a, stream);
+  return a.D == 256 ? launch_dims<__half, 256>(a, stream) : launch_dims<__half, 128>(a, stream);
 }
 
 }  // namespace dflash

@@ -127,6 +127,55 @@ def test_additive_mask():
     assert np.abs(out - want).max() < ATOL
 
 
+MASK_CASES = [
+    # B, Hq, Hkv, N (incl. the 16 block keys), D, dtype
+    (2, 16, 2, 16 + 1000, 256, "bf16"),       # mask rows read 16 bytes at a time (N a multiple of 8)
+    (3, 8, 2, 16 + 77, 128, "bf16"),          # N = 93: element-wise mask reads, ragged tile edge
+    (1, 16, 1, 16 + 519, 256, "fp16"),        # GQA 16 (two query tiles per KV head), odd N, fp16 floor
+    (32, 16, 2, 16 + 600, 256, "bf16"),       # cluster pairs
+    (20, 16, 2, 16 + 696, 256, "bf16"),       # three equal cuts, merged by the last finisher
+    (80, 8, 2, 16 + 304, 128, "fp16"),        # stream-K ranges
+]
+
+
+def _random_mask(shape, dtype, seed):
+    """Mostly zeros, some finite biases, some hidden keys; values rounded to the attention dtype as the API does."""
+    rng = np.random.default_rng(seed)
+    m = np.where(rng.random(shape) < 0.3, rng.standard_normal(shape) * 2.0, 0.0).astype(np.float32)
+    m[rng.random(shape) < 0.2] = -np.inf
+    m[rng.random(shape) < 0.02] = -1e9 if dtype == "bf16" else -65504.0        # the usual "large negative" fill: finite, not hidden
+    return torch.from_numpy(m).to(TORCH_DT[dtype]).float().numpy()
+
+
+@pytest.mark.parametrize("case", MASK_CASES, ids=lambda c: "x".join(map(str, c)))
+def test_additive_mask_on_the_tensor_core_path(case):
+    B, Hq, Hkv, N, D, dtype = case
+    x = O.make_sdpa_inputs(B, Hq, Hkv, N, D, 1300 + B + N, dtype)
+    mask = _random_mask((B, Hq, 16, N), dtype, 77 + N)
+    mask[0, 1, 3, :] = -np.inf                                                   # a row with no visible key: zeros out
+    mask[0, 0, 15, N - 1] = -np.inf                                              # a token that may not see itself
+    launches0 = K().launch_count()
+    out = run(x, dtype, mask=dev(mask)).float().cpu().numpy()
+    assert K().launch_count() - launches0 <= 2                                   # the tensor-core kernel (and at most its merge)
+    want = O.verify_sdpa(x["q"], x["k"], x["v"], x["scale"], mask=mask, in_dtype=dtype)
+    assert np.abs(out - want).max() < ATOL
+    assert not out[0, 1, 3].any()
+    # an all-zero mask changes nothing, bit for bit
+    plain = run(x, dtype)
+    zero = run(x, dtype, mask=torch.zeros(B, Hq, 16, N, device="cuda"))
+    assert torch.equal(plain, zero)
+
+
+def test_additive_mask_with_ragged_lengths():
+    B, Hq, Hkv, N, D = 5, 16, 2, 16 + 800, 256
+    x = O.make_sdpa_inputs(B, Hq, Hkv, N, D, 1402, "bf16")
+    lens = np.array([N, 16, 16 + 129, 16 + 500, 16 + 37], np.int32)
+    mask = _random_mask((B, Hq, 16, N), "bf16", 5)
+    out = run(x, "bf16", mask=dev(mask), kv_len=dev(lens)).float().cpu().numpy()
+    want = O.verify_sdpa(x["q"], x["k"], x["v"], x["scale"], mask=mask, kv_len=lens)
+    assert np.abs(out - want).max() < ATOL
+
+
 def test_out_of_contract_shapes_return_none():
     q = torch.zeros(1, 16, 8, 256, dtype=torch.bfloat16, device="cuda")
     k = torch.zeros(1, 2, 64, 256, dtype=torch.bfloat16, device="cuda")
