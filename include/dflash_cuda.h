@@ -30,7 +30,9 @@ typedef enum {
   DFLASH_ERR_UNSUPPORTED = -2,   /* shape or dtype outside the supported set (the reference returns nil / falls back) */
   DFLASH_ERR_CUDA = -3,          /* a CUDA runtime or driver call failed; see dflash_last_error_string() */
   DFLASH_ERR_WORKSPACE = -4,     /* workspace missing or smaller than *_workspace_bytes() */
-  DFLASH_ERR_DEVICE_TIMEOUT = -5 /* a bounded device-side wait gave up (reported by dflash_device_status) */
+  DFLASH_ERR_DEVICE_TIMEOUT = -5, /* a bounded device-side wait gave up (reported by dflash_device_status) */
+  DFLASH_ERR_DEVICE_DATA = -6     /* a kernel found device-resident data out of range, e.g. a KV position beyond the
+                                     cache's capacity (reported by dflash_device_status) */
 } dflash_status;
 
 typedef enum { DFLASH_F32 = 0, DFLASH_BF16 = 1, DFLASH_F16 = 2, DFLASH_U8 = 3 } dflash_dtype;
@@ -172,6 +174,31 @@ int32_t dflash_accept_lengths(const uint32_t* posterior, const int32_t* verify_i
 int32_t dflash_rebuild_conv_state(const void* conv_snapshot, const void* qkv, const int32_t* steps_per_seq,
                                   int32_t steps_all, void* out, int32_t B, int32_t T, int32_t keep,
                                   int64_t row_bytes, int32_t* rows_out, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * KV cache maintenance around the verify attention, without the accepted count on the host.
+ * Replaces the cache update of the target forward and the trim of restoreAfterAcceptance,
+ * Sources/DFlash/DFlashRuntime.swift:188-223 (targetLen = start + accepted inputs;
+ * cache.trim(offset - targetLen)).
+ * dflash_kv_append writes the block's rows k_new / v_new [B,Hkv,T,D] (dtype) behind the committed
+ * tokens: row t of sequence b goes to position kv_len[b] + t (kv_len == NULL: len_all + t) of
+ *   a dense cache  [B,Hkv,capacity,D]                       (page_table == NULL), or
+ *   a paged pool   [num_pages,Hkv,page_tokens,D] through page_table int32[B,max_pages]
+ *   (the layout dflash_verify_sdpa reads).
+ * kv_len_out (int32[B] or NULL, not the same array as kv_len) receives kv_len[b] + T, the length
+ * the verify attention must be given.  A position beyond the capacity, or on a page that is
+ * negative or >= num_pages, is skipped and dflash_device_status then returns
+ * DFLASH_ERR_DEVICE_DATA.
+ * dflash_kv_commit: kv_len[b] += clamp(commit[b], 0, T) with commit = replay_len of
+ * dflash_accept_lengths (accepted drafts + 1).  Rejected rows stay in place and are overwritten
+ * by the next block: the trim.
+ */
+int32_t dflash_kv_append(const void* k_new, const void* v_new, void* k_cache, void* v_cache,
+                         const int32_t* page_table, const int32_t* kv_len, int32_t len_all,
+                         int32_t* kv_len_out, int32_t B, int32_t Hkv, int32_t T, int32_t D,
+                         int32_t capacity, int32_t page_tokens, int32_t max_pages, int32_t num_pages,
+                         int32_t dtype, void* stream);
+int32_t dflash_kv_commit(int32_t* kv_len, const int32_t* commit, int32_t B, int32_t T, void* stream);
 
 /* ---------------------------------------------------------------------------------------------
  * TurboQuant 3-bit KV codec, 128-dimension blocks (a 256-dimension head vector is two blocks).

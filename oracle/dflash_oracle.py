@@ -256,6 +256,42 @@ def accept_block(verify_ids, posterior):
     return accept, 1 + accept, int(posterior[accept])
 
 
+class TrimmableKVCache:
+    """The attention cache as the verify cycle uses it: one growing [Hkv, n, D] history per sequence.
+
+    update() is the append of the target forward over the block; restore() follows
+    restoreTargetCacheAfterAcceptance, Sources/DFlash/DFlashRuntime.swift:188-223, for a trimmable
+    cache: offset > targetLen => trim(offset - targetLen), with targetLen = start + accepted
+    inputs.  Per-sequence lengths (the reference runs B = 1)."""
+
+    def __init__(self, batch: int, kv_heads: int, head_dim: int, dtype=np.float32):
+        self.k = [np.zeros((kv_heads, 0, head_dim), dtype) for _ in range(batch)]
+        self.v = [np.zeros((kv_heads, 0, head_dim), dtype) for _ in range(batch)]
+
+    def offset(self, b: int) -> int:
+        return self.k[b].shape[1]
+
+    def update(self, k_new, v_new):
+        """k_new, v_new [B,Hkv,T,D]: appended behind every sequence's history."""
+        for b in range(len(self.k)):
+            self.k[b] = np.concatenate([self.k[b], np.asarray(k_new[b], self.k[b].dtype)], axis=1)
+            self.v[b] = np.concatenate([self.v[b], np.asarray(v_new[b], self.v[b].dtype)], axis=1)
+
+    def trim(self, b: int, n: int) -> int:
+        n = min(self.offset(b), max(0, int(n)))
+        keep = self.offset(b) - n
+        self.k[b] = self.k[b][:, :keep]
+        self.v[b] = self.v[b][:, :keep]
+        return n
+
+    def restore(self, start_lens, accepted_inputs):
+        """After verification: sequence b keeps start_lens[b] + accepted_inputs[b] rows (:212-218)."""
+        for b in range(len(self.k)):
+            target_len = int(start_lens[b]) + int(accepted_inputs[b])
+            if self.offset(b) > target_len:
+                self.trim(b, self.offset(b) - target_len)
+
+
 # --------------------------------------------------------------------------------------------
 # Block-verify SDPA
 # --------------------------------------------------------------------------------------------

@@ -13,7 +13,7 @@ LIB_PATH = os.environ.get("DFLASH_CUDA_LIB") or os.path.join(_PKG, "lib", "libdf
 
 F32, BF16, F16, U8 = 0, 1, 2, 3
 KV_DENSE, KV_TURBO3 = 0, 1
-OK, ERR_INVALID_ARG, ERR_UNSUPPORTED, ERR_CUDA, ERR_WORKSPACE, ERR_DEVICE_TIMEOUT = 0, -1, -2, -3, -4, -5
+OK, ERR_INVALID_ARG, ERR_UNSUPPORTED, ERR_CUDA, ERR_WORKSPACE, ERR_DEVICE_TIMEOUT, ERR_DEVICE_DATA = 0, -1, -2, -3, -4, -5, -6
 
 _vp, _i32, _u64, _sz, _f32 = C.c_void_p, C.c_int32, C.c_uint64, C.c_size_t, C.c_float
 
@@ -28,6 +28,8 @@ SIGNATURES = {
     "dflash_greedy_tokens": (_i32, [_vp, _vp, _vp, _i32, _i32, _i32, _vp]),
     "dflash_accept_lengths": (_i32, [_vp] * 5 + [_i32, _i32, _vp]),
     "dflash_rebuild_conv_state": (_i32, [_vp, _vp, _vp, _i32, _vp, _i32, _i32, _i32, C.c_int64, C.POINTER(_i32), _vp]),
+    "dflash_kv_append": (_i32, [_vp] * 6 + [_i32, _vp] + [_i32] * 9 + [_vp]),
+    "dflash_kv_commit": (_i32, [_vp, _vp, _i32, _i32, _vp]),
     "dflash_turbo_encode": (_i32, [_vp] * 5 + [C.c_int64, _i32, _i32, _vp]),
     "dflash_turbo_decode": (_i32, [_vp] * 5 + [C.c_int64, _i32, _i32, _vp]),
     "dflash_partition_plan": (_i32, [_i32, _i32, C.POINTER(_i32)]),

@@ -268,6 +268,10 @@ int32_t dflash_device_status(void* stream) {
   if (host != 0) {
     DFLASH_CUDA_CHECK(cudaMemsetAsync(word, 0, sizeof(int), s));
     DFLASH_CUDA_CHECK(cudaStreamSynchronize(s));
+    if (host == 16) {   // kStatusKvRange, kv_cache.cu
+      set_error("kv_append skipped a row: position beyond the cache's capacity or on an unmapped page");
+      return DFLASH_ERR_DEVICE_DATA;
+    }
     set_error("a device-side bounded wait gave up (code %d)", host);
     return DFLASH_ERR_DEVICE_TIMEOUT;
   }

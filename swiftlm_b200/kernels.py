@@ -223,6 +223,27 @@ def launch_count() -> int:
     return int(_lib.lib().dflash_launch_count())
 
 
+def kv_append(k_new, v_new, k_cache, v_cache, kv_len=None, len_all: int = 0, page_table=None, kv_len_out=None) -> None:
+    """Writes the block's rows k_new / v_new [B,Hkv,T,D] behind the committed tokens of a dense cache [B,Hkv,capacity,D]
+    or, with page_table int32[B,max_pages], of a page pool [pages,Hkv,page_tokens,D]: row t of sequence b lands at
+    position kv_len[b] + t (len_all + t without kv_len).  kv_len_out receives kv_len + T, the length the verify
+    attention sees.  Replaces the cache update before the target forward (Sources/DFlash/DFlashRuntime.swift:188-223)."""
+    B, Hkv, T, D = k_new.shape
+    if page_table is not None:
+        num_pages, page_tokens, max_pages, capacity = k_cache.shape[0], k_cache.shape[2], page_table.shape[1], 0
+    else:
+        num_pages, page_tokens, max_pages, capacity = 0, 0, 0, k_cache.shape[2]
+    _lib.check(_lib.lib().dflash_kv_append(
+        _ptr(k_new), _ptr(v_new), _ptr(k_cache), _ptr(v_cache), _ptr(page_table), _ptr(kv_len), int(len_all),
+        _ptr(kv_len_out), B, Hkv, T, D, capacity, page_tokens, max_pages, num_pages, _DT[k_new.dtype], _stream()))
+
+
+def kv_commit(kv_len, commit, block: int = 16) -> None:
+    """kv_len[b] += clamp(commit[b], 0, block): keeps the accepted prefix of the block just appended and
+    leaves the rejected rows to be overwritten (the reference's cache.trim(offset - targetLen))."""
+    _lib.check(_lib.lib().dflash_kv_commit(_ptr(kv_len), _ptr(commit), kv_len.numel(), int(block), _stream()))
+
+
 def gated_delta_into(q, k, v, g, beta, state, n_per_seq, y, state_out, tape=None, mask=None) -> None:
     """Allocation-free form of gated_delta_kernel_with_tape: every buffer is supplied by the
     caller (contiguous, on the current device, dtypes as documented there).  state_out may be

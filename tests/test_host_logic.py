@@ -82,3 +82,36 @@ def test_sequence_sharded_step_with_gloo_all_gather(tmp_path, n_seq):
     port = _free_port()
     mp.spawn(_gloo_worker, args=(world, port, n_seq, str(tmp_path)), nprocs=world, join=True)
     assert all(os.path.exists(tmp_path / f"ok{r}") for r in range(world))
+
+
+def test_paged_kv_cache_page_bookkeeping_on_the_host():
+    """Page hand-out, table rows and return of unreachable pages (no kernel runs: CPU tensors)."""
+    from swiftlm_b200.kv_cache import KVCacheFull, PagedKVCache
+    c = PagedKVCache(2, 1, 8, 16, num_pages=5, max_pages=3, device="cpu")
+    c.reserve(0, 17)
+    c.reserve(1, 48)
+    assert c.pages_of(0) == [0, 1] and c.pages_of(1) == [2, 3, 4] and c.free_pages == 0
+    with pytest.raises(KVCacheFull):
+        c.reserve(0, 49)                       # a fourth page does not fit the table
+    with pytest.raises(KVCacheFull):
+        c.reserve(0, 33)                       # a third page would, but the pool is empty
+    c._shrink(1, 16)
+    assert c.pages_of(1) == [2] and c.free_pages == 2
+    assert c._table_host.tolist() == [[0, 1, -1], [2, -1, -1]]
+    c.reserve(0, 48)
+    assert len(c.pages_of(0)) == 3 and c.free_pages == 1
+    assert len({*c.pages_of(0), *c.pages_of(1)}) == 4
+
+
+def test_oracle_trimmable_cache_follows_the_restore_rule():
+    from oracle import dflash_oracle as O
+    ref = O.TrimmableKVCache(2, 1, 4)
+    blk = np.arange(2 * 1 * 16 * 4, dtype=np.float32).reshape(2, 1, 16, 4)
+    ref.update(blk, -blk)
+    ref.restore([0, 0], [5, 16])               # targetLen = start + accepted inputs
+    assert ref.offset(0) == 5 and ref.offset(1) == 16
+    ref.update(blk, -blk)
+    ref.restore([5, 16], [1, 9])
+    assert ref.offset(0) == 6 and ref.offset(1) == 25
+    np.testing.assert_array_equal(ref.k[0][0, 5], blk[0, 0, 0])       # the new block starts right behind the kept prefix
+    np.testing.assert_array_equal(ref.v[1][0, 24], -blk[1, 0, 8])
