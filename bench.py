@@ -541,6 +541,17 @@ def run_case(args):
         units = cfg["B_seq"] * cfg["L"] * cfg["Hv"]
         info = {"case": args.case, "head_states": units,
                 "algorithmic_bytes_per_launch": units * 131072.0 + 642.0 * float(x["n"].sum().item()) * cfg["Hv"]}
+    elif args.case in ("turbo_decode_k_small", "turbo_decode_v_small"):
+        # a quarter of one attention layer of configs[4]: 16 sequences x 2 KV heads x 8192 tokens x 256 dims
+        is_key = args.case == "turbo_decode_k_small"
+        g = torch.Generator(device=device).manual_seed(SEED + 4000)
+        kv = torch.randn(16, 2, 8192, 256, device=device, generator=g).bfloat16()
+        packed, signs, norm, rnorm = kernels.turbo_encode(kv, is_key)
+        dec = torch.empty_like(kv)
+        for _ in range(args.warmup + args.steps):
+            kernels.turbo_decode_into(packed, signs, norm, rnorm, dec)
+        blocks = kv.numel() // 128
+        info = {"case": args.case, "blocks": blocks, "algorithmic_bytes_per_launch": blocks * ((68 if is_key else 50) + 256)}
     else:
         cfg = CFG2
         g = torch.Generator(device=device).manual_seed(SEED + 2000)
@@ -562,7 +573,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--case", default=None, choices=["replay_small", "delta_replay_small", "sdpa_small"],
+    ap.add_argument("--case", default=None, choices=["replay_small", "delta_replay_small", "sdpa_small", "turbo_decode_k_small", "turbo_decode_v_small"],
                     help="run one small single-kernel case (for profiler captures) instead of the benchmark")
     args = ap.parse_args()
     if args.case:
