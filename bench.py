@@ -334,6 +334,7 @@ def run_gpu(args):
             out = {"error": "failed on another rank"}
         return out
 
+    variants = guarded(lambda: run_replay_variants(torch, kernels, device, x, y, state_out, heads, n_sum_heads, peaks, max_over_ranks))
     sd_long = guarded(lambda: run_sdpa_long(torch, kernels, device, rank, world, peaks, max_over_ranks))
     # ---- the composed verify step, configs[4]: 64 sequences sharded by sequence over the ranks ----
     del x
@@ -376,12 +377,55 @@ def run_gpu(args):
         "gpu_launches": launches,
         "clocks": clocks,
         "sdpa": sd,
+        "replay_variants": variants,
         "sdpa_long": sd_long,
         "verify_step": vstep,
     }
     print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
+
+
+def run_replay_variants(torch, kernels, device, x, y, state_out, heads, n_sum_heads, peaks, max_over_ranks):
+    """The other variants of the replay kernels on configs[1] (rank-local, same inputs as the headline): the delta-tape
+    replay, a [B,T] step mask instead of lengths, and the per-channel gate [B,T,Hv,Dk] (forward and delta-tape replay).
+    Times are CUDA-event means over 5 calls after 3 warm-up calls; bytes are the algorithmic bytes of each variant."""
+    B, T, Hv, D = x["v"].shape
+    gen = torch.Generator(device=device).manual_seed(SEED + 1500)
+    tape = torch.empty(B, T, Hv, D, device=device)
+    kernels.gated_delta_into(x["q"], x["k"], x["v"], x["g"], x["beta"], x["state"], None, y, state_out, tape=tape)
+    mask = (torch.arange(T, device=device)[None, :] < x["n"][:, None]).to(torch.bfloat16)       # the same steps as n
+    g_vec = torch.exp(-torch.nn.functional.softplus(torch.randn(B, T, Hv, D, device=device, generator=gen))).bfloat16()
+    step_bytes = 256 + 128 + 128 + 2 + 2 + 256           # v, k share, q share, beta, g, y (bf16 inputs)
+    tape_bytes = 512 + 128 + 2                            # recorded delta (fp32), k share, g
+    cases = {
+        "delta_tape_replay": (lambda: kernels.tape_replay_into(tape, x["k"], x["g"], x["state"], x["n"], state_out),
+                              heads * 131072.0 + tape_bytes * n_sum_heads),
+        "forward_step_mask": (lambda: kernels.gated_delta_into(x["q"], x["k"], x["v"], x["g"], x["beta"], x["state"], None, y,
+                                                               state_out, mask=mask),
+                              heads * 131072.0 + step_bytes * n_sum_heads),
+        "forward_vector_gate": (lambda: kernels.gated_delta_into(x["q"], x["k"], x["v"], g_vec, x["beta"], x["state"], x["n"], y,
+                                                                 state_out),
+                                heads * 131072.0 + (step_bytes - 2 + 2 * D) * n_sum_heads),
+        "delta_tape_replay_vector_gate": (lambda: kernels.tape_replay_into(tape, x["k"], g_vec, x["state"], x["n"], state_out),
+                                          heads * 131072.0 + (tape_bytes - 2 + 2 * D) * n_sum_heads),
+    }
+    out = {"config": "configs[1] per GPU (73728 head-states, n~U{0..16} per sequence); mean of 5 calls"}
+    for name, (fn, nbytes) in cases.items():
+        for _ in range(3):
+            fn()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(5):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = max_over_ranks(e0.elapsed_time(e1) / 5)
+        gbs = nbytes / (ms * 1e-3) / 1e9
+        out[name] = {"ms": ms, "head_states_per_s_per_gpu": heads / (ms * 1e-3), "gbs": gbs, "frac_of_hbm_peak": gbs / peaks["hbm_gbs"]}
+    kernels.device_status()
+    return out
 
 
 def run_sdpa(torch, kernels, device, args, peaks):

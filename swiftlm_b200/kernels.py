@@ -223,6 +223,17 @@ def launch_count() -> int:
     return int(_lib.lib().dflash_launch_count())
 
 
+def tape_replay_into(tape, k, g, state, n_per_seq, state_out, mask=None) -> None:
+    """Allocation-free form of tape_replay_kernel: every buffer is supplied by the caller (contiguous, on the current
+    device; tape and state fp32).  state_out may be the same tensor as state."""
+    B, T, Hv, Dv = tape.shape
+    Hk, Dk = k.shape[2], k.shape[3]
+    mask_t, mdt = _mask_arg(mask)
+    _lib.check(_lib.lib().dflash_tape_replay(
+        _ptr(tape), _ptr(k), _ptr(g), _ptr(state), _ptr(mask_t), _ptr(n_per_seq), _ptr(state_out),
+        B, T, Hk, Hv, Dk, Dv, int(g.dim() == 4), _DT[k.dtype], mdt, _stream()))
+
+
 def kv_append(k_new, v_new, k_cache, v_cache, kv_len=None, len_all: int = 0, page_table=None, kv_len_out=None) -> None:
     """Writes the block's rows k_new / v_new [B,Hkv,T,D] behind the committed tokens of a dense cache [B,Hkv,capacity,D]
     or, with page_table int32[B,max_pages], of a page pool [pages,Hkv,page_tokens,D]: row t of sequence b lands at
