@@ -5,6 +5,7 @@
 //                                          (gatedDeltaKernelWithTape), :737 (batchedSDPA2Pass)
 //   dflash::host::RecurrentRollbackCache   Sources/DFlash/RecurrentRollbackCache.swift:34-182
 //   dflash::host::restoreAfterAcceptance   Sources/DFlash/DFlashRuntime.swift:188-223
+//   dflash::host::PagedKVCache             the attention cache's update and trim around the verify pass, :188-223
 //   dflash::host::partitionPlan            (no counterpart: one process per GPU)
 //
 // Same names, argument meaning and error behaviour: batchedSDPA2Pass returns an empty optional where
@@ -244,6 +245,118 @@ inline void restoreAfterAcceptance(std::vector<RecurrentRollbackCache*>& caches,
     else c->rollback(acceptanceLength, stream);
   }
 }
+
+// ---- attention KV cache around the verify pass ---------------------------------------------------
+// The cache update of the target forward and the trim of restoreTargetCacheAfterAcceptance
+// (Sources/DFlash/DFlashRuntime.swift:188-223) for a cache whose rows live in a page pool
+// [pages, Hkv, pageTokens, D] (the layout batchedSDPA2Pass reads through a page table).  Committed lengths
+// stay on the device: appendBlock -> attend -> commit never reads the accepted count.  Pages are handed out
+// on the host from an upper bound of every sequence's length; sync() reads the true lengths, tightens the
+// bounds and returns unreachable pages.  attend() needs pageTokens to be a multiple of 128.
+class PagedKVCache {
+ public:
+  PagedKVCache(int32_t batch, int32_t kvHeads, int32_t headDim, int32_t pageTokens, int32_t numPages, int32_t maxPages,
+               DType dtype = DType::BF16)
+      : B_(batch), Hkv_(kvHeads), D_(headDim), pageTokens_(pageTokens), numPages_(numPages), maxPages_(maxPages), dtype_(dtype),
+        tableHost_((size_t)batch * maxPages, -1), pages_(batch), upper_(batch, 0) {
+    kPool = Tensor::empty({numPages, kvHeads, pageTokens, headDim}, dtype);
+    vPool = Tensor::empty({numPages, kvHeads, pageTokens, headDim}, dtype);
+    checkCuda(cudaMemset(kPool.data(), 0, kPool.nbytes()));
+    checkCuda(cudaMemset(vPool.data(), 0, vPool.nbytes()));
+    pageTable = Tensor::fromHost(tableHost_.data(), {batch, maxPages}, DType::I32);
+    std::vector<int32_t> zeros(batch, 0);
+    kvLen = Tensor::fromHost(zeros.data(), {batch}, DType::I32);
+    kvLenBlock = Tensor::fromHost(zeros.data(), {batch}, DType::I32);
+    for (int32_t p = numPages - 1; p >= 0; --p) free_.push_back(p);   // page 0 is handed out first
+  }
+  int32_t freePages() const { return (int32_t)free_.size(); }
+  const std::vector<int32_t>& pagesOf(int32_t b) const { return pages_.at(b); }
+
+  // Makes positions [0, tokens) of sequence b addressable; throws Error(DFLASH_ERR_WORKSPACE) when the pool or the table is full.
+  void reserve(int32_t b, int64_t tokens) {
+    const int64_t need = (tokens + pageTokens_ - 1) / pageTokens_;
+    if (need > maxPages_) throw Error(DFLASH_ERR_WORKSPACE, "PagedKVCache: sequence needs more pages than its table holds");
+    while ((int64_t)pages_[b].size() < need) {
+      if (free_.empty()) throw Error(DFLASH_ERR_WORKSPACE, "PagedKVCache: page pool exhausted");
+      const int32_t page = free_.back();
+      free_.pop_back();
+      tableHost_[(size_t)b * maxPages_ + pages_[b].size()] = page;
+      pages_[b].push_back(page);
+      dirty_ = true;
+    }
+  }
+  // kNew, vNew [B,Hkv,T,D]: row t of sequence b goes to position kvLen[b] + t.  Returns the lengths including the block.
+  const Tensor& appendBlock(const Tensor& kNew, const Tensor& vNew, cudaStream_t stream = nullptr) {
+    const int32_t T = (int32_t)kNew.dim(2);
+    for (int32_t b = 0; b < B_; ++b) reserve(b, upper_[b] + T);
+    flushTable(stream);
+    check(dflash_kv_append(kNew.data(), vNew.data(), kPool.data(), vPool.data(), static_cast<const int32_t*>(pageTable.data()),
+                           static_cast<const int32_t*>(kvLen.data()), 0, static_cast<int32_t*>(kvLenBlock.data()), B_, Hkv_, T, D_, 0,
+                           pageTokens_, maxPages_, numPages_, (int32_t)dtype_, stream));
+    appended_ = T;
+    return kvLenBlock;
+  }
+  // Block-verify attention of queries [B,Hq,16,D] over the committed tokens and the block just appended.
+  std::optional<Tensor> attend(const Tensor& queries, float scale, cudaStream_t stream = nullptr) {
+    const int32_t Hq = (int32_t)queries.dim(1);
+    int64_t nMax = 0;
+    for (int64_t u : upper_) nMax = u > nMax ? u : nMax;
+    nMax += appended_;
+    if (nMax > (int64_t)maxPages_ * pageTokens_) nMax = (int64_t)maxPages_ * pageTokens_;
+    const size_t need = dflash_verify_sdpa_workspace_bytes(B_, Hq, Hkv_, D_, (int32_t)nMax);
+    if (!ws_.defined() || ws_.nbytes() < need) ws_ = Tensor::empty({(int64_t)need}, DType::U8);
+    Tensor out = Tensor::empty(queries.shape(), queries.dtype());
+    const int32_t st = dflash_verify_sdpa(queries.data(), kPool.data(), vPool.data(), static_cast<const int32_t*>(pageTable.data()),
+                                          static_cast<const int32_t*>(kvLenBlock.data()), nullptr, out.data(), ws_.data(), ws_.nbytes(),
+                                          B_, Hq, Hkv_, 16, D_, (int32_t)nMax, pageTokens_, maxPages_, scale, (int32_t)queries.dtype(),
+                                          DFLASH_KV_DENSE, stream);
+    if (st == DFLASH_ERR_UNSUPPORTED) return std::nullopt;
+    check(st);
+    return out;
+  }
+  // commitCount: device int32[B], accepted drafts + 1 (replay_len of dflash_accept_lengths).
+  void commit(const Tensor& commitCount, cudaStream_t stream = nullptr) {
+    check(dflash_kv_commit(static_cast<int32_t*>(kvLen.data()), static_cast<const int32_t*>(commitCount.data()), B_, appended_, stream));
+    for (int32_t b = 0; b < B_; ++b) upper_[b] += appended_;
+    appended_ = 0;
+  }
+  // Reads the committed lengths, tightens the host bounds and returns the pages beyond them to the pool.
+  std::vector<int32_t> sync(cudaStream_t stream = nullptr) {
+    std::vector<int32_t> lens(B_);
+    kvLen.toHost(lens.data(), stream);
+    for (int32_t b = 0; b < B_; ++b) {
+      upper_[b] = lens[b];
+      const int64_t keep = ((int64_t)lens[b] + pageTokens_ - 1) / pageTokens_;
+      while ((int64_t)pages_[b].size() > keep) {
+        free_.push_back(pages_[b].back());
+        pages_[b].pop_back();
+        tableHost_[(size_t)b * maxPages_ + pages_[b].size()] = -1;
+        dirty_ = true;
+      }
+    }
+    flushTable(stream);
+    return lens;
+  }
+
+  Tensor kPool, vPool, pageTable, kvLen, kvLenBlock;
+
+ private:
+  void flushTable(cudaStream_t stream) {
+    if (!dirty_) return;
+    // pageable source: the copy has read the host table when the call returns, so it may be edited again at once
+    checkCuda(cudaMemcpyAsync(pageTable.data(), tableHost_.data(), tableHost_.size() * sizeof(int32_t), cudaMemcpyHostToDevice, stream));
+    dirty_ = false;
+  }
+  int32_t B_, Hkv_, D_, pageTokens_, numPages_, maxPages_;
+  DType dtype_;
+  std::vector<int32_t> tableHost_;
+  std::vector<std::vector<int32_t>> pages_;
+  std::vector<int64_t> upper_;
+  std::vector<int32_t> free_;
+  Tensor ws_;
+  int32_t appended_ = 0;
+  bool dirty_ = false;
+};
 
 // Contiguous [begin, end) ranges of `units` work units (sequences, or (sequence, KV head) pairs) per GPU.
 inline std::vector<std::pair<int32_t, int32_t>> partitionPlan(int32_t units, int32_t nGpus) {

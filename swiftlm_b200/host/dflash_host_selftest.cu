@@ -2,7 +2,8 @@
 // outside reference: the replay of a recorded tape reproduces the forward state; rollback(n) leaves
 // the state of a forward pass over n + 1 steps and the conv window concat(snapshot, qkv)[n+1 : n+4];
 // the per-sequence rollback agrees with the scalar one; batchedSDPA2Pass returns no value outside
-// its contract and equals the allocation-free entry point inside it.  Exit code 0 = all passed.
+// its contract and equals the allocation-free entry point inside it; the paged KV cache keeps exactly the
+// accepted rows and its attention equals the dense one.  Exit code 0 = all passed.
 #include <cuda_bf16.h>
 
 #include <cmath>
@@ -122,7 +123,74 @@ int main() {
       EXPECT(host<uint16_t>(*out) == host<uint16_t>(o2), "workspace and allocation-free attention agree bitwise");
     }
 
-    // 6. partition plan
+    // 6. paged KV cache: append / attend / commit cycles against a dense history kept on the host
+    {
+      const int KB = 2, KH = 2, KD = 256, PT = 128, NP = 8, MP = 4, KT = 16;
+      PagedKVCache cache(KB, KH, KD, PT, NP, MP);
+      std::vector<std::vector<uint16_t>> histK(KB), histV(KB);      // per sequence: rows [n][KH][KD]
+      const int commits[4][2] = {{16, 3}, {1, 16}, {9, 9}, {16, 2}};
+      bool rowsOk = true, attnOk = true, lensOk = true;
+      for (int cycle = 0; cycle < 4; ++cycle) {
+        Tensor kn = randBf16({KB, KH, KT, KD}, -1.f, 1.f), vn = randBf16({KB, KH, KT, KD}, -1.f, 1.f);
+        Tensor qn = randBf16({KB, 16, 16, KD}, -1.f, 1.f);
+        const std::vector<uint16_t> hk = host<uint16_t>(kn), hv = host<uint16_t>(vn);
+        for (int b = 0; b < KB; ++b)
+          for (int t = 0; t < KT; ++t)
+            for (int h = 0; h < KH; ++h) {
+              const size_t src = (((size_t)b * KH + h) * KT + t) * KD;
+              histK[b].insert(histK[b].end(), hk.begin() + src, hk.begin() + src + KD);
+              histV[b].insert(histV[b].end(), hv.begin() + src, hv.begin() + src + KD);
+            }
+        const Tensor& lensBlk = cache.appendBlock(kn, vn);
+        const std::vector<int32_t> lb = host<int32_t>(lensBlk);
+        for (int b = 0; b < KB; ++b) lensOk = lensOk && lb[b] == (int32_t)(histK[b].size() / (KH * KD));
+        // dense ragged attention over the host history must equal the paged one bit for bit
+        int nMax = 0;
+        for (int b = 0; b < KB; ++b) nMax = lb[b] > nMax ? lb[b] : nMax;
+        std::vector<uint16_t> dk((size_t)KB * KH * nMax * KD, 0), dv(dk.size(), 0);
+        for (int b = 0; b < KB; ++b)
+          for (int n = 0; n < lb[b]; ++n)
+            for (int h = 0; h < KH; ++h) {
+              const size_t dst = (((size_t)b * KH + h) * nMax + n) * KD, src = ((size_t)n * KH + h) * KD;
+              std::memcpy(&dk[dst], &histK[b][src], KD * 2);
+              std::memcpy(&dv[dst], &histV[b][src], KD * 2);
+            }
+        Tensor dkT = Tensor::fromHost(dk.data(), {KB, KH, nMax, KD}, DType::BF16), dvT = Tensor::fromHost(dv.data(), {KB, KH, nMax, KD}, DType::BF16);
+        Tensor dense = Tensor::empty(qn.shape(), DType::BF16);
+        const size_t need = dflash_verify_sdpa_workspace_bytes(KB, 16, KH, KD, nMax);
+        Tensor ws = Tensor::empty({(int64_t)need}, DType::U8);
+        check(dflash_verify_sdpa(qn.data(), dkT.data(), dvT.data(), nullptr, static_cast<const int32_t*>(lensBlk.data()), nullptr, dense.data(),
+                                 ws.data(), ws.nbytes(), KB, 16, KH, 16, KD, nMax, 0, 0, 1.f / 16.f, DFLASH_BF16, DFLASH_KV_DENSE, nullptr));
+        auto paged = cache.attend(qn, 1.f / 16.f);
+        attnOk = attnOk && paged.has_value() && host<uint16_t>(*paged) == host<uint16_t>(dense);
+        // commit: keep accepted + 1 rows of the block
+        const int32_t cc[2] = {commits[cycle][0], commits[cycle][1]};
+        cache.commit(Tensor::fromHost(cc, {KB}, DType::I32));
+        for (int b = 0; b < KB; ++b) {
+          histK[b].resize(histK[b].size() - (size_t)(KT - cc[b]) * KH * KD);
+          histV[b].resize(histV[b].size() - (size_t)(KT - cc[b]) * KH * KD);
+        }
+      }
+      const std::vector<int32_t> lens = cache.sync();
+      const std::vector<uint16_t> pool = host<uint16_t>(cache.kPool);
+      for (int b = 0; b < KB; ++b) {
+        lensOk = lensOk && lens[b] == (int32_t)(histK[b].size() / (KH * KD));
+        lensOk = lensOk && (int)cache.pagesOf(b).size() == (lens[b] + PT - 1) / PT;
+        for (int n = 0; n < lens[b] && rowsOk; ++n)
+          for (int h = 0; h < KH; ++h) {
+            const size_t at = (((size_t)cache.pagesOf(b)[n / PT] * KH + h) * PT + n % PT) * KD;
+            rowsOk = rowsOk && std::memcmp(&pool[at], &histK[b][((size_t)n * KH + h) * KD], KD * 2) == 0;
+          }
+      }
+      EXPECT(lensOk, "paged KV cache: lengths and page counts follow append / commit");
+      EXPECT(rowsOk, "paged KV cache: committed rows equal the host history");
+      EXPECT(attnOk, "paged KV cache: attention over pages equals attention over the dense history bitwise");
+      bool threw = false;
+      try { cache.reserve(0, (int64_t)MP * PT + 1); } catch (const Error&) { threw = true; }
+      EXPECT(threw, "paged KV cache: a sequence longer than its table is refused");
+    }
+
+    // 7. partition plan
     auto plan = partitionPlan(10, 4);
     EXPECT(plan.size() == 4 && plan[0].first == 0 && plan[3].second == 10 && plan[0].second - plan[0].first == 3, "partition plan");
     checkCuda(cudaDeviceSynchronize());
