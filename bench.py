@@ -4,7 +4,7 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
 
 One "step" is one pass of the hot path over one batch of seeded synthetic input: the
-gated-delta tape replay of BASELINE configs[1] (64 sequences x 36 linear-attention layers x 32
+gated-delta tape replay of configs[1] of the benchmark definition (64 sequences x 36 linear-attention layers x 32
 v-heads, Dk = Dv = 128, T = 16, bf16 per-token inputs, fp32 state, per-sequence accepted length
 n ~ U{0..16}).  The headline `value` is replayed head-states per second with all inputs
 resident in HBM; `e2e` is the same metric through the package's host-buffer API (pinned host
