@@ -272,6 +272,10 @@ int32_t dflash_device_status(void* stream) {
       set_error("kv_append skipped a row: position beyond the cache's capacity or on an unmapped page");
       return DFLASH_ERR_DEVICE_DATA;
     }
+    if (host == 6) {
+      set_error("verify_sdpa: a unit was cut into more key ranges than the merge kernel takes; its output is incomplete");
+      return DFLASH_ERR_DEVICE_DATA;
+    }
     set_error("a device-side bounded wait gave up (code %d)", host);
     return DFLASH_ERR_DEVICE_TIMEOUT;
   }

@@ -1018,12 +1018,16 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
 }
 
 // ---- merge of the split-KV partials ----------------------------------------------------------
-// One block per (unit, 16 rows); thread (r, c): row r of the group, D/16 consecutive columns.
+// One block per (unit, 16 rows, 64 columns); the ranges of a unit are summed in slot order.
 template <typename InT, int D>
 __global__ void __launch_bounds__(256) sdpa_tc_merge_kernel(const TcParams p, int n_slots) {
-  __shared__ int s_slots[64];
+  // One CTA combines 16 rows x 64 columns of one unit: thread = (row, one float4 of columns).  A unit has at most one
+  // range per CTA of the main kernel, so kMaxRanges covers every GPU with up to 512 SMs; more is reported, not dropped.
+  constexpr int kMaxRanges = 512;
+  __shared__ int s_slots[kMaxRanges];
+  __shared__ float s_f[kMaxRanges][16];    // per range and row: exp2(m - max), then the same divided by the denominator
   __shared__ int s_count;
-  const int unit = blockIdx.x, rgrp = blockIdx.y;
+  const int unit = blockIdx.x, rgrp = blockIdx.y, cgrp = blockIdx.z;
   // slots of this unit, in slot order (a fixed summation order keeps results bit-reproducible)
   if (threadIdx.x < 32) {
     int count = 0;
@@ -1032,49 +1036,59 @@ __global__ void __launch_bounds__(256) sdpa_tc_merge_kernel(const TcParams p, in
       const bool hit = i < n_slots && p.slot_unit[i] == unit;
       const unsigned m = __ballot_sync(0xffffffffu, hit);
       const int pos = count + __popc(m & ((1u << threadIdx.x) - 1u));
-      if (hit && pos < 64) s_slots[pos] = i;
+      if (hit && pos < kMaxRanges) s_slots[pos] = i;
       count += __popc(m);
     }
-    if (threadIdx.x == 0) s_count = count;
+    if (threadIdx.x == 0) {
+      s_count = count;
+      if (count > kMaxRanges) atomicExch(p.status, 6);
+    }
   }
   __syncthreads();
-  const int cnt = s_count < 64 ? s_count : 64;
+  const int cnt = s_count < kMaxRanges ? s_count : kMaxRanges;
   if (cnt == 0) return;   // the unit was written directly by a CTA that covered all of it
   const SdpaArgs& a = p.a;
   const int per_b = a.Hkv * p.MT;
   const int b = unit / per_b, kvh = (unit / p.MT) % a.Hkv, mt = unit % p.MT;
-  const int r = rgrp * 16 + (threadIdx.x >> 4);          // row of the 128-row tile
+  const int rl = threadIdx.x >> 4;                       // row inside the CTA's 16
+  const int r = rgrp * 16 + rl;                          // row of the 128-row tile
   const int rr = mt * kRowsM + r;
-  if (rr >= p.R) return;
-  constexpr int W = D / 16;
-  const int c0 = (threadIdx.x & 15) * W;
-  float mmax = -INFINITY;
-  for (int i = 0; i < cnt; ++i) mmax = fmaxf(mmax, p.part_m[(long long)s_slots[i] * kRowsM + r]);
-  float acc[W];
-#pragma unroll
-  for (int i = 0; i < W; ++i) acc[i] = 0.f;
-  float den = 0.f;
-  for (int i = 0; i < cnt; ++i) {
-    const long long base = (long long)s_slots[i] * kRowsM + r;
-    const float m = p.part_m[base];
-    const float f = (m == -INFINITY) ? 0.f : exp2f(m - mmax);
-    den += f * p.part_l[base];
-    const float* src = p.part_o + (long long)s_slots[i] * kRowsM * D;
-#pragma unroll
-    for (int q = 0; q < W / 4; ++q) {
-      const float4 v = *reinterpret_cast<const float4*>(src + ((long long)(c0 / 4 + q) * kRowsM + r) * 4);
-      acc[4 * q] += f * v.x; acc[4 * q + 1] += f * v.y; acc[4 * q + 2] += f * v.z; acc[4 * q + 3] += f * v.w;
+  // per-row weights once per CTA: thread (row, j) takes ranges j, j + 16, ...
+  {
+    const int j = threadIdx.x & 15;
+    float mmax = -INFINITY;
+    for (int i = 0; i < cnt; ++i) mmax = fmaxf(mmax, p.part_m[(long long)s_slots[i] * kRowsM + r]);
+    for (int i = j; i < cnt; i += 16) {
+      const float m = p.part_m[(long long)s_slots[i] * kRowsM + r];
+      s_f[i][rl] = (m == -INFINITY) ? 0.f : exp2f(m - mmax);
     }
   }
+  __syncthreads();
+  if (rr >= p.R) return;
+  float den = 0.f;
+  for (int i = 0; i < cnt; ++i) den += s_f[i][rl] * p.part_l[(long long)s_slots[i] * kRowsM + r];   // same order in every thread of the row
   const float inv = den == 0.f ? 1.f : 1.f / den;
-  InT* orow = reinterpret_cast<InT*>(a.out) + ((((long long)b * a.Hq + (long long)kvh * p.G + (rr >> 4)) * 16) + (rr & 15)) * D + c0;
+  const int c4 = cgrp * 16 + (threadIdx.x & 15);         // float4 index inside the row
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  const float* src = p.part_o + ((long long)c4 * kRowsM + r) * 4;
+  int i = 0;
+  for (; i + 4 <= cnt; i += 4) {                          // four independent loads in flight
+    float4 v[4];
 #pragma unroll
-  for (int q = 0; q < W / 8; ++q) {
-    uint32_t w[4];
+    for (int u = 0; u < 4; ++u) v[u] = __ldcg(reinterpret_cast<const float4*>(src + (long long)s_slots[i + u] * kRowsM * D));
 #pragma unroll
-    for (int i = 0; i < 4; ++i) w[i] = pack2<InT>(acc[8 * q + 2 * i] * inv, acc[8 * q + 2 * i + 1] * inv);
-    *reinterpret_cast<uint4*>(orow + 8 * q) = make_uint4(w[0], w[1], w[2], w[3]);
+    for (int u = 0; u < 4; ++u) {
+      const float f = s_f[i + u][rl];
+      acc.x += f * v[u].x; acc.y += f * v[u].y; acc.z += f * v[u].z; acc.w += f * v[u].w;
+    }
   }
+  for (; i < cnt; ++i) {
+    const float4 v = __ldcg(reinterpret_cast<const float4*>(src + (long long)s_slots[i] * kRowsM * D));
+    const float f = s_f[i][rl];
+    acc.x += f * v.x; acc.y += f * v.y; acc.z += f * v.z; acc.w += f * v.w;
+  }
+  InT* orow = reinterpret_cast<InT*>(a.out) + ((((long long)b * a.Hq + (long long)kvh * p.G + (rr >> 4)) * 16) + (rr & 15)) * D + c4 * 4;
+  *reinterpret_cast<uint2*>(orow) = make_uint2(pack2<InT>(acc.x * inv, acc.y * inv), pack2<InT>(acc.z * inv, acc.w * inv));
 }
 
 size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
@@ -1208,7 +1222,7 @@ int32_t launch_typed(const SdpaArgs& a, cudaStream_t stream) {
   DFLASH_LAUNCH_CHECK();
   count_launch();
   if (need_merge_kernel) {
-    sdpa_tc_merge_kernel<InT, D><<<dim3(p.units, kRowsM / 16), 256, 0, stream>>>(p, (int)(2 * grid));
+    sdpa_tc_merge_kernel<InT, D><<<dim3(p.units, kRowsM / 16, D / 64), 256, 0, stream>>>(p, (int)(2 * grid));
     DFLASH_LAUNCH_CHECK();
     count_launch();
   }

@@ -176,6 +176,21 @@ def test_additive_mask_with_ragged_lengths():
     assert np.abs(out - want).max() < ATOL
 
 
+@pytest.mark.parametrize("case", [(1, 16, 2, 16 + 20000, 256), (1, 32, 8, 16 + 30000, 128), (2, 16, 1, 16 + 12000, 256)],
+                         ids=lambda c: "x".join(map(str, c)))
+def test_single_sequence_long_context(case):
+    """One or two sequences with a long history (the reference's own serving shape): a (sequence, KV head) unit is cut
+    into as many key ranges as there are SMs per unit, far more than the in-kernel merge takes, so the merge kernel
+    combines up to one range per SM."""
+    B, Hq, Hkv, N, D = case
+    x = O.make_sdpa_inputs(B, Hq, Hkv, N, D, 1500 + N, "bf16")
+    out = run(x, "bf16").float().cpu().numpy()
+    want = CO.verify_sdpa(x["q"], x["k"], x["v"], x["scale"])
+    assert np.abs(out - want).max() < ATOL
+    again = run(x, "bf16").float().cpu().numpy()
+    np.testing.assert_array_equal(out, again)                   # the merge order is fixed: bitwise repeatable
+
+
 def test_out_of_contract_shapes_return_none():
     q = torch.zeros(1, 16, 8, 256, dtype=torch.bfloat16, device="cuda")
     k = torch.zeros(1, 2, 64, 256, dtype=torch.bfloat16, device="cuda")
