@@ -135,6 +135,7 @@ MASK_CASES = [
     (32, 16, 2, 16 + 600, 256, "bf16"),       # cluster pairs
     (20, 16, 2, 16 + 696, 256, "bf16"),       # three equal cuts, merged by the last finisher
     (80, 8, 2, 16 + 304, 128, "fp16"),        # stream-K ranges
+    (1, 16, 2, 16 + 9000, 256, "bf16"),       # one sequence: a range per SM, combined by the merge kernel
 ]
 
 
