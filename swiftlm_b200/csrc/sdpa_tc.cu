@@ -1018,16 +1018,18 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
 }
 
 // ---- merge of the split-KV partials ----------------------------------------------------------
-// One block per (unit, 16 rows, 64 columns); the ranges of a unit are summed in slot order.
+// One block per (unit, 32 rows, 32 columns); the ranges of a unit are summed in slot order.
 template <typename InT, int D>
 __global__ void __launch_bounds__(256) sdpa_tc_merge_kernel(const TcParams p, int n_slots) {
-  // One CTA combines 16 rows x 64 columns of one unit: thread = (row, one float4 of columns).  A unit has at most one
-  // range per CTA of the main kernel, so kMaxRanges covers every GPU with up to 512 SMs; more is reported, not dropped.
-  constexpr int kMaxRanges = 512;
+  // One CTA combines 32 rows x 8 float4 columns of one unit: lane = row (the partials keep the 128 rows of a float4
+  // column contiguous, so a warp reads 512 contiguous bytes per range), warp = column.  A unit has at most one range
+  // per CTA of the main kernel, so kMaxRanges covers every GPU with up to 320 SMs; more is reported, not dropped.
+  constexpr int kMaxRanges = 320;
   __shared__ int s_slots[kMaxRanges];
-  __shared__ float s_f[kMaxRanges][16];    // per range and row: exp2(m - max), then the same divided by the denominator
+  __shared__ float s_f[kMaxRanges][32];    // per range and row: exp2(m - max over the ranges)
   __shared__ int s_count;
   const int unit = blockIdx.x, rgrp = blockIdx.y, cgrp = blockIdx.z;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   // slots of this unit, in slot order (a fixed summation order keeps results bit-reproducible)
   if (threadIdx.x < 32) {
     int count = 0;
@@ -1050,41 +1052,39 @@ __global__ void __launch_bounds__(256) sdpa_tc_merge_kernel(const TcParams p, in
   const SdpaArgs& a = p.a;
   const int per_b = a.Hkv * p.MT;
   const int b = unit / per_b, kvh = (unit / p.MT) % a.Hkv, mt = unit % p.MT;
-  const int rl = threadIdx.x >> 4;                       // row inside the CTA's 16
-  const int r = rgrp * 16 + rl;                          // row of the 128-row tile
+  const int r = rgrp * 32 + lane;                        // row of the 128-row tile
   const int rr = mt * kRowsM + r;
-  // per-row weights once per CTA: thread (row, j) takes ranges j, j + 16, ...
+  // per-row weights once per CTA: warp w takes ranges w, w + 8, ...
   {
-    const int j = threadIdx.x & 15;
     float mmax = -INFINITY;
     for (int i = 0; i < cnt; ++i) mmax = fmaxf(mmax, p.part_m[(long long)s_slots[i] * kRowsM + r]);
-    for (int i = j; i < cnt; i += 16) {
+    for (int i = warp; i < cnt; i += 8) {
       const float m = p.part_m[(long long)s_slots[i] * kRowsM + r];
-      s_f[i][rl] = (m == -INFINITY) ? 0.f : exp2f(m - mmax);
+      s_f[i][lane] = (m == -INFINITY) ? 0.f : exp2f(m - mmax);
     }
   }
   __syncthreads();
   if (rr >= p.R) return;
   float den = 0.f;
-  for (int i = 0; i < cnt; ++i) den += s_f[i][rl] * p.part_l[(long long)s_slots[i] * kRowsM + r];   // same order in every thread of the row
+  for (int i = 0; i < cnt; ++i) den += s_f[i][lane] * p.part_l[(long long)s_slots[i] * kRowsM + r];   // same order in every warp
   const float inv = den == 0.f ? 1.f : 1.f / den;
-  const int c4 = cgrp * 16 + (threadIdx.x & 15);         // float4 index inside the row
+  const int c4 = cgrp * 8 + warp;                        // float4 index inside the row
   float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
   const float* src = p.part_o + ((long long)c4 * kRowsM + r) * 4;
   int i = 0;
-  for (; i + 4 <= cnt; i += 4) {                          // four independent loads in flight
-    float4 v[4];
+  for (; i + 8 <= cnt; i += 8) {                          // eight independent loads in flight
+    float4 v[8];
 #pragma unroll
-    for (int u = 0; u < 4; ++u) v[u] = __ldcg(reinterpret_cast<const float4*>(src + (long long)s_slots[i + u] * kRowsM * D));
+    for (int u = 0; u < 8; ++u) v[u] = __ldcg(reinterpret_cast<const float4*>(src + (long long)s_slots[i + u] * kRowsM * D));
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      const float f = s_f[i + u][rl];
+    for (int u = 0; u < 8; ++u) {
+      const float f = s_f[i + u][lane];
       acc.x += f * v[u].x; acc.y += f * v[u].y; acc.z += f * v[u].z; acc.w += f * v[u].w;
     }
   }
   for (; i < cnt; ++i) {
     const float4 v = __ldcg(reinterpret_cast<const float4*>(src + (long long)s_slots[i] * kRowsM * D));
-    const float f = s_f[i][rl];
+    const float f = s_f[i][lane];
     acc.x += f * v.x; acc.y += f * v.y; acc.z += f * v.z; acc.w += f * v.w;
   }
   InT* orow = reinterpret_cast<InT*>(a.out) + ((((long long)b * a.Hq + (long long)kvh * p.G + (rr >> 4)) * 16) + (rr & 15)) * D + c4 * 4;
@@ -1222,7 +1222,7 @@ int32_t launch_typed(const SdpaArgs& a, cudaStream_t stream) {
   DFLASH_LAUNCH_CHECK();
   count_launch();
   if (need_merge_kernel) {
-    sdpa_tc_merge_kernel<InT, D><<<dim3(p.units, kRowsM / 16, D / 64), 256, 0, stream>>>(p, (int)(2 * grid));
+    sdpa_tc_merge_kernel<InT, D><<<dim3(p.units, kRowsM / 32, D / 32), 256, 0, stream>>>(p, (int)(2 * grid));
     DFLASH_LAUNCH_CHECK();
     count_launch();
   }
