@@ -576,6 +576,19 @@ def run_case(args):
         units = cfg["B_seq"] * cfg["L"] * cfg["Hv"]
         alg = replay_bytes(float(x["n"].sum().item()) * cfg["Hv"], units)
         info = {"case": args.case, "head_states": units, "algorithmic_bytes_per_launch": alg}
+    elif args.case == "replay_vec_small":
+        # the same 16 sequences with a per-channel gate [B,T,Hv,Dk]
+        cfg = dict(CFG1, B_seq=16)
+        x = make_replay_inputs(torch, device, SEED + 1000, cfg)
+        gen = torch.Generator(device=device).manual_seed(SEED + 1500)
+        g_vec = torch.exp(-torch.nn.functional.softplus(torch.randn(*x["v"].shape[:3], cfg["D"], device=device, generator=gen))).bfloat16()
+        y = torch.empty_like(x["v"])
+        out = torch.empty_like(x["state"])
+        for _ in range(args.warmup + args.steps):
+            kernels.gated_delta_into(x["q"], x["k"], x["v"], g_vec, x["beta"], x["state"], x["n"], y, out)
+        units = cfg["B_seq"] * cfg["L"] * cfg["Hv"]
+        n_sum = float(x["n"].sum().item()) * cfg["Hv"]
+        info = {"case": args.case, "head_states": units, "algorithmic_bytes_per_launch": units * 131072.0 + (770 + 2 * cfg["D"]) * n_sum}
     elif args.case == "delta_replay_small":
         cfg = dict(CFG1, B_seq=16)
         x = make_replay_inputs(torch, device, SEED + 1000, cfg)
@@ -617,7 +630,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--case", default=None, choices=["replay_small", "delta_replay_small", "sdpa_small", "turbo_decode_k_small", "turbo_decode_v_small"],
+    ap.add_argument("--case", default=None, choices=["replay_small", "replay_vec_small", "delta_replay_small", "sdpa_small", "turbo_decode_k_small", "turbo_decode_v_small"],
                     help="run one small single-kernel case (for profiler captures) instead of the benchmark")
     args = ap.parse_args()
     if args.case:
