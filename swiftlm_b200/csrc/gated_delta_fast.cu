@@ -337,14 +337,9 @@ gdn_fast_kernel(const __grid_constant__ CUtensorMap state_map, const GdnArgs a, 
         kk[box][0] = f2(k4.x, k4.y);
         kk[box][1] = f2(k4.z, k4.w);
       }
-      float2 gg2[4][2];   // per-channel gate of this thread's 16 columns
-      if (VEC) {
-        const InT* grow = reinterpret_cast<const InT*>(sm + L::raw_g) + ((it & 1) * kTmax + t) * kD;
-#pragma unroll
-        for (int box = 0; box < 4; ++box) load4_as_f32x2<InT>(grow + 32 * box + col, gg2[box]);
-      } else {
-        Gd *= s_g[slot * 16 + t];
-      }
+      // per-channel gate: this thread's 16 columns of the step's gate row, read box by box where they are used
+      const InT* grow = VEC ? reinterpret_cast<const InT*>(sm + L::raw_g) + ((it & 1) * kTmax + t) * kD + col : nullptr;
+      if (!VEC) Gd *= s_g[slot * 16 + t];
       if (!VEC && Gd < 1e-12f) {  // uniform per work item: U <- Gd * U, Gd <- 1
         const float2 G2 = f2(Gd, Gd);
 #pragma unroll
@@ -361,25 +356,33 @@ gdn_fast_kernel(const __grid_constant__ CUtensorMap state_map, const GdnArgs a, 
 #pragma unroll
         for (int i = 0; i < 4; ++i) d[i] = d32[t * 16 + r_sub + 4 * i] * inv_G;
 #pragma unroll
-        for (int box = 0; box < 4; ++box)
+        for (int box = 0; box < 4; ++box) {
+          float2 gb[2];
+          if (VEC) load4_as_f32x2<InT>(grow + 32 * box, gb);
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
             const float2 dd = f2(d[i], d[i]);
 #pragma unroll
             for (int j = 0; j < 2; ++j)
-              S[i][box][j] = __ffma2_rn(dd, kk[box][j], VEC ? __fmul2_rn(S[i][box][j], gg2[box][j]) : S[i][box][j]);
+              S[i][box][j] = __ffma2_rn(dd, kk[box][j], VEC ? __fmul2_rn(S[i][box][j], gb[j]) : S[i][box][j]);
           }
+        }
       } else {
         const float beta = s_beta[slot * 16 + t];
         float part[4];
+        if (VEC) {   // decay column by column first, as the reference does
+#pragma unroll
+          for (int box = 0; box < 4; ++box) {
+            float2 gb[2];
+            load4_as_f32x2<InT>(grow + 32 * box, gb);
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+              for (int j = 0; j < 2; ++j) S[i][box][j] = __fmul2_rn(S[i][box][j], gb[j]);
+          }
+        }
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-          if (VEC) {
-#pragma unroll
-            for (int box = 0; box < 4; ++box)
-#pragma unroll
-              for (int j = 0; j < 2; ++j) S[i][box][j] = __fmul2_rn(S[i][box][j], gg2[box][j]);
-          }
           float2 acc0 = __fmul2_rn(S[i][0][0], kk[0][0]), acc1 = __fmul2_rn(S[i][0][1], kk[0][1]);
 #pragma unroll
           for (int box = 1; box < 4; ++box) {
