@@ -609,6 +609,18 @@ def run_case(args):
             kernels.turbo_decode_into(packed, signs, norm, rnorm, dec)
         blocks = kv.numel() // 128
         info = {"case": args.case, "blocks": blocks, "algorithmic_bytes_per_launch": blocks * ((68 if is_key else 50) + 256)}
+    elif args.case == "sdpa_single_long":
+        # one sequence with 102 400 + 16 keys (the reference's own serving shape at configs[3]'s context): two
+        # (sequence, KV head) units, so every unit is cut into one key range per SM and the merge kernel combines them
+        g = torch.Generator(device=device).manual_seed(SEED + 3000)
+        N = 102400 + 16
+        q = torch.randn(1, 16, 16, 256, device=device, generator=g).bfloat16()
+        kvs = [(torch.randn(1, 2, N, 256, device=device, generator=g).bfloat16(),
+                torch.randn(1, 2, N, 256, device=device, generator=g).bfloat16()) for _ in range(2)]
+        out = torch.empty_like(q)
+        for i in range(args.warmup + args.steps):
+            kernels.batched_sdpa_2pass(q, kvs[i % 2][0], kvs[i % 2][1], 1.0 / 16.0, out=out)
+        info = {"case": args.case, "flops_per_launch": 4.0 * 16 * 16 * N * 256, "algorithmic_bytes_per_launch": 2.0 * 2 * N * 256 * 2 + 2 * q.numel() * 2}
     else:
         cfg = CFG2
         g = torch.Generator(device=device).manual_seed(SEED + 2000)
@@ -630,7 +642,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--case", default=None, choices=["replay_small", "replay_vec_small", "delta_replay_small", "sdpa_small", "turbo_decode_k_small", "turbo_decode_v_small"],
+    ap.add_argument("--case", default=None, choices=["replay_small", "replay_vec_small", "delta_replay_small", "sdpa_small", "sdpa_single_long", "turbo_decode_k_small", "turbo_decode_v_small"],
                     help="run one small single-kernel case (for profiler captures) instead of the benchmark")
     args = ap.parse_args()
     if args.case:

@@ -1018,10 +1018,10 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
 }
 
 // ---- merge of the split-KV partials ----------------------------------------------------------
-// One block per (unit, 32 rows, 32 columns); the ranges of a unit are summed in slot order.
+// One block per (unit, 32 rows, 16 columns); the ranges of a unit are summed in slot order.
 template <typename InT, int D>
-__global__ void __launch_bounds__(256) sdpa_tc_merge_kernel(const TcParams p, int n_slots) {
-  // One CTA combines 32 rows x 8 float4 columns of one unit: lane = row (the partials keep the 128 rows of a float4
+__global__ void __launch_bounds__(128) sdpa_tc_merge_kernel(const TcParams p, int n_slots) {
+  // One CTA (4 warps) combines 32 rows x 4 float4 columns of one unit: lane = row (the partials keep the 128 rows of a float4
   // column contiguous, so a warp reads 512 contiguous bytes per range), warp = column.  A unit has at most one range
   // per CTA of the main kernel, so kMaxRanges covers every GPU with up to 320 SMs; more is reported, not dropped.
   constexpr int kMaxRanges = 320;
@@ -1054,11 +1054,11 @@ __global__ void __launch_bounds__(256) sdpa_tc_merge_kernel(const TcParams p, in
   const int b = unit / per_b, kvh = (unit / p.MT) % a.Hkv, mt = unit % p.MT;
   const int r = rgrp * 32 + lane;                        // row of the 128-row tile
   const int rr = mt * kRowsM + r;
-  // per-row weights once per CTA: warp w takes ranges w, w + 8, ...
+  // per-row weights once per CTA: warp w takes ranges w, w + 4, ...
   {
     float mmax = -INFINITY;
     for (int i = 0; i < cnt; ++i) mmax = fmaxf(mmax, p.part_m[(long long)s_slots[i] * kRowsM + r]);
-    for (int i = warp; i < cnt; i += 8) {
+    for (int i = warp; i < cnt; i += 4) {
       const float m = p.part_m[(long long)s_slots[i] * kRowsM + r];
       s_f[i][lane] = (m == -INFINITY) ? 0.f : exp2f(m - mmax);
     }
@@ -1068,7 +1068,7 @@ __global__ void __launch_bounds__(256) sdpa_tc_merge_kernel(const TcParams p, in
   float den = 0.f;
   for (int i = 0; i < cnt; ++i) den += s_f[i][lane] * p.part_l[(long long)s_slots[i] * kRowsM + r];   // same order in every warp
   const float inv = den == 0.f ? 1.f : 1.f / den;
-  const int c4 = cgrp * 8 + warp;                        // float4 index inside the row
+  const int c4 = cgrp * 4 + warp;                        // float4 index inside the row
   float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
   const float* src = p.part_o + ((long long)c4 * kRowsM + r) * 4;
   int i = 0;
@@ -1222,7 +1222,7 @@ int32_t launch_typed(const SdpaArgs& a, cudaStream_t stream) {
   DFLASH_LAUNCH_CHECK();
   count_launch();
   if (need_merge_kernel) {
-    sdpa_tc_merge_kernel<InT, D><<<dim3(p.units, kRowsM / 32, D / 32), 256, 0, stream>>>(p, (int)(2 * grid));
+    sdpa_tc_merge_kernel<InT, D><<<dim3(p.units, kRowsM / 32, D / 16), 128, 0, stream>>>(p, (int)(2 * grid));
     DFLASH_LAUNCH_CHECK();
     count_launch();
   }
