@@ -171,6 +171,27 @@ def cpu_replay_sample(seqs: int, repeats: int = 1):
     return heads / best, best, CO.num_threads(), heads
 
 
+def cpu_sdpa_sample(seqs: int = 4, repeats: int = 3):
+    """CPU statement of the verify attention (the oracle's C restatement of the reference kernel's semantics, OpenMP over
+    (sequence, query head)) on `seqs` of the 32 sequences of configs[2]."""
+    import numpy as np
+
+    from oracle import c_oracle as CO
+    from oracle import dflash_oracle as O
+    cfg = CFG2
+    x = O.make_sdpa_inputs(seqs, cfg["Hq"], cfg["Hkv"], cfg["N"], cfg["D"], SEED + 2000, "bf16")
+    CO.verify_sdpa(x["q"], x["k"], x["v"], x["scale"])          # warm-up (thread pool, page faults)
+    best = float("inf")
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        CO.verify_sdpa(x["q"], x["k"], x["v"], x["scale"])
+        best = min(best, time.perf_counter() - t0)
+    flops = sdpa_flops() * seqs / cfg["B"]
+    return {"value": flops / best / 1e12, "unit": "TFLOP/s", "cores": CO.num_threads(), "kind": "port",
+            "sample": f"{seqs} of {cfg['B']} sequences of configs[2] (best of {repeats} passes, {best:.2f} s each), OpenMP C "
+                      f"restatement of the reference kernel's arithmetic (one key at a time, fp32)"}
+
+
 def cpu_ops_sample(seqs: int = 2):
     """Times the op-for-op Torch-CPU statement of the reference's CPU path (five full-state passes per token,
     all intra-op threads) on `seqs` sequences x 36 layers of configs[1]."""
@@ -355,6 +376,8 @@ def run_gpu(args):
                "sample": f"16 of 64 sequences x 36 layers x 32 heads ({sample_heads} head-states, best of 6 passes, {dt:.2f} s each), OpenMP "
                          f"row-wise C restatement of the reference's ops path",
                "ops_path": cpu_ops_sample(2)}
+        if isinstance(sd, dict) and "error" not in sd:
+            sd["cpu_baseline"] = cpu_sdpa_sample()
 
     line = {
         "metric": "replayed_head_states_per_s", "value": value, "unit": "head-states/s", "n_gpus": world,
