@@ -1144,7 +1144,11 @@ int32_t launch_typed(const SdpaArgs& a, cudaStream_t stream) {
   if (!a.kv_len) {
     const int c = n_sm / p.units;
     static const int mode = [] { const char* e = getenv("DFLASH_SDPA_SPLIT"); return e ? atoi(e) : -1; }();   // -1 auto, 0 stream-K
-    if (mode != 0 && c >= 1 && c <= kFusedMax && tiles_per_unit >= c && (long long)p.units * c * 5 >= (long long)n_sm * 4) {
+    // Equal cuts leave n_sm - units * c SMs idle.  With long units that costs more than stream-K's partials and merge
+    // (measured: about ten key tiles' worth of time): B=60, N=16400 runs 12 % faster as stream-K, B=64, N=4112 4 % slower.
+    const double idle_tiles = c >= 1 ? (double)tiles_per_unit / c * (1.0 - (double)p.units * c / n_sm) : 0.0;
+    if (mode != 0 && c >= 1 && c <= kFusedMax && tiles_per_unit >= c && (long long)p.units * c * 5 >= (long long)n_sm * 4 &&
+        (mode > 0 || idle_tiles < 10.0)) {
       p.split = c;
       p.pair = c == 2 ? 1 : 0;
       grid = (long long)p.units * c;

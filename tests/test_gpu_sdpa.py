@@ -57,6 +57,7 @@ CASES = [
     (16, 16, 2, 16 + 900, 256, "fp16"),       # 32 units: four equal cuts per unit
     (80, 16, 2, 16 + 300, 256, "bf16"),       # 160 units on 148 SMs: stream-K ranges that cover whole units and pieces
     (37, 16, 2, 16 + 130, 256, "bf16"),       # 74 units of two tiles: one tile per CTA of a pair
+    (60, 16, 2, 16 + 6900, 256, "bf16"),      # 120 long units: whole-unit CTAs would idle 28 SMs, so stream-K ranges are used
 ]
 
 
