@@ -422,7 +422,10 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       uint32_t fill = 0;        // ring slots filled so far
       uint32_t seg_idx = 0;
       bool ok = true;
-      auto load_chunk = [&](const CUtensorMap* map, const Segment& sg, int tile, int c) -> bool {
+      // Paged KV: the page of a tile is looked up once per stream (K runs one tile ahead of V), not once per chunk.
+      struct PageRef { int b, index, page; };
+      PageRef ref_k{-1, -1, 0}, ref_v{-1, -1, 0};
+      auto load_chunk = [&](const CUtensorMap* map, PageRef& ref, const Segment& sg, int tile, int c) -> bool {
         const uint32_t stage = fill % kStages;
         {
           TR_T0();
@@ -433,8 +436,11 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         ptx::mbar_arrive_expect_tx(&bars[SL::b_kv_full + stage], kChunkBytes);
         const int n0 = tile * kBlockN;
         if (a.page_table) {
-          const int page = a.page_table[(long long)sg.b * a.max_pages + n0 / a.page_tokens];
-          ptx::tma_load_4d(sm + SL::ring + stage * kChunkBytes, map, c * 64, n0 % a.page_tokens, sg.kvh, page,
+          if (c == 0) {
+            const int index = n0 / a.page_tokens;
+            if (index != ref.index || sg.b != ref.b) ref = PageRef{sg.b, index, a.page_table[(long long)sg.b * a.max_pages + index]};
+          }
+          ptx::tma_load_4d(sm + SL::ring + stage * kChunkBytes, map, c * 64, n0 - ref.index * a.page_tokens, sg.kvh, ref.page,
                            &bars[SL::b_kv_full + stage]);
         } else {
           ptx::tma_load_4d(sm + SL::ring + stage * kChunkBytes, map, c * 64, n0, sg.kvh, sg.b, &bars[SL::b_kv_full + stage]);
@@ -451,9 +457,9 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         // K_lo, then (K_{j+1}, V_j) pairs, then V_last: the order the MMA warp consumes them
         for (int j = s.tile_lo; ok && j <= s.tile_hi; ++j) {
           if (j < s.tile_hi)
-            for (int c = 0; ok && c < kQChunks; ++c) ok = load_chunk(&map_k, s, j, c);
+            for (int c = 0; ok && c < kQChunks; ++c) ok = load_chunk(&map_k, ref_k, s, j, c);
           if (j > s.tile_lo)
-            for (int c = 0; ok && c < kQChunks; ++c) ok = load_chunk(&map_v, s, j - 1, c);
+            for (int c = 0; ok && c < kQChunks; ++c) ok = load_chunk(&map_v, ref_v, s, j - 1, c);
         }
         ++seg_idx;
       }
