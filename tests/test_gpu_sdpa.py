@@ -57,6 +57,8 @@ CASES = [
     (16, 16, 2, 16 + 900, 256, "fp16"),       # 32 units: four equal cuts per unit
     (80, 16, 2, 16 + 300, 256, "bf16"),       # 160 units on 148 SMs: stream-K ranges that cover whole units and pieces
     (37, 16, 2, 16 + 130, 256, "bf16"),       # 74 units of two tiles: one tile per CTA of a pair
+    (8, 16, 2, 16 + 2400, 256, "bf16"),       # 16 units: nine equal cuts per unit, combined by the merge kernel
+    (5, 16, 2, 16 + 3000, 128, "fp16"),       # 10 units: fourteen equal cuts per unit
     (60, 16, 2, 16 + 6900, 256, "bf16"),      # 120 long units: whole-unit CTAs would idle 28 SMs, so stream-K ranges are used
 ]
 
