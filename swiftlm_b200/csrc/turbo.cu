@@ -10,9 +10,9 @@
 //
 // The codec is integer/byte work whose results must match the reference bit for bit, so every
 // floating-point operation is performed in the reference's order with explicitly rounded
-// adds and multiplies (no fused multiply-add).  One thread owns one 128-block.  The encoder walks
-// it sequentially in shared memory (element i of thread t at [i][t]: conflict-free); the decoder,
-// which sits on the attention read path, keeps the block in registers.
+// adds and multiplies (no fused multiply-add).  One thread owns one 128-block and keeps it in
+// registers, in the encoder and in the decoder; an encoder that walks the block sequentially in
+// shared memory (element i of thread t at [i][t]) serves arrays that are not 16-byte aligned.
 #include "common.cuh"
 #include "turbo_tables.cuh"
 
@@ -255,29 +255,143 @@ int32_t launch_decode_typed(const uint8_t* packed, const uint8_t* signs, const u
   return DFLASH_OK;
 }
 
+// ---- encode: one thread per 128-block, the block lives in registers ------------------------------
+// Same statement order as turbo_encode_kernel above (the sums of squares run sequentially over i, the butterflies
+// stage by stage), with the block in registers instead of strided shared memory.  The CTA's 64 blocks are first staged
+// in shared memory with coalesced loads; the normalised vector a key needs again for its residual is recomputed from
+// that stage (same operands, same bits) rather than kept in a second register file's worth of state.
+template <typename InT> __device__ __forceinline__ void load8_in(const InT* src, float (&o)[8]);
+template <> __device__ __forceinline__ void load8_in<float>(const float* src, float (&o)[8]) {
+  const float4 a = *reinterpret_cast<const float4*>(src), b = *reinterpret_cast<const float4*>(src + 4);
+  o[0] = a.x; o[1] = a.y; o[2] = a.z; o[3] = a.w; o[4] = b.x; o[5] = b.y; o[6] = b.z; o[7] = b.w;
+}
+template <> __device__ __forceinline__ void load8_in<__nv_bfloat16>(const __nv_bfloat16* src, float (&o)[8]) {
+  const uint4 u = *reinterpret_cast<const uint4*>(src);
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(h[i]); o[2 * i] = f.x; o[2 * i + 1] = f.y; }
+}
+template <> __device__ __forceinline__ void load8_in<__half>(const __half* src, float (&o)[8]) {
+  const uint4 u = *reinterpret_cast<const uint4*>(src);
+  const __half2* h = reinterpret_cast<const __half2*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) { const float2 f = __half22float2(h[i]); o[2 * i] = f.x; o[2 * i + 1] = f.y; }
+}
+
+template <typename InT>
+__global__ void __launch_bounds__(kDecThreads)
+turbo_encode_regs_kernel(const InT* __restrict__ x, uint8_t* __restrict__ packed, uint8_t* __restrict__ signs,
+                         uint16_t* __restrict__ norm, uint16_t* __restrict__ rnorm, long long n, int is_key) {
+  extern __shared__ float sh[];
+  float* c3 = sh;                                            // [8][kDecThreads]: one copy of the centroids per thread column
+  constexpr int kRowBytes = kBlock * (int)sizeof(InT) + 16;  // the pad keeps neighbouring threads' 16-byte pieces on different banks
+  uint8_t* stage = reinterpret_cast<uint8_t*>(sh + 8 * kDecThreads);
+  for (int i = threadIdx.x; i < 8 * kDecThreads; i += kDecThreads) c3[i] = TURBO_C3[i / kDecThreads];
+  const long long first = (long long)blockIdx.x * kDecThreads;
+  const long long here = n - first < kDecThreads ? n - first : kDecThreads;
+  constexpr int kPieces = kBlock * (int)sizeof(InT) / 16;
+  for (int p = threadIdx.x; p < (int)here * kPieces; p += kDecThreads) {
+    const int t = p / kPieces, off = p % kPieces;
+    *reinterpret_cast<uint4*>(stage + t * kRowBytes + off * 16) =
+        *reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(x + (first + t) * kBlock) + off * 16);
+  }
+  __syncthreads();
+  const long long v = first + threadIdx.x;
+  if (v >= n) return;
+  const InT* mine = reinterpret_cast<const InT*>(stage + threadIdx.x * kRowBytes);
+  float w[kBlock];
+  float ns = 0.f;
+#pragma unroll
+  for (int g8 = 0; g8 < kBlock / 8; ++g8) {
+    float f[8];
+    load8_in<InT>(mine + g8 * 8, f);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      w[g8 * 8 + e] = f[e];
+      ns = __fadd_rn(ns, __fmul_rn(f[e], f[e]));
+    }
+  }
+  const float gn = __fsqrt_rn(ns), inv = gn > 1e-10f ? __fdiv_rn(1.f, gn) : 0.f;
+#pragma unroll
+  for (int i = 0; i < kBlock; ++i) w[i] = __fmul_rn(w[i], inv);
+  rot_regs(w, TURBO_S1_NEG, TURBO_S2_NEG);
+  // 3-bit indices: little-endian bit stream (:19), 8 indices -> 3 bytes; the centroid vector replaces the work vector
+  float rs = 0.f;
+  unsigned int pk[12];
+#pragma unroll
+  for (int i = 0; i < 12; ++i) pk[i] = 0u;
+#pragma unroll
+  for (int i = 0; i < kBlock; ++i) {
+    const int idx = nearest3(w[i]);
+    const float c = c3[idx * kDecThreads + threadIdx.x];
+    const int bit = 3 * i, word = bit >> 5, off = bit & 31;
+    pk[word] |= (unsigned int)idx << off;
+    if (off > 29) pk[word + 1] |= (unsigned int)idx >> (32 - off);
+    rs = __fadd_rn(rs, __fmul_rn(c, c));
+    w[i] = c;
+  }
+  uint4* pout = reinterpret_cast<uint4*>(packed + v * 48);
+  pout[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+  pout[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+  pout[2] = make_uint4(pk[8], pk[9], pk[10], pk[11]);
+  if (!is_key) {
+    const float rn2 = __fsqrt_rn(rs);
+    norm[v] = to_f16_trunc(rn2 > 1e-10f ? __fdiv_rn(gn, rn2) : gn);        // :73
+    return;
+  }
+  rot_regs(w, TURBO_S2_NEG, TURBO_S1_NEG);                                 // inverse rotation of the centroids (:91)
+  float rns = 0.f;
+#pragma unroll
+  for (int g8 = 0; g8 < kBlock / 8; ++g8) {
+    float f[8];
+    load8_in<InT>(mine + g8 * 8, f);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const float r = __fsub_rn(__fmul_rn(f[e], inv), w[g8 * 8 + e]);      // normalised input minus its quantised image
+      w[g8 * 8 + e] = r;
+      rns = __fadd_rn(rns, __fmul_rn(r, r));
+    }
+  }
+  rot_regs(w, TURBO_Q1_NEG, TURBO_Q2_NEG);                                 // :93
+  unsigned int sg[4] = {0u, 0u, 0u, 0u};
+#pragma unroll
+  for (int i = 0; i < kBlock; ++i) sg[i >> 5] |= (w[i] >= 0.f ? 1u : 0u) << (i & 31);
+  *reinterpret_cast<uint4*>(signs + v * 16) = make_uint4(sg[0], sg[1], sg[2], sg[3]);
+  norm[v] = to_f16_trunc(gn);
+  rnorm[v] = to_f16_trunc(__fsqrt_rn(rns));
+}
+
+template <typename InT>
+int32_t launch_encode_typed(const void* x, uint8_t* packed, uint8_t* signs, uint16_t* norm, uint16_t* rnorm, long long n, int is_key,
+                            cudaStream_t stream) {
+  const unsigned grid = (unsigned)((n + kDecThreads - 1) / kDecThreads);
+  const bool aligned = !(((uintptr_t)x | (uintptr_t)packed | (is_key ? (uintptr_t)signs : 0)) & 15);
+  if (aligned) {   // the block in registers, 16-byte loads and stores
+    const size_t smem = 8 * kDecThreads * sizeof(float) + kDecThreads * (kBlock * sizeof(InT) + 16);
+    DFLASH_CUDA_CHECK(cudaFuncSetAttribute(turbo_encode_regs_kernel<InT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    turbo_encode_regs_kernel<InT><<<grid, kDecThreads, smem, stream>>>((const InT*)x, packed, signs, norm, rnorm, n, is_key);
+  } else {         // byte-wise access, any alignment
+    const size_t smem = 2 * kBlock * kThreadsPerCta * sizeof(float);
+    DFLASH_CUDA_CHECK(cudaFuncSetAttribute(turbo_encode_kernel<InT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    turbo_encode_kernel<InT><<<grid, kThreadsPerCta, smem, stream>>>((const InT*)x, packed, signs, norm, rnorm, n, is_key);
+  }
+  return DFLASH_OK;
+}
+
 }  // namespace
 
 int32_t launch_turbo_encode(const void* x, uint8_t* packed, uint8_t* signs, uint16_t* norm, uint16_t* rnorm,
                             long long n, int is_key, int in_dtype, cudaStream_t stream) {
-  const unsigned grid = (unsigned)((n + kThreadsPerCta - 1) / kThreadsPerCta);
-  const size_t smem = 2 * kBlock * kThreadsPerCta * sizeof(float);
+  int32_t st;
   switch (in_dtype) {
-    case DFLASH_F32:
-      DFLASH_CUDA_CHECK(cudaFuncSetAttribute(turbo_encode_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-      turbo_encode_kernel<float><<<grid, kThreadsPerCta, smem, stream>>>((const float*)x, packed, signs, norm, rnorm, n, is_key);
-      break;
-    case DFLASH_BF16:
-      DFLASH_CUDA_CHECK(cudaFuncSetAttribute(turbo_encode_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-      turbo_encode_kernel<__nv_bfloat16><<<grid, kThreadsPerCta, smem, stream>>>((const __nv_bfloat16*)x, packed, signs, norm, rnorm, n, is_key);
-      break;
-    case DFLASH_F16:
-      DFLASH_CUDA_CHECK(cudaFuncSetAttribute(turbo_encode_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-      turbo_encode_kernel<__half><<<grid, kThreadsPerCta, smem, stream>>>((const __half*)x, packed, signs, norm, rnorm, n, is_key);
-      break;
+    case DFLASH_F32: st = launch_encode_typed<float>(x, packed, signs, norm, rnorm, n, is_key, stream); break;
+    case DFLASH_BF16: st = launch_encode_typed<__nv_bfloat16>(x, packed, signs, norm, rnorm, n, is_key, stream); break;
+    case DFLASH_F16: st = launch_encode_typed<__half>(x, packed, signs, norm, rnorm, n, is_key, stream); break;
     default:
       set_error("turbo_encode: unsupported dtype %d", in_dtype);
       return DFLASH_ERR_UNSUPPORTED;
   }
+  if (st != DFLASH_OK) return st;
   DFLASH_LAUNCH_CHECK();
   count_launch();
   return DFLASH_OK;

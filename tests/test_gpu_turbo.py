@@ -42,6 +42,21 @@ def test_codec_bit_exact_against_oracle(is_key):
     assert rel < 0.15
 
 
+def test_encode_of_an_unaligned_input_takes_the_bytewise_kernel_and_agrees():
+    """The register-resident encoder needs 16-byte aligned arrays; anything else takes the byte-wise kernel.  Both
+    must produce the same bytes."""
+    g = torch.Generator(device="cuda").manual_seed(9)
+    buf = torch.randn(2 + 70 * 128, device="cuda", generator=g)
+    x_off = buf[2:].view(70, 128)                       # 8 bytes past a 16-byte boundary
+    assert x_off.data_ptr() % 16 != 0
+    x_al = x_off.clone()
+    for is_key in (False, True):
+        a = K().turbo_encode(x_off, is_key)
+        b = K().turbo_encode(x_al, is_key)
+        for u, v in zip(a, b):
+            assert (u is None and v is None) or torch.equal(u, v)
+
+
 def test_head_dim_256_is_two_blocks_and_bf16_io():
     g = torch.Generator(device="cuda").manual_seed(5)
     kv = torch.randn(2, 2, 40, 256, device="cuda", generator=g).bfloat16()
