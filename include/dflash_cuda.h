@@ -210,6 +210,8 @@ int32_t dflash_kv_commit(int32_t* kv_len, const int32_t* commit, int32_t B, int3
  *   signs    uint8[n_blocks,16]  K only: sign bits of the rotated residual (NULL for V)
  *   norm     uint16[n_blocks]    fp16 bits: ||k|| (K) or ||v|| / ||centroid vector|| (V)
  *   rnorm    uint16[n_blocks]    K only: fp16 bits of the residual norm (NULL for V)
+ * dflash_turbo_decode needs packed, signs and out 16-byte aligned.  dflash_turbo_encode takes any
+ * alignment; with x, packed and signs 16-byte aligned it runs its fast kernel (same bytes).
  */
 int32_t dflash_turbo_encode(const void* x, uint8_t* packed, uint8_t* signs, uint16_t* norm, uint16_t* rnorm,
                             int64_t n_blocks, int32_t is_key, int32_t in_dtype, void* stream);
