@@ -160,7 +160,7 @@ def cpu_replay_sample(seqs: int, repeats: int = 1):
     x = O.make_gdn_inputs(B, cfg["T"], cfg["Hk"], cfg["Hv"], cfg["D"], cfg["D"], SEED + 1000, False, "bf16")
     rng = np.random.default_rng(SEED + 1001)
     x["n"] = np.repeat(rng.integers(0, cfg["T"] + 1, seqs), cfg["L"]).astype(np.int32)
-    CO.load()
+    CO.use_all_cores()
     best = None
     for _ in range(repeats):
         t0 = time.perf_counter()
@@ -180,6 +180,7 @@ def cpu_sdpa_sample(seqs: int = 4, repeats: int = 3):
     from oracle import dflash_oracle as O
     cfg = CFG2
     x = O.make_sdpa_inputs(seqs, cfg["Hq"], cfg["Hkv"], cfg["N"], cfg["D"], SEED + 2000, "bf16")
+    CO.use_all_cores()
     CO.verify_sdpa(x["q"], x["k"], x["v"], x["scale"])          # warm-up (thread pool, page faults)
     best = float("inf")
     for _ in range(repeats):
@@ -205,6 +206,7 @@ def cpu_ops_sample(seqs: int = 2):
     n = np.repeat(rng.integers(0, cfg["T"] + 1, seqs), cfg["L"]).astype(np.int32)
     mask = (np.arange(cfg["T"])[None, :] < n[:, None]).astype(np.float32)
     t = {k_: torch.from_numpy(np.ascontiguousarray(v_)) for k_, v_ in x.items() if k_ != "n"}
+    torch.set_num_threads(len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1))
     best = None
     for _ in range(2):
         t0 = time.perf_counter()

@@ -29,8 +29,11 @@ def load():
     global _LIB
     if _LIB is None:
         path = os.path.join(_HERE, "_build", "liboracle.so")
-        if not os.path.exists(path):
-            build()
+        try:
+            build()          # make is incremental: a no-op unless a source is newer than the library
+        except (OSError, subprocess.CalledProcessError):
+            if not os.path.exists(path):
+                raise
         _LIB = C.CDLL(path)
         _LIB.oracle_num_threads.restype = C.c_int
     return _LIB
@@ -60,6 +63,14 @@ def load_ref():
 
 def num_threads() -> int:
     return load().oracle_num_threads()
+
+
+def use_all_cores() -> int:
+    """Lets the OpenMP loops use every core this process may run on, whatever OMP_NUM_THREADS says (torchrun exports
+    OMP_NUM_THREADS=1 to its ranks).  Returns the thread count."""
+    cores = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    load().oracle_set_num_threads(int(cores))
+    return num_threads()
 
 
 def _opt(a, dtype):

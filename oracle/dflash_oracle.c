@@ -20,6 +20,15 @@
 #include <omp.h>
 #endif
 
+/* Overrides the OpenMP thread count (launchers such as torchrun export OMP_NUM_THREADS=1). */
+void oracle_set_num_threads(int n) {
+#ifdef _OPENMP
+  if (n > 0) omp_set_num_threads(n);
+#else
+  (void)n;
+#endif
+}
+
 int oracle_num_threads(void) {
 #ifdef _OPENMP
   return omp_get_max_threads();
