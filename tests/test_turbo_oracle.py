@@ -144,3 +144,36 @@ def test_k_codec_inner_product_snr_matches_reference():
     sc = np.float32(REF.turbo_ref_ff16(C.c_uint16(int(norm[0]))))
     want = ((d + sf * qs) * sc).astype(np.float32)
     np.testing.assert_array_equal(want, dec[0])
+
+
+def test_rotated_domain_attention_equals_decode_then_attend():
+    """The form a fused kernel would compute (queries and outputs rotated, no key or value decoded) against the
+    plain statement: decode every block with the codec, then block-verify attention."""
+    from oracle import dflash_oracle as O
+    from oracle import turbo_rotated_attention as TR
+    rng = np.random.default_rng(20260330)
+    B, Hq, Hkv, Nc, Nh, D = 2, 4, 2, 150, 21, 256
+    q = rng.standard_normal((B, Hq, 16, D)).astype(np.float32)
+    k = rng.standard_normal((B, Hkv, Nc + Nh, D)).astype(np.float32)
+    v = rng.standard_normal((B, Hkv, Nc + Nh, D)).astype(np.float32)
+    kb = k[:, :, :Nc].reshape(B, Hkv, Nc, D // 128, 128)
+    vb = v[:, :, :Nc].reshape(B, Hkv, Nc, D // 128, 128)
+    k_enc = CO.turbo_encode_k(kb)
+    v_enc = CO.turbo_encode_v(vb)
+    # rotation helpers agree with the codec: decode = norm * (R^-1 c + coef * rnorm * Rq s)
+    c = TR.C3[TR.unpack_indices(k_enc[0])]
+    s = TR.unpack_signs(k_enc[1])
+    coef = np.float32(TR.QJL_C / np.float32(128.0))
+    dec = (TR.rot(c, "S2", "S1") + coef * TR._f16(k_enc[3])[..., None] * TR.rot(s, "Q1", "Q2")) * TR._f16(k_enc[2])[..., None]
+    want_k = CO.turbo_decode_k(*k_enc)
+    assert np.abs(dec - want_k).max() < 2e-6 * np.abs(want_k).max()
+    # decode-then-attend
+    kd = np.concatenate([want_k.reshape(B, Hkv, Nc, D), k[:, :, Nc:]], axis=2)
+    vd = np.concatenate([CO.turbo_decode_v(*v_enc).reshape(B, Hkv, Nc, D), v[:, :, Nc:]], axis=2)
+    want = O.verify_sdpa(q, kd, vd, 1.0 / 16.0, in_dtype="bf16")
+    got = TR.verify_sdpa_rotated(q, k_enc, v_enc, 1.0 / 16.0, k_hot=k[:, :, Nc:], v_hot=v[:, :, Nc:])
+    assert np.abs(got - want).max() < 1e-4
+    # no hot window at all is out of contract for the verify block, but a window of exactly the block is the minimum
+    got16 = TR.verify_sdpa_rotated(q, k_enc, v_enc, 1.0 / 16.0, k_hot=k[:, :, Nc:Nc + 16], v_hot=v[:, :, Nc:Nc + 16])
+    kd16, vd16 = kd[:, :, :Nc + 16], vd[:, :, :Nc + 16]
+    assert np.abs(got16 - O.verify_sdpa(q, kd16, vd16, 1.0 / 16.0, in_dtype="bf16")).max() < 1e-4
