@@ -9,9 +9,11 @@ v-heads, Dk = Dv = 128, T = 16, bf16 per-token inputs, fp32 state, per-sequence 
 n ~ U{0..16}).  The headline `value` is replayed head-states per second with all inputs
 resident in HBM; `e2e` is the same metric through the package's host-buffer API (pinned host
 memory in, pinned host memory out, copies inside the timed region).  The verify attention of
-configs[2] is timed in the same run and reported under "sdpa".  With N > 1 (torchrun) every
-rank replays its own 64 sequences (sequence-sharded, no collective on the data path); the line
-reports the whole-job aggregate and the max-over-ranks time.
+configs[2] is timed in the same run and reported under "sdpa".  With N > 1 (torchrun) the ONE
+batch of 64 sequences is sharded by sequence over the ranks (64/32/16/8 sequences per GPU, no
+collective on the data path: strong scaling); the line reports the whole-job aggregate and the
+max-over-ranks time.  "weak_scaling" in the same line repeats the measurement with 64 sequences
+on every rank.
 
 `--impl reference` times the CPU statement of the same path (the oracle port of the
 reference's ops path, OpenMP over all host cores) on a bounded sample of the same workload.
@@ -47,11 +49,11 @@ def measured_peaks():
     return dict(hbm_gbs=6650.0, bf16_tflops=1590.0, bf16_tflops_sustained=1400.0, source="fallback")
 
 
-# DRAM bytes moved per algorithmic byte, from the committed ncu captures (dram__bytes_read.sum +
-# dram__bytes_write.sum of one launch on a smaller case of the same kernel; traffic grows in
-# proportion to the units processed):
-#   profiles/gdn_tc_forward_replay_small.md     2.6157 GB moved / 2.5627 GB algorithmic
-#   profiles/sdpa_tc_sdpa_small.md              277.6 MB moved / 277.9 MB algorithmic (no merge kernel for configs[2])
+# DRAM bytes moved per algorithmic byte, scaled from a smaller case: dram__bytes_read.sum +
+# dram__bytes_write.sum of one profiled launch of the same kernel on 16 of the 64 sequences
+# (2.6157 GB moved for 2.5627 GB algorithmic; traffic grows in proportion to the head-states
+# processed), and of one launch of configs[2] itself for the attention (277.6 MB moved for
+# 277.9 MB algorithmic, no merge kernel in that regime).
 TRAFFIC_PER_ALGORITHMIC_BYTE = {"gdn_tc_forward": 1.0207, "sdpa_tc": 0.9990}
 
 
@@ -111,9 +113,17 @@ class ClockSampler:
 # ------------------------------------------------------------------------------------------------
 
 
-def make_replay_inputs(torch, device, seed, cfg=CFG1, pinned_host=False):
+def make_replay_inputs(torch, device, seed, cfg=CFG1, seq_range=None):
     """configs[1]: q,k ~ N(0,1) L2-normalised; v ~ N(0,1); beta = sigmoid(N); g = exp(-softplus(N));
-    S0 ~ N(0, 0.02); n ~ U{0..T} per sequence, shared by the sequence's layers."""
+    S0 ~ N(0, 0.02); n ~ U{0..T} per sequence, shared by the sequence's layers.  seq_range = (lo, hi)
+    builds only that rank's sequences of the batch (its own seeded stream; the accepted lengths are
+    those of the whole batch's draw, so that every sharding replays the same lengths)."""
+    n_all = None
+    if seq_range is not None:
+        gn = torch.Generator(device="cpu").manual_seed(seed)
+        n_all = torch.randint(0, cfg["T"] + 1, (cfg["B_seq"],), generator=gn)
+        cfg = dict(cfg, B_seq=seq_range[1] - seq_range[0])
+        seed = seed + 7919 * seq_range[0]
     B = cfg["B_seq"] * cfg["L"]
     T, Hk, Hv, D = cfg["T"], cfg["Hk"], cfg["Hv"], cfg["D"]
     g = torch.Generator(device=device).manual_seed(seed)
@@ -127,6 +137,8 @@ def make_replay_inputs(torch, device, seed, cfg=CFG1, pinned_host=False):
         state=0.02 * torch.randn(B, Hv, D, D, device=device, generator=g),
         n=torch.randint(0, T + 1, (cfg["B_seq"],), device=device, generator=g).repeat_interleave(cfg["L"]).int(),
     )
+    if n_all is not None:
+        x["n"] = n_all[seq_range[0]:seq_range[1]].to(device).repeat_interleave(cfg["L"]).int()
     return x
 
 
@@ -237,7 +249,7 @@ def run_reference(args):
     line = {
         "impl": "reference", "metric": "replayed_head_states_per_s", "value": value, "unit": "head-states/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": workload_name(), "sample": sample},
         "cpu_baseline": {"value": value, "unit": "head-states/s", "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": "head-states/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -284,48 +296,60 @@ def run_gpu(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
+    from swiftlm_b200 import partition
+
     peaks = measured_peaks()
     cfg = CFG1
-    x = make_replay_inputs(torch, device, SEED + 1000 + rank)
-    heads = cfg["B_seq"] * cfg["L"] * cfg["Hv"]
+    heads_per_seq = cfg["L"] * cfg["Hv"]
+    total_heads = cfg["B_seq"] * heads_per_seq
+
+    def time_replay(x, steps, warmup, sampler=None):
+        """W untimed + K timed steps of the replay over the rank's sequences, bracketed by barrier + synchronize on
+        both sides; returns (max-over-ranks ms per step, this rank's mean CUDA-event ms per launch, launches)."""
+        y = torch.empty_like(x["v"])
+        state_out = torch.empty_like(x["state"])
+
+        def step():
+            kernels.gated_delta_into(x["q"], x["k"], x["v"], x["g"], x["beta"], x["state"], x["n"], y, state_out)
+
+        if sampler is not None:
+            sampler.start()   # runs through warm-up (same workload) and the timed steps
+        for _ in range(warmup):
+            step()
+        barrier()
+        launches0 = kernels.launch_count()
+        evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+        barrier()
+        t_start = torch.cuda.Event(enable_timing=True)
+        t_end = torch.cuda.Event(enable_timing=True)
+        t_start.record()
+        for e0, e1 in evs:
+            e0.record()
+            step()
+            e1.record()
+        t_end.record()
+        barrier()
+        launches = kernels.launch_count() - launches0
+        total_ms = max_over_ranks(t_start.elapsed_time(t_end))
+        kernel_ms = statistics.mean(e0.elapsed_time(e1) for e0, e1 in evs)
+        kernels.device_status()
+        return total_ms / steps, kernel_ms, launches, (y, state_out)
+
+    # ---- headline: the ONE batch of configs[1], its 64 sequences dealt to the ranks (strong scaling) ----
+    lo, hi = partition.plan(cfg["B_seq"], world)[rank]
+    x = make_replay_inputs(torch, device, SEED + 1000, seq_range=(lo, hi))
+    heads = (hi - lo) * heads_per_seq
     n_sum_heads = float(x["n"].sum().item()) * cfg["Hv"]
     alg_bytes = replay_bytes(n_sum_heads, heads)
-    # inputs (5.4 GB) and outputs (5.1 GB) exceed the 126 MB L2 many times over: no flush needed
-    y = torch.empty_like(x["v"])
-    state_out = torch.empty_like(x["state"])
-
-    def step():
-        kernels.gated_delta_into(x["q"], x["k"], x["v"], x["g"], x["beta"], x["state"], x["n"], y, state_out)
-
+    # per GPU, inputs plus outputs are 10.6 GB / N per step (1.3 GB at N = 8): far above the 126 MB L2, no flush needed
     sampler = ClockSampler(local)
-    if rank == 0:
-        sampler.start()   # runs through warm-up (same workload) and the timed steps
-    for _ in range(args.warmup):
-        step()
-    barrier()
-    launches0 = kernels.launch_count()
-    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
-    barrier()
-    t_start = torch.cuda.Event(enable_timing=True)
-    t_end = torch.cuda.Event(enable_timing=True)
-    t_start.record()
-    for e0, e1 in evs:
-        e0.record()
-        step()
-        e1.record()
-    t_end.record()
-    barrier()
-    launches = kernels.launch_count() - launches0
+    ms_per_step, kernel_ms, launches, (y, state_out) = time_replay(x, args.steps, args.warmup, sampler if rank == 0 else None)
     clocks = sampler.stop() if rank == 0 else None
-    total_ms = max_over_ranks(t_start.elapsed_time(t_end))
-    kernel_ms = statistics.mean(e0.elapsed_time(e1) for e0, e1 in evs)
-    kernels.device_status()
-    ms_per_step = total_ms / args.steps
-    value = world * heads / (ms_per_step * 1e-3)
+    value = total_heads / (ms_per_step * 1e-3)
     achieved_gbs = alg_bytes / (kernel_ms * 1e-3) / 1e9
     traffic = TRAFFIC_PER_ALGORITHMIC_BYTE["gdn_tc_forward"]
 
-    # ---- end to end through the host-buffer API (rank-local pinned buffers) ----
+    # ---- end to end through the host-buffer API (rank-local pinned buffers, the same sharded batch) ----
     e2e_steps = max(1, min(args.steps, 3))
     hx = host_api.pin_replay_inputs(x)
     hout = host_api.alloc_replay_outputs(hx)
@@ -339,8 +363,25 @@ def run_gpu(args):
     t1.record()
     barrier()
     e2e_ms = max_over_ranks(t0.elapsed_time(t1)) / e2e_steps
-    e2e_value = world * heads / (e2e_ms * 1e-3)
+    e2e_value = total_heads / (e2e_ms * 1e-3)
+    if world > 1:   # whole-job bytes per step: the sum over the ranks' shards
+        t = torch.tensor([float(h2d), float(d2h)], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.SUM)
+        h2d, d2h = int(t[0].item()), int(t[1].item())
     del hx, hout
+
+    # ---- the same kernel with 64 sequences on every rank (weak scaling; at N = 1 it is the headline itself) ----
+    weak = None
+    if world > 1:
+        del x, y, state_out
+        torch.cuda.empty_cache()
+        x = make_replay_inputs(torch, device, SEED + 1000 + rank, seq_range=(0, cfg["B_seq"]))
+        w_ms, w_kernel_ms, _, (y, state_out) = time_replay(x, args.steps, args.warmup)
+        heads = total_heads
+        n_sum_heads = float(x["n"].sum().item()) * cfg["Hv"]
+        weak = {"value": world * total_heads / (w_ms * 1e-3), "unit": "head-states/s", "ms_per_step": w_ms,
+                "per_gpu_batch": "64 sequences (73728 head-states)", "scaling": "weak",
+                "frac_of_hbm_peak_per_gpu": replay_bytes(n_sum_heads, total_heads) / (w_kernel_ms * 1e-3) / 1e9 / peaks["hbm_gbs"]}
 
     # ---- verify attention, configs[2] (rank-local, same on every rank) ----
     sd = run_sdpa(torch, kernels, device, args, peaks)
@@ -371,29 +412,29 @@ def run_gpu(args):
             dist.destroy_process_group()
         return
 
-    cpu = None
-    if world == 1 or True:
-        v, dt, threads, sample_heads = cpu_replay_sample(16, repeats=6)
-        cpu = {"value": v, "unit": "head-states/s", "cores": threads, "kind": "port",
-               "sample": f"16 of 64 sequences x 36 layers x 32 heads ({sample_heads} head-states, best of 6 passes, {dt:.2f} s each), OpenMP "
-                         f"row-wise C restatement of the reference's ops path",
-               "ops_path": cpu_ops_sample(2)}
-        if isinstance(sd, dict) and "error" not in sd:
-            sd["cpu_baseline"] = cpu_sdpa_sample()
+    v, dt, threads, sample_heads = cpu_replay_sample(16, repeats=6)
+    cpu = {"value": v, "unit": "head-states/s", "cores": threads, "kind": "port",
+           "sample": f"16 of 64 sequences x 36 layers x 32 heads ({sample_heads} head-states, best of 6 passes, {dt:.2f} s each), OpenMP "
+                     f"row-wise C restatement of the reference's ops path",
+           "ops_path": cpu_ops_sample(2)}
+    if isinstance(sd, dict) and "error" not in sd:
+        sd["cpu_baseline"] = cpu_sdpa_sample()
 
     line = {
         "metric": "replayed_head_states_per_s", "value": value, "unit": "head-states/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": workload_name(), "per_gpu_batch": "64 sequences (73728 head-states)",
-                   "global_batch": f"{64 * world} sequences", "parallelism": f"sequence-sharded x{world}, no collective",
-                   "l2": "inputs (5.4 GB) and outputs (5.1 GB) per step exceed the 126 MB L2; no flush needed",
+        "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": workload_name(), "global_batch": "64 sequences (73728 head-states)",
+                   "per_gpu_batch": f"{hi - lo} sequences on rank 0 ({'/'.join(str(e - b) for b, e in partition.plan(cfg['B_seq'], world))})",
+                   "parallelism": f"the batch's sequences dealt to {world} rank(s) in contiguous ranges, no collective",
+                   "l2": f"inputs plus outputs per GPU and step are {10.6 / world:.1f} GB, far above the 126 MB L2; no flush needed",
                    "seed": SEED + 1000},
-        "roofline": {"bound": "hbm", "kernel": "gdn_tc_kernel (bf16 inputs, forward with tape)", "achieved": achieved_gbs,
+        "roofline": {"bound": "hbm", "kernel": "gdn_tc_kernel (bf16 inputs; forward to the accepted length, y and state out, no tape written)",
+                     "achieved": achieved_gbs,
                      "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved_gbs / peaks["hbm_gbs"],
                      "peak_source": peaks["source"], "algorithmic_bytes_per_launch": alg_bytes,
-                     "kernel_ms": kernel_ms,
-                     "traffic": traffic * alg_bytes},
+                     "kernel_ms": kernel_ms, "units_per_launch": f"{(hi - lo) * heads_per_seq} head-states on rank 0",
+                     "traffic": traffic * alg_bytes, "traffic_source": "scaled from a profiled launch of the same kernel on 16 sequences"},
         "cpu_baseline": cpu,
         "e2e": {"value": e2e_value, "unit": "head-states/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "ms_per_step": e2e_ms, "steps": e2e_steps,
@@ -401,6 +442,7 @@ def run_gpu(args):
                         "sequence and pipelined on copy/compute streams"},
         "gpu_launches": launches,
         "clocks": clocks,
+        "weak_scaling": weak,
         "sdpa": sd,
         "replay_variants": variants,
         "sdpa_long": sd_long,

@@ -107,8 +107,14 @@ int32_t dflash_tape_replay(const float* tape, const void* k, const void* g, cons
  *   dense KV, page_table == NULL:   k,v [B,Hkv,N,D]
  *   paged KV, page_table != NULL:   k,v [num_pages,Hkv,page_tokens,D]; page_table int32
  *           [B,max_pages]; logical token n of sequence b lives in page page_table[b][n/page_tokens]
- *           at row n % page_tokens (page_tokens a multiple of 128; not part of the reference)
- *   kv_len_per_seq int32[B] or NULL (every sequence has N keys); 16 <= N_b <= N
+ *           at row n % page_tokens (page_tokens a multiple of 128; not part of the reference).
+ *           num_pages is the pool's page count: a table entry outside [0, num_pages) reads as
+ *           zero keys/values instead of memory outside the pool, and dflash_device_status then
+ *           returns DFLASH_ERR_DEVICE_DATA.  Ignored (pass 0) for dense KV.
+ *   kv_len_per_seq int32[B] or NULL (every sequence has N keys); 16 <= N_b <= N.  The array is
+ *           read on the device; an entry outside that range is clamped to [0, N] before any
+ *           address is formed from it and reported the same way (a sequence clamped to 0 keys
+ *           gets no output)
  *   mask    additive [B,Hq,16,N] dtype or NULL; a value < the most negative finite value of
  *           dtype hides the key (:551), otherwise it is added to the score (:553)
  *   workspace: dflash_verify_sdpa_workspace_bytes() bytes of device scratch (split-KV partials)
@@ -119,8 +125,8 @@ int32_t dflash_verify_sdpa(const void* q, const void* k, const void* v, const in
                            const int32_t* kv_len_per_seq, const void* mask, void* out,
                            void* workspace, size_t workspace_bytes, int32_t B, int32_t Hq,
                            int32_t Hkv, int32_t T, int32_t D, int32_t N, int32_t page_tokens,
-                           int32_t max_pages, float scale, int32_t dtype, int32_t kv_format,
-                           void* stream);
+                           int32_t max_pages, int32_t num_pages, float scale, int32_t dtype,
+                           int32_t kv_format, void* stream);
 
 size_t dflash_verify_sdpa_workspace_bytes(int32_t B, int32_t Hq, int32_t Hkv, int32_t D, int32_t N);
 /* The same for a given kv_format: DFLASH_KV_TURBO3 adds room for K and V expanded to `dtype`
@@ -133,15 +139,18 @@ size_t dflash_verify_sdpa_workspace_bytes_ex(int32_t B, int32_t Hq, int32_t Hkv,
  * that must never reach cudaMalloc).  It has no counterpart in the reference.  The split-KV
  * partials live in a 40 MiB device array that is part of the library image (every GPU that loads
  * the library holds it until exit): enough for head_dim <= 256 on up to 158 SMs; a call that needs
- * more returns DFLASH_ERR_WORKSPACE.  Nothing is allocated.  The first call on a device resolves
- * the array's address and loads the kernels: make it before any stream capture.  All calls share
- * the array (it keeps the previous call's contents; nothing needs clearing), so calls that
- * overlap on the GPU race: serialise them. */
+ * more returns DFLASH_ERR_WORKSPACE.  Dense or paged KV only: DFLASH_KV_TURBO3 is answered with
+ * DFLASH_ERR_UNSUPPORTED, because that form is expanded into scratch (B*Hkv*N*D*4 bytes) before
+ * attending.  Arguments are checked before the device is touched, so a bad call gets the same
+ * answer as from dflash_verify_sdpa.  Nothing is allocated.  The first valid call on a device
+ * resolves the array's address and loads the kernels: make it before any stream capture.  All
+ * calls share the array (it keeps the previous call's contents; nothing needs clearing), so calls
+ * that overlap on the GPU race: serialise them. */
 int32_t dflash_verify_sdpa_noalloc(const void* q, const void* k, const void* v, const int32_t* page_table,
                                    const int32_t* kv_len_per_seq, const void* mask, void* out, int32_t B,
                                    int32_t Hq, int32_t Hkv, int32_t T, int32_t D, int32_t N,
-                                   int32_t page_tokens, int32_t max_pages, float scale, int32_t dtype,
-                                   int32_t kv_format, void* stream);
+                                   int32_t page_tokens, int32_t max_pages, int32_t num_pages, float scale,
+                                   int32_t dtype, int32_t kv_format, void* stream);
 
 /* ---------------------------------------------------------------------------------------------
  * Acceptance bookkeeping on the device (no host round trip of the accepted length).
@@ -160,6 +169,14 @@ int32_t dflash_greedy_tokens(const void* logits, const uint8_t* suppress, uint32
 int32_t dflash_accept_lengths(const uint32_t* posterior, const int32_t* verify_ids, int32_t* accept,
                               int32_t* next_token, int32_t* replay_len, int32_t B, int32_t T,
                               void* stream);
+/* out[b,:] = logits[b, clamp(row_per_seq[b], 0, T-1), :]: the verify-logits row of each sequence's
+ * accepted position, i.e. the row whose argmax is next_token (posterior[acceptanceLen],
+ * Sources/DFlash/DFlashRuntime.swift:547), picked with the accepted count still on the device.
+ * This is the logits slice a sequence-sharded step all-gathers next to the acceptance results
+ * (a sampler or log-probability consumer on another rank needs that row, not the other T-1).
+ * logits [B,T,V] logits_dtype; row_per_seq int32[B] (accept of dflash_accept_lengths); out [B,V]. */
+int32_t dflash_gather_logits_rows(const void* logits, const int32_t* row_per_seq, void* out, int32_t B,
+                                  int32_t T, int32_t V, int32_t logits_dtype, void* stream);
 
 /* ---------------------------------------------------------------------------------------------
  * Conv-window rebuild of the rollback cache: replaces RecurrentRollbackCache.rebuildConvState,
@@ -185,8 +202,8 @@ int32_t dflash_rebuild_conv_state(const void* conv_snapshot, const void* qkv, co
  *   a dense cache  [B,Hkv,capacity,D]                       (page_table == NULL), or
  *   a paged pool   [num_pages,Hkv,page_tokens,D] through page_table int32[B,max_pages]
  *   (the layout dflash_verify_sdpa reads).
- * kv_len_out (int32[B] or NULL, not the same array as kv_len) receives kv_len[b] + T, the length
- * the verify attention must be given.  A position beyond the capacity, or on a page that is
+ * kv_len_out (int32[B] or NULL, not the same array as kv_len) receives min(kv_len[b] + T, capacity),
+ * the length the verify attention must be given.  A position beyond the capacity, or on a page that is
  * negative or >= num_pages, is skipped and dflash_device_status then returns
  * DFLASH_ERR_DEVICE_DATA.
  * dflash_kv_commit: kv_len[b] += clamp(commit[b], 0, T) with commit = replay_len of
@@ -229,8 +246,20 @@ int32_t dflash_turbo_decode(const uint8_t* packed, const uint8_t* signs, const u
 int32_t dflash_partition_plan(int32_t units, int32_t n_gpus, int32_t* begin_end_host);
 
 /* Reads (and clears) the device-side status word of the current device after synchronising
- * `stream`: 0, or DFLASH_ERR_DEVICE_TIMEOUT if a kernel's bounded wait gave up. */
+ * `stream`: 0; DFLASH_ERR_DEVICE_TIMEOUT if a kernel's bounded wait gave up (every device-side
+ * wait has a poll budget and the kernel returns when it runs out); DFLASH_ERR_DEVICE_DATA if a
+ * kernel met device-resident data out of range (a KV position past the capacity, a page id outside
+ * the pool, a kv_len_per_seq entry outside [16, N], a unit cut into more key ranges than the merge
+ * takes). */
 int32_t dflash_device_status(void* stream);
+
+/* Test hook, no counterpart in the reference: launches a two-warp kernel whose first warp waits, with
+ * a budget of `polls` polls (1 .. 2^20), on a barrier that nothing arrives at, and whose second warp
+ * must leave through the kernel's abort flag.  Exercises the give-up path of the bounded waits
+ * without faulting or hanging anything; afterwards dflash_device_status returns
+ * DFLASH_ERR_DEVICE_TIMEOUT once.  left_by_flag (device int32 or NULL) is set to 1 when the second
+ * warp left because of the flag. */
+int32_t dflash_selftest_bounded_wait(uint32_t polls, int32_t* left_by_flag, void* stream);
 
 int32_t dflash_device_count(void);
 const char* dflash_last_error_string(void);

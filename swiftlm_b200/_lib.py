@@ -21,12 +21,13 @@ _vp, _i32, _u64, _sz, _f32 = C.c_void_p, C.c_int32, C.c_uint64, C.c_size_t, C.c_
 SIGNATURES = {
     "dflash_gated_delta_tape": (_i32, [_vp] * 11 + [_i32] * 9 + [_vp]),
     "dflash_tape_replay": (_i32, [_vp] * 7 + [_i32] * 9 + [_vp]),
-    "dflash_verify_sdpa": (_i32, [_vp] * 8 + [_sz] + [_i32] * 8 + [_f32, _i32, _i32, _vp]),
+    "dflash_verify_sdpa": (_i32, [_vp] * 8 + [_sz] + [_i32] * 9 + [_f32, _i32, _i32, _vp]),
     "dflash_verify_sdpa_workspace_bytes_ex": (_sz, [_i32] * 6),
     "dflash_verify_sdpa_workspace_bytes": (_sz, [_i32] * 5),
-    "dflash_verify_sdpa_noalloc": (_i32, [_vp] * 7 + [_i32] * 8 + [_f32, _i32, _i32, _vp]),
+    "dflash_verify_sdpa_noalloc": (_i32, [_vp] * 7 + [_i32] * 9 + [_f32, _i32, _i32, _vp]),
     "dflash_greedy_tokens": (_i32, [_vp, _vp, _vp, _i32, _i32, _i32, _vp]),
     "dflash_accept_lengths": (_i32, [_vp] * 5 + [_i32, _i32, _vp]),
+    "dflash_gather_logits_rows": (_i32, [_vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp]),
     "dflash_rebuild_conv_state": (_i32, [_vp, _vp, _vp, _i32, _vp, _i32, _i32, _i32, C.c_int64, C.POINTER(_i32), _vp]),
     "dflash_kv_append": (_i32, [_vp] * 6 + [_i32, _vp] + [_i32] * 9 + [_vp]),
     "dflash_kv_commit": (_i32, [_vp, _vp, _i32, _i32, _vp]),
@@ -34,6 +35,7 @@ SIGNATURES = {
     "dflash_turbo_decode": (_i32, [_vp] * 5 + [C.c_int64, _i32, _i32, _vp]),
     "dflash_partition_plan": (_i32, [_i32, _i32, C.POINTER(_i32)]),
     "dflash_device_status": (_i32, [_vp]),
+    "dflash_selftest_bounded_wait": (_i32, [C.c_uint32, _vp, _vp]),
     "dflash_device_count": (_i32, []),
     "dflash_last_error_string": (C.c_char_p, []),
     "dflash_launch_count": (_u64, []),

@@ -101,6 +101,28 @@ int32_t check_gdn_shape(int B, int T, int Hk, int Hv, int Dk, int Dv, int dtype,
 }
 
 }  // namespace
+
+// Everything dflash_verify_sdpa can reject before it touches the device; shared with the entry point
+// that brings its own scratch so that both answer a bad call the same way.
+int32_t sdpa_check_args(const void* q, const void* k, const void* v, const int32_t* page_table, const void* out,
+                        int32_t B, int32_t Hq, int32_t Hkv, int32_t T, int32_t D, int32_t N, int32_t page_tokens,
+                        int32_t max_pages, int32_t num_pages, int32_t dtype, int32_t kv_format) {
+  if (!q || !k || (!v && kv_format == DFLASH_KV_DENSE) || !out) return bad("null tensor pointer");
+  if (B <= 0 || Hq <= 0 || Hkv <= 0 || N <= 0) return bad("non-positive dimension");
+  // eligibility of the reference's kernel, Sources/DFlash/DFlashKernels.swift:755-758
+  if (T != 16) { set_error("unsupported query length %d (the verify block has 16 rows)", T); return DFLASH_ERR_UNSUPPORTED; }
+  if (dtype != DFLASH_BF16 && dtype != DFLASH_F16) { set_error("unsupported dtype %d (bf16 or f16)", dtype); return DFLASH_ERR_UNSUPPORTED; }
+  if (D != 128 && D != 256) { set_error("unsupported head_dim %d (128 or 256)", D); return DFLASH_ERR_UNSUPPORTED; }
+  if (Hq % Hkv != 0) { set_error("unsupported heads: Hq=%d not a multiple of Hkv=%d", Hq, Hkv); return DFLASH_ERR_UNSUPPORTED; }
+  if (N < 16) { set_error("unsupported N=%d: the 16 block keys are part of the KV", N); return DFLASH_ERR_UNSUPPORTED; }
+  if (kv_format != DFLASH_KV_DENSE && kv_format != DFLASH_KV_TURBO3) { set_error("unsupported kv_format %d in dflash_verify_sdpa", kv_format); return DFLASH_ERR_UNSUPPORTED; }
+  if (page_table && (page_tokens <= 0 || page_tokens % 128 != 0 || max_pages <= 0 || num_pages <= 0 ||
+                     (long long)max_pages * page_tokens < N))
+    return bad("paged KV needs page_tokens % 128 == 0, max_pages * page_tokens >= N and the pool's num_pages");
+  if (kv_format == DFLASH_KV_DENSE && (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(out)))
+    return bad("tensor base pointers must be 16-byte aligned");
+  return DFLASH_OK;
+}
 }  // namespace dflash
 
 using namespace dflash;
@@ -120,9 +142,7 @@ int32_t dflash_gated_delta_tape(const void* q, const void* k, const void* v, con
   GdnArgs a{q, k, v, g, beta, state_in, mask, n_per_seq, y, state_out, tape,
             B, T, Hk, Hv, Dk, Dv, g_is_vector ? 1 : 0, in_dtype, mask_dtype, false};
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-  // DFLASH_GDN_TC=0 keeps the block on the CUDA-core kernel (for comparisons)
-  static const bool use_tc = [] { const char* e = getenv("DFLASH_GDN_TC"); return !(e && e[0] == '0'); }();
-  if (use_tc && gdn_tc_supported(a)) return launch_gdn_tc(a, s);
+  if (gdn_tc_supported(a)) return launch_gdn_tc(a, s);
   if (gdn_fast_supported(a)) return launch_gdn_fast(a, s);
   return launch_gdn_generic(a, s);
 }
@@ -145,17 +165,9 @@ int32_t dflash_tape_replay(const float* tape, const void* k, const void* g, cons
 int32_t dflash_verify_sdpa(const void* q, const void* k, const void* v, const int32_t* page_table,
                            const int32_t* kv_len_per_seq, const void* mask, void* out, void* workspace,
                            size_t workspace_bytes, int32_t B, int32_t Hq, int32_t Hkv, int32_t T,
-                           int32_t D, int32_t N, int32_t page_tokens, int32_t max_pages, float scale,
-                           int32_t dtype, int32_t kv_format, void* stream) {
-  if (!q || !k || (!v && kv_format == DFLASH_KV_DENSE) || !out) return bad("null tensor pointer");
-  if (B <= 0 || Hq <= 0 || Hkv <= 0 || N <= 0) return bad("non-positive dimension");
-  // eligibility of the reference's kernel, Sources/DFlash/DFlashKernels.swift:755-758
-  if (T != 16) { set_error("unsupported query length %d (the verify block has 16 rows)", T); return DFLASH_ERR_UNSUPPORTED; }
-  if (dtype != DFLASH_BF16 && dtype != DFLASH_F16) { set_error("unsupported dtype %d (bf16 or f16)", dtype); return DFLASH_ERR_UNSUPPORTED; }
-  if (D != 128 && D != 256) { set_error("unsupported head_dim %d (128 or 256)", D); return DFLASH_ERR_UNSUPPORTED; }
-  if (Hq % Hkv != 0) { set_error("unsupported heads: Hq=%d not a multiple of Hkv=%d", Hq, Hkv); return DFLASH_ERR_UNSUPPORTED; }
-  if (N < 16) { set_error("unsupported N=%d: the 16 block keys are part of the KV", N); return DFLASH_ERR_UNSUPPORTED; }
-  if (kv_format != DFLASH_KV_DENSE && kv_format != DFLASH_KV_TURBO3) { set_error("unsupported kv_format %d in dflash_verify_sdpa", kv_format); return DFLASH_ERR_UNSUPPORTED; }
+                           int32_t D, int32_t N, int32_t page_tokens, int32_t max_pages, int32_t num_pages,
+                           float scale, int32_t dtype, int32_t kv_format, void* stream) {
+  if (int32_t st = sdpa_check_args(q, k, v, page_table, out, B, Hq, Hkv, T, D, N, page_tokens, max_pages, num_pages, dtype, kv_format)) return st;
   if (kv_format == DFLASH_KV_TURBO3) {
     // expand K and V into the front of the workspace, then attend over the expanded copy
     if (page_table) { set_error("TurboQuant KV behind a page table is not supported"); return DFLASH_ERR_UNSUPPORTED; }
@@ -185,15 +197,11 @@ int32_t dflash_verify_sdpa(const void* q, const void* k, const void* v, const in
       DFLASH_CUDA_CHECK(cudaMemcpy2DAsync(ws + kv_bytes + off, pitch, t->v_hot, row, row, (size_t)pairs, cudaMemcpyDeviceToDevice, s));
     }
     return dflash_verify_sdpa(q, ws, ws + kv_bytes, nullptr, kv_len_per_seq, mask, out, ws + 2 * kv_bytes, workspace_bytes - 2 * kv_bytes,
-                              B, Hq, Hkv, T, D, N, 0, 0, scale, dtype, DFLASH_KV_DENSE, stream);
+                              B, Hq, Hkv, T, D, N, 0, 0, 0, scale, dtype, DFLASH_KV_DENSE, stream);
   }
-  if (page_table && (page_tokens <= 0 || page_tokens % 128 != 0 || max_pages <= 0 ||
-                     (long long)max_pages * page_tokens < N))
-    return bad("paged KV needs page_tokens % 128 == 0 and max_pages * page_tokens >= N");
-  if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(out) || (workspace && !aligned16(workspace)))
-    return bad("tensor base pointers must be 16-byte aligned");
+  if (workspace && !aligned16(workspace)) return bad("tensor base pointers must be 16-byte aligned");
   SdpaArgs a{q, k, v, page_table, kv_len_per_seq, mask, out, workspace, workspace_bytes,
-             B, Hq, Hkv, D, N, page_tokens, max_pages, scale, dtype};
+             B, Hq, Hkv, D, N, page_tokens, max_pages, page_table ? num_pages : 0, scale, dtype};
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   if (sdpa_tc_supported(a)) return launch_sdpa_tc(a, s);
   return launch_sdpa_simple(a, s);
@@ -226,6 +234,19 @@ int32_t dflash_accept_lengths(const uint32_t* posterior, const int32_t* verify_i
   if (B <= 0 || T <= 0) return bad("non-positive dimension");
   return launch_accept_lengths(posterior, verify_ids, accept, next_token, replay_len, B, T,
                                reinterpret_cast<cudaStream_t>(stream));
+}
+
+int32_t dflash_gather_logits_rows(const void* logits, const int32_t* row_per_seq, void* out, int32_t B, int32_t T,
+                                  int32_t V, int32_t logits_dtype, void* stream) {
+  if (!logits || !row_per_seq || !out) return bad("null tensor pointer");
+  if (B <= 0 || T <= 0 || V <= 0) return bad("non-positive dimension");
+  if (logits_dtype != DFLASH_F32 && logits_dtype != DFLASH_BF16 && logits_dtype != DFLASH_F16) {
+    set_error("gather_logits_rows: unsupported logits dtype %d", logits_dtype);
+    return DFLASH_ERR_UNSUPPORTED;
+  }
+  const long long row_bytes = (long long)V * (long long)dtype_size(logits_dtype);
+  if (row_bytes % 16 == 0 && (!aligned16(logits) || !aligned16(out))) return bad("tensor base pointers must be 16-byte aligned");
+  return launch_gather_rows(logits, row_per_seq, out, B, T, row_bytes, reinterpret_cast<cudaStream_t>(stream));
 }
 
 int32_t dflash_turbo_encode(const void* x, uint8_t* packed, uint8_t* signs, uint16_t* norm, uint16_t* rnorm,
@@ -268,16 +289,25 @@ int32_t dflash_device_status(void* stream) {
   if (host != 0) {
     DFLASH_CUDA_CHECK(cudaMemsetAsync(word, 0, sizeof(int), s));
     DFLASH_CUDA_CHECK(cudaStreamSynchronize(s));
-    if (host == 16) {   // kStatusKvRange, kv_cache.cu
-      set_error("kv_append skipped a row: position beyond the cache's capacity or on an unmapped page");
-      return DFLASH_ERR_DEVICE_DATA;
+    switch (host) {
+      case kStatusKvRange:
+        set_error("a KV position beyond the cache's capacity, or a page id outside the pool: kv_append skipped the row / "
+                  "verify_sdpa read the page as zeros");
+        return DFLASH_ERR_DEVICE_DATA;
+      case kStatusKvLen:
+        set_error("verify_sdpa: a kv_len_per_seq entry outside [16, N] was clamped; that sequence's output is not the attention "
+                  "over its keys (no output at all for a length <= 0)");
+        return DFLASH_ERR_DEVICE_DATA;
+      case kStatusMergeRanges:
+        set_error("verify_sdpa: a unit was cut into more key ranges than the merge kernel takes; its output is incomplete");
+        return DFLASH_ERR_DEVICE_DATA;
+      case kStatusSmemAlign:
+        set_error("a kernel found its shared-memory window misaligned and did not run");
+        return DFLASH_ERR_CUDA;
+      default:
+        set_error("a device-side bounded wait gave up (code %d)", host);
+        return DFLASH_ERR_DEVICE_TIMEOUT;
     }
-    if (host == 6) {
-      set_error("verify_sdpa: a unit was cut into more key ranges than the merge kernel takes; its output is incomplete");
-      return DFLASH_ERR_DEVICE_DATA;
-    }
-    set_error("a device-side bounded wait gave up (code %d)", host);
-    return DFLASH_ERR_DEVICE_TIMEOUT;
   }
   return DFLASH_OK;
 }

@@ -85,7 +85,34 @@ __global__ void accept_kernel(const uint32_t* __restrict__ posterior, const int3
   if (replay_len) replay_len[b] = acc + 1;
 }
 
+// out[b, :] = logits[b, clamp(row[b], 0, T-1), :] as raw bytes (16-byte copies where the row allows it): the
+// logits row that produced a sequence's next token, picked with the accepted count still on the device.
+__global__ void __launch_bounds__(256) gather_rows_kernel(const uint8_t* __restrict__ logits, const int32_t* __restrict__ row,
+                                                          uint8_t* __restrict__ out, int T, long long row_bytes) {
+  const int b = blockIdx.y;
+  int r = row[b];
+  r = r < 0 ? 0 : (r >= T ? T - 1 : r);
+  const uint8_t* src = logits + ((long long)b * T + r) * row_bytes;
+  uint8_t* dst = out + (long long)b * row_bytes;
+  const long long i0 = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 16, stride = (long long)gridDim.x * blockDim.x * 16;
+  if (row_bytes % 16 == 0) {
+    for (long long i = i0; i < row_bytes; i += stride) *reinterpret_cast<uint4*>(dst + i) = *reinterpret_cast<const uint4*>(src + i);
+  } else {
+    for (long long i = i0; i < row_bytes; i += stride)
+      for (int j = 0; j < 16 && i + j < row_bytes; ++j) dst[i + j] = src[i + j];
+  }
+}
+
 }  // namespace
+
+int32_t launch_gather_rows(const void* logits, const int32_t* row, void* out, int B, int T, long long row_bytes, cudaStream_t stream) {
+  const int chunks = (int)((row_bytes / 16 + 255) / 256);
+  gather_rows_kernel<<<dim3(chunks < 1 ? 1 : (chunks > 64 ? 64 : chunks), B), 256, 0, stream>>>(
+      reinterpret_cast<const uint8_t*>(logits), row, reinterpret_cast<uint8_t*>(out), T, row_bytes);
+  DFLASH_LAUNCH_CHECK();
+  count_launch();
+  return DFLASH_OK;
+}
 
 int32_t launch_greedy_tokens(const void* logits, const uint8_t* suppress, uint32_t* posterior, int rows,
                              int V, int logits_dtype, cudaStream_t stream) {

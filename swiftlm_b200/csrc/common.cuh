@@ -17,6 +17,23 @@ void count_launch(int n = 1);
 int* device_status_word();
 int sm_count();
 
+// Codes a kernel leaves in the per-device status word; dflash_device_status maps them to a
+// dflash_status in one place (abi.cu).  Codes below 16 are bounded waits that gave up
+// (DFLASH_ERR_DEVICE_TIMEOUT) except where noted; 16 and above are device-resident data out of
+// range (DFLASH_ERR_DEVICE_DATA).
+enum DeviceStatusCode : int {
+  kStatusGdnWait = 1,        // gated-delta kernels: an mbarrier wait gave up
+  kStatusMbarWait = 2,       // attention: an mbarrier wait gave up
+  kStatusExchangeWait = 3,   // attention: the two half-row softmax threads never met
+  kStatusSmemAlign = 4,      // dynamic shared memory window not 1024-byte aligned (never seen)
+  kStatusGroupWait = 5,      // attention: meeting point of the softmax warps
+  kStatusPeerWait = 6,       // attention: the cluster partner never arrived
+  kStatusMergeRanges = 7,    // merge kernel: a unit was cut into more key ranges than it takes (data, not a wait)
+  kStatusSelftestWait = 8,   // dflash_selftest_bounded_wait: the wait that nothing satisfies gave up (as it must)
+  kStatusKvRange = 16,       // a KV position beyond the capacity, or a page id outside the pool
+  kStatusKvLen = 17,         // attention: a kv_len_per_seq entry outside [16, N] (clamped)
+};
+
 #define DFLASH_CUDA_CHECK(expr)                                                          \
   do {                                                                                   \
     cudaError_t _e = (expr);                                                             \
@@ -106,12 +123,17 @@ struct SdpaArgs {
   void* out;
   void* workspace;
   size_t workspace_bytes;
-  int B, Hq, Hkv, D, N, page_tokens, max_pages;
+  int B, Hq, Hkv, D, N, page_tokens, max_pages, num_pages;
   float scale;
   int dtype;
 };
 
 size_t sdpa_workspace_bytes(int B, int Hq, int Hkv, int D, int N);
+// Scratch of the kernel a call will actually run on, given a workspace at least this large.
+size_t sdpa_scratch_bytes_for_call(int B, int Hq, int D, float scale, bool ragged);
+int32_t sdpa_check_args(const void* q, const void* k, const void* v, const int32_t* page_table, const void* out,
+                        int32_t B, int32_t Hq, int32_t Hkv, int32_t T, int32_t D, int32_t N, int32_t page_tokens,
+                        int32_t max_pages, int32_t num_pages, int32_t dtype, int32_t kv_format);
 int32_t launch_sdpa_simple(const SdpaArgs& a, cudaStream_t stream);
 bool sdpa_tc_supported(const SdpaArgs& a);
 int32_t launch_sdpa_tc(const SdpaArgs& a, cudaStream_t stream);
@@ -121,6 +143,9 @@ int32_t launch_greedy_tokens(const void* logits, const uint8_t* suppress, uint32
 int32_t launch_accept_lengths(const uint32_t* posterior, const int32_t* verify_ids, int32_t* accept,
                               int32_t* next_token, int32_t* replay_len, int B, int T,
                               cudaStream_t stream);
+
+int32_t launch_gather_rows(const void* logits, const int32_t* row, void* out, int B, int T, long long row_bytes,
+                           cudaStream_t stream);
 
 int32_t launch_turbo_encode(const void* x, uint8_t* packed, uint8_t* signs, uint16_t* norm, uint16_t* rnorm,
                             long long n, int is_key, int in_dtype, cudaStream_t stream);

@@ -278,7 +278,7 @@ gdn_fast_kernel(const __grid_constant__ CUtensorMap state_map, const GdnArgs a, 
     phase ^= 1u;
     ptx::cp_async_wait_all();
     if (__syncthreads_or(!arrived)) {
-      if (tid == 0) atomicExch(status, 1);
+      if (tid == 0) atomicExch(status, kStatusGdnWait);
       return;  // the wait budget ran out: report and leave
     }
     const uint32_t bits = s_bits[it % 3];

@@ -120,7 +120,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 gdn_tc_kernel(const __grid_constant__ TcMaps maps, const GdnArgs a, int* status) {
   extern __shared__ __align__(1024) uint8_t sm[];
   if ((ptx::smem_u32(sm) & 1023u) != 0u) {
-    if (threadIdx.x == 0) atomicExch(status, 4);
+    if (threadIdx.x == 0) atomicExch(status, kStatusSmemAlign);
     return;
   }
   const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
@@ -641,7 +641,7 @@ gdn_tc_kernel(const __grid_constant__ TcMaps maps, const GdnArgs a, int* status)
   }
 
   PH_FLUSH();
-  if (failed && lane == 0) atomicExch(status, 1);
+  if (failed && lane == 0) atomicExch(status, kStatusGdnWait);
   if (tid == 0) ptx::bulk_wait_all();   // shared memory must outlive the last store
   ptx::tc_fence_before();
   __syncthreads();

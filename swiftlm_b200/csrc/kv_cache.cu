@@ -16,8 +16,6 @@
 
 namespace dflash {
 
-constexpr int kStatusKvRange = 16;
-
 namespace {
 
 constexpr int kRowsPerBlock = 8;
@@ -44,7 +42,11 @@ __global__ void __launch_bounds__(kRowsPerBlock * 32) kv_append_kernel(const App
   const int h = (int)((row / p.T) % p.Hkv);
   const int b = (int)(row / ((long long)p.T * p.Hkv));
   const int base = p.kv_len ? p.kv_len[b] : p.len_all;
-  if (p.kv_len_out && h == 0 && t == 0 && lane == 0) p.kv_len_out[b] = base + p.T;
+  if (p.kv_len_out && h == 0 && t == 0 && lane == 0) {
+    // never hand the attention a length past the cache: rows that did not fit were skipped (and reported)
+    const long long want = (long long)(base < 0 ? 0 : base) + p.T;
+    p.kv_len_out[b] = (int)(want < p.capacity ? want : p.capacity);
+  }
   const int pos = base + t;
   long long dst_row = -1;
   if (base >= 0 && pos < p.capacity) {

@@ -46,11 +46,27 @@ __device__ __forceinline__ bool mbar_try_wait(void* bar, uint32_t parity) {
 // Bounded wait.  Returns false if the phase did not complete within the poll budget
 // (each poll may itself block for a hardware-defined short time).
 constexpr uint32_t kWaitPolls = 1u << 22;
-__device__ __forceinline__ bool mbar_wait(void* bar, uint32_t parity) {
-  for (uint32_t i = 0; i < kWaitPolls; ++i) {
+__device__ __forceinline__ bool mbar_wait(void* bar, uint32_t parity, uint32_t polls = kWaitPolls) {
+  for (uint32_t i = 0; i < polls; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
     if (i > 64) __nanosleep(32);
   }
+  return false;
+}
+// Bounded wait of a kernel whose roles unwind together: gives up after `polls` polls, or as soon as another
+// role has given up (the CTA's abort flag).  The first to give up raises the flag and records `code` in the
+// device status word.  Returns false when the phase was not seen complete.
+__device__ __forceinline__ bool mbar_wait_or_abort(void* bar, uint32_t parity, volatile int* abort_flag, int* status,
+                                                   int code, uint32_t polls = kWaitPolls) {
+  for (uint32_t i = 0; i < polls; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((i & 63u) == 63u) {
+      if (*abort_flag) return false;
+      __nanosleep(40);
+    }
+  }
+  *abort_flag = 1;
+  atomicExch(status, code);
   return false;
 }
 

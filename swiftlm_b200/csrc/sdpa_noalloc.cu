@@ -28,7 +28,7 @@ namespace dflash {
 namespace {
 
 // 40 MiB: enough for head_dim <= 256 on a GPU with up to 158 SMs (2 partial slots per SM, each
-// 128 rows x (head_dim + 2) floats) and for the additive-mask path at any batch size.
+// 128 rows x (head_dim + 2) floats).
 constexpr size_t kScratchBytes = 40u << 20;
 static __device__ __align__(256) unsigned char g_sdpa_scratch[kScratchBytes];
 
@@ -61,22 +61,31 @@ extern "C" int32_t dflash_verify_sdpa_noalloc(const void* q, const void* k, cons
                                               const int32_t* page_table, const int32_t* kv_len_per_seq,
                                               const void* mask, void* out, int32_t B, int32_t Hq, int32_t Hkv,
                                               int32_t T, int32_t D, int32_t N, int32_t page_tokens,
-                                              int32_t max_pages, float scale, int32_t dtype, int32_t kv_format,
-                                              void* stream) {
+                                              int32_t max_pages, int32_t num_pages, float scale, int32_t dtype,
+                                              int32_t kv_format, void* stream) {
   using namespace dflash;
-  if (B <= 0 || Hq <= 0 || Hkv <= 0 || D <= 0 || N <= 0) {
-    set_error("invalid argument: non-positive dimension");
-    return DFLASH_ERR_INVALID_ARG;
+  // 1. everything that can be rejected without touching the device, exactly as dflash_verify_sdpa answers it
+  if (int32_t st = sdpa_check_args(q, k, v, page_table, out, B, Hq, Hkv, T, D, N, page_tokens, max_pages, num_pages,
+                                   dtype, kv_format))
+    return st;
+  if (kv_format != DFLASH_KV_DENSE) {
+    // the compressed form is expanded into scratch before attending: B*Hkv*N*D*4 bytes, which the built-in
+    // area cannot hold for any realistic context
+    set_error("verify_sdpa_noalloc: TurboQuant KV is not taken here (its expansion needs B*Hkv*N*D*4 bytes of scratch); "
+              "use dflash_verify_sdpa with a workspace");
+    return DFLASH_ERR_UNSUPPORTED;
   }
-  const size_t need = sdpa_workspace_bytes(B, Hq, Hkv, D, N);
+  // 2. the scratch the kernel that will run needs (the tensor-core kernel for every call it takes)
+  const size_t need = sdpa_scratch_bytes_for_call(B, Hq, D, scale, kv_len_per_seq != nullptr);
   if (need > kScratchBytes) {
     set_error("verify_sdpa_noalloc: this call needs %zu bytes of scratch but the built-in area holds %zu "
               "(head_dim <= 256 on up to 158 SMs); use dflash_verify_sdpa with a workspace",
               need, (size_t)kScratchBytes);
     return DFLASH_ERR_WORKSPACE;
   }
+  // 3. only now the device: the array's address (first call on this device), then the launch
   void* scratch = nullptr;
   if (int32_t st = scratch_for_current_device(&scratch)) return st;
   return dflash_verify_sdpa(q, k, v, page_table, kv_len_per_seq, mask, out, scratch, kScratchBytes, B, Hq, Hkv, T, D,
-                            N, page_tokens, max_pages, scale, dtype, kv_format, stream);
+                            N, page_tokens, max_pages, num_pages, scale, dtype, kv_format, stream);
 }

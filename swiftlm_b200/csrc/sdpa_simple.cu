@@ -44,7 +44,8 @@ __global__ void __launch_bounds__(kRows * 32) sdpa_simple_kernel(SimpleParams p)
   const int b = bh / a.Hq, h = bh % a.Hq;
   const int hk = h / (a.Hq / a.Hkv);
   const int dpt = a.D >> 5;
-  const int Nb = a.kv_len ? a.kv_len[b] : a.N;
+  int Nb = a.kv_len ? a.kv_len[b] : a.N;
+  Nb = Nb < 0 ? 0 : (Nb > a.N ? a.N : Nb);   // a length outside [0, N] is clamped (the tensor-core kernel reports it)
   const int chunk = (Nb + p.splits - 1) / p.splits;
   const int n0 = split * chunk, n1 = min(Nb, n0 + chunk);
   const int last = Nb - kRows + r;  // last visible key of this row
@@ -65,6 +66,7 @@ __global__ void __launch_bounds__(kRows * 32) sdpa_simple_kernel(SimpleParams p)
     long long row_off;
     if (a.page_table) {
       const int page = a.page_table[(long long)b * a.max_pages + n / a.page_tokens];
+      if (page < 0 || (a.num_pages > 0 && page >= a.num_pages)) continue;   // a page id outside the pool hides its keys
       row_off = (((long long)page * a.Hkv + hk) * a.page_tokens + n % a.page_tokens) * a.D;
     } else {
       row_off = (((long long)b * a.Hkv + hk) * a.N + n) * a.D;

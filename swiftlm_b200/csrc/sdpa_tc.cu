@@ -6,7 +6,8 @@
 // (128 FLOP/B), so the kernel is organised around keeping TMA loads in flight; the tensor
 // pipe and the softmax run in the shadow of the loads.
 //
-// One persistent CTA per SM (no cluster, cta_group::1, no multicast), 10 warps:
+// One persistent CTA per SM (cta_group::1, no multicast; the cluster-pair split regime below launches
+// two-CTA clusters that exchange through distributed shared memory), 10 warps:
 //   warp 0     TMA producer: Q tile (4 boxes of 128 rows x 64 elements) and a ring of 16 KiB
 //              K / V boxes (128 keys x 64 elements, 128-byte swizzle), order K0 K1 V0 K2 V1 ...
 //   warp 1     MMA issuer (one lane): S = Q K^T (128 x 128 x D, both operands in shared memory,
@@ -158,10 +159,14 @@ __device__ __forceinline__ int cta_of(const TcParams& p, long long total, long l
   return (int)(((pos + 1) * C - 1) / total);
 }
 
-__device__ __forceinline__ int tiles_of(const TcParams& p, int b) {
-  const int n = p.a.kv_len ? p.a.kv_len[b] : p.a.N;
-  return (n + kBlockN - 1) / kBlockN;
+// Keys of sequence b.  A device-resident length outside [0, N] is clamped here (and reported once per launch by
+// CTA 0): nothing downstream may index the page table or the tensor maps with it unclamped.
+__device__ __forceinline__ int keys_of(const TcParams& p, int b) {
+  if (!p.a.kv_len) return p.a.N;
+  const int n = p.a.kv_len[b];
+  return n < 0 ? 0 : (n > p.a.N ? p.a.N : n);
 }
+__device__ __forceinline__ int tiles_of(const TcParams& p, int b) { return (keys_of(p, b) + kBlockN - 1) / kBlockN; }
 
 // Iterates the segments of one CTA's tile range.  All roles run the same iterator.
 struct SegmentIter {
@@ -174,11 +179,14 @@ struct SegmentIter {
   __device__ bool next(Segment& s) {
     if (pos >= end) return false;
     const int per_b = p.a.Hkv * p.MT;
+    // a sequence without keys (length clamped to 0) has no tiles and owns no tile positions: pass over its units
+    while (p.a.kv_len && unit < p.units && keys_of(p, unit / per_b) == 0) unit += per_b - unit % per_b;
+    if (unit >= p.units) return false;
     s.unit = unit;
     s.b = unit / per_b;
     s.kvh = (unit / p.MT) % p.a.Hkv;
     s.mt = unit % p.MT;
-    s.n_keys = p.a.kv_len ? p.a.kv_len[s.b] : p.a.N;
+    s.n_keys = keys_of(p, s.b);
     s.tiles_in_unit = (s.n_keys + kBlockN - 1) / kBlockN;
     s.tile_lo = tile;
     const long long left = end - pos;
@@ -205,16 +213,7 @@ __device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr, uint32_t lbo_b
 }
 
 __device__ __forceinline__ bool wait_or_abort(void* bar, uint32_t parity, volatile int* abort_flag, int* status) {
-  for (uint32_t i = 0; i < ptx::kWaitPolls; ++i) {
-    if (ptx::mbar_try_wait(bar, parity)) return true;
-    if ((i & 63u) == 63u) {
-      if (*abort_flag) return false;
-      __nanosleep(40);
-    }
-  }
-  *abort_flag = 1;
-  atomicExch(status, 2);
-  return false;
+  return ptx::mbar_wait_or_abort(bar, parity, abort_flag, status, kStatusMbarWait);
 }
 
 __device__ __forceinline__ float fast_exp2(float x) {   // ex2.approx: exp2(-inf) = +0
@@ -267,7 +266,7 @@ __device__ __forceinline__ bool wait_peer_or_abort(void* bar, uint32_t parity, v
     }
   }
   *abort_flag = 1;
-  atomicExch(status, 6);
+  atomicExch(status, kStatusPeerWait);
   return false;
 }
 
@@ -332,7 +331,7 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* sm = smem_raw;
   if ((ptx::smem_u32(sm) & 1023u) != 0u) {   // swizzled tiles need 1024-byte alignment; never seen violated
-    if (threadIdx.x == 0) atomicExch(p.status, 4);
+    if (threadIdx.x == 0) atomicExch(p.status, kStatusSmemAlign);
     return;
   }
   uint64_t* bars = reinterpret_cast<uint64_t*>(sm + SL::bars);
@@ -350,8 +349,14 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
   if (a.kv_len) {
     // ragged lengths: every CTA sums the per-sequence tile counts itself (B is small)
     long long sum = 0;
-    for (int b = 0; b < a.B; ++b) sum += tiles_of(p, b);
+    bool in_range = true;
+    for (int b = 0; b < a.B; ++b) {
+      sum += tiles_of(p, b);
+      const int n = a.kv_len[b];
+      in_range = in_range && n >= 16 && n <= a.N;
+    }
     total = sum * a.Hkv * p.MT;
+    if (!in_range && blockIdx.x == 0 && threadIdx.x == 0) atomicExch(p.status, kStatusKvLen);
   }
   long long begin, end;
   cta_range(p, total, blockIdx.x, begin, end);
@@ -438,7 +443,12 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         if (a.page_table) {
           if (c == 0) {
             const int index = n0 / a.page_tokens;
-            if (index != ref.index || sg.b != ref.b) ref = PageRef{sg.b, index, a.page_table[(long long)sg.b * a.max_pages + index]};
+            if (index != ref.index || sg.b != ref.b) {
+              // index < max_pages because n0 < N <= max_pages * page_tokens (host check, lengths clamped to N).
+              // A page id outside the pool reads as zeros (the tensor map ends at num_pages) and is reported.
+              ref = PageRef{sg.b, index, a.page_table[(long long)sg.b * a.max_pages + index]};
+              if ((unsigned)ref.page >= (unsigned)a.num_pages) { ref.page = a.num_pages; atomicExch(p.status, kStatusKvRange); }
+            }
           }
           ptx::tma_load_4d(sm + SL::ring + stage * kChunkBytes, map, c * 64, n0 - ref.index * a.page_tokens, sg.kvh, ref.page,
                            &bars[SL::b_kv_full + stage]);
@@ -593,7 +603,7 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       }
       got = __all_sync(0xffffffffu, got);
       if (!got) {
-        if (lane == 0 && !*abort_flag) { *abort_flag = 1; atomicExch(p.status, 3); }
+        if (lane == 0 && !*abort_flag) { *abort_flag = 1; atomicExch(p.status, kStatusExchangeWait); }
         return false;
       }
       __threadfence_block();
@@ -619,7 +629,7 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       }
       got = __all_sync(0xffffffffu, got);
       if (!got) {
-        if (lane == 0 && !*abort_flag) { *abort_flag = 1; atomicExch(p.status, 5); }
+        if (lane == 0 && !*abort_flag) { *abort_flag = 1; atomicExch(p.status, kStatusGroupWait); }
         return false;
       }
       __threadfence_block();
@@ -1049,7 +1059,7 @@ __global__ void __launch_bounds__(128) sdpa_tc_merge_kernel(const TcParams p, in
     }
     if (threadIdx.x == 0) {
       s_count = count;
-      if (count > kMaxRanges) atomicExch(p.status, 6);
+      if (count > kMaxRanges) atomicExch(p.status, kStatusMergeRanges);
     }
   }
   __syncthreads();
@@ -1149,7 +1159,7 @@ int32_t launch_typed(const SdpaArgs& a, cudaStream_t stream) {
   bool need_merge_kernel = true;
   if (!a.kv_len) {
     const int c = n_sm / p.units;
-    static const int mode = [] { const char* e = getenv("DFLASH_SDPA_SPLIT"); return e ? atoi(e) : -1; }();   // -1 auto, 0 stream-K
+    constexpr int mode = -1;   // -1: choose; 0: always stream-K; > 0: equal cuts whenever they apply (for experiments, at compile time)
     // Equal cuts leave n_sm - units * c SMs idle.  With long units that costs more than stream-K's partials and merge
     // (measured: about ten key tiles' worth of time): B=60, N=16400 runs 12 % faster as stream-K, B=64, N=4112 4 % slower.
     const double idle_tiles = c >= 1 ? (double)tiles_per_unit / c * (1.0 - (double)p.units * c / n_sm) : 0.0;
@@ -1194,8 +1204,8 @@ int32_t launch_typed(const SdpaArgs& a, cudaStream_t stream) {
   auto encode_kv = [&](CUtensorMap* m, const void* base) -> CUresult {
     cuuint64_t dims[4], strides[3];
     if (a.page_table) {
-      // pool [num_pages, Hkv, page_tokens, D]; the page count is not passed: bound it by the table's range
-      dims[0] = D; dims[1] = a.page_tokens; dims[2] = a.Hkv; dims[3] = (cuuint64_t)1 << 22;
+      // pool [num_pages, Hkv, page_tokens, D]: a page coordinate at or beyond num_pages is filled with zeros
+      dims[0] = D; dims[1] = a.page_tokens; dims[2] = a.Hkv; dims[3] = (cuuint64_t)a.num_pages;
       strides[0] = (cuuint64_t)D * 2; strides[1] = (cuuint64_t)a.page_tokens * D * 2; strides[2] = (cuuint64_t)a.Hkv * a.page_tokens * D * 2;
     } else {
       dims[0] = D; dims[1] = a.N; dims[2] = a.Hkv; dims[3] = a.B;
@@ -1248,13 +1258,22 @@ size_t sdpa_workspace_bytes(int B, int Hq, int Hkv, int D, int N) {
   return (simple > tc ? simple : tc) + 256;
 }
 
+// What keeps a call off the tensor-core kernel apart from a missing workspace.
+static bool tc_takes(int B, float scale, bool ragged) {
+  if (ragged && B > 4096) return false;
+  return scale > 0.f;                                // the running maximum assumes a positive scale
+}
+
 bool sdpa_tc_supported(const SdpaArgs& a) {
   if (a.D != 128 && a.D != 256) return false;
   if (a.dtype != DFLASH_BF16 && a.dtype != DFLASH_F16) return false;
-  if (a.kv_len && a.B > 4096) return false;
-  if (!(a.scale > 0.f)) return false;                // the running maximum assumes a positive scale
+  if (!tc_takes(a.B, a.scale, a.kv_len != nullptr)) return false;
   if (!a.workspace || a.workspace_bytes < tc_workspace_bytes(a.D)) return false;
   return true;
+}
+
+size_t sdpa_scratch_bytes_for_call(int B, int Hq, int D, float scale, bool ragged) {
+  return tc_takes(B, scale, ragged) ? tc_workspace_bytes(D) : sdpa_simple_workspace_bytes(B, Hq, D);
 }
 
 template <typename InT, int D>

@@ -137,7 +137,7 @@ struct DFlashKernels {
     if (!ws.defined() || ws.nbytes() < need) ws = Tensor::empty({(int64_t)need}, DType::U8);
     Tensor out = Tensor::empty(queries.shape(), queries.dtype());
     const int32_t st = dflash_verify_sdpa(queries.data(), keys.data(), values.data(), nullptr, nullptr, mask ? mask->data() : nullptr,
-                                          out.data(), ws.data(), ws.nbytes(), B, Hq, Hkv, T, D, N, 0, 0, scale,
+                                          out.data(), ws.data(), ws.nbytes(), B, Hq, Hkv, T, D, N, 0, 0, 0, scale,
                                           (int32_t)queries.dtype(), DFLASH_KV_DENSE, stream);
     if (st == DFLASH_ERR_UNSUPPORTED) return std::nullopt;
     check(st);
@@ -308,7 +308,7 @@ class PagedKVCache {
     Tensor out = Tensor::empty(queries.shape(), queries.dtype());
     const int32_t st = dflash_verify_sdpa(queries.data(), kPool.data(), vPool.data(), static_cast<const int32_t*>(pageTable.data()),
                                           static_cast<const int32_t*>(kvLenBlock.data()), nullptr, out.data(), ws_.data(), ws_.nbytes(),
-                                          B_, Hq, Hkv_, 16, D_, (int32_t)nMax, pageTokens_, maxPages_, scale, (int32_t)queries.dtype(),
+                                          B_, Hq, Hkv_, 16, D_, (int32_t)nMax, pageTokens_, maxPages_, numPages_, scale, (int32_t)queries.dtype(),
                                           DFLASH_KV_DENSE, stream);
     if (st == DFLASH_ERR_UNSUPPORTED) return std::nullopt;
     check(st);

@@ -118,7 +118,7 @@ int main() {
     EXPECT(!DFlashKernels::batchedSDPA2Pass(qbad, ka, va, 1.f / 16.f).has_value(), "batchedSDPA2Pass returns no value for 8 query rows");
     if (out) {
       Tensor o2 = Tensor::empty(qa.shape(), DType::BF16);
-      check(dflash_verify_sdpa_noalloc(qa.data(), ka.data(), va.data(), nullptr, nullptr, nullptr, o2.data(), 2, 16, 2, 16, 256, 716, 0, 0,
+      check(dflash_verify_sdpa_noalloc(qa.data(), ka.data(), va.data(), nullptr, nullptr, nullptr, o2.data(), 2, 16, 2, 16, 256, 716, 0, 0, 0,
                                        1.f / 16.f, DFLASH_BF16, DFLASH_KV_DENSE, nullptr));
       EXPECT(host<uint16_t>(*out) == host<uint16_t>(o2), "workspace and allocation-free attention agree bitwise");
     }
@@ -160,7 +160,7 @@ int main() {
         const size_t need = dflash_verify_sdpa_workspace_bytes(KB, 16, KH, KD, nMax);
         Tensor ws = Tensor::empty({(int64_t)need}, DType::U8);
         check(dflash_verify_sdpa(qn.data(), dkT.data(), dvT.data(), nullptr, static_cast<const int32_t*>(lensBlk.data()), nullptr, dense.data(),
-                                 ws.data(), ws.nbytes(), KB, 16, KH, 16, KD, nMax, 0, 0, 1.f / 16.f, DFLASH_BF16, DFLASH_KV_DENSE, nullptr));
+                                 ws.data(), ws.nbytes(), KB, 16, KH, 16, KD, nMax, 0, 0, 0, 1.f / 16.f, DFLASH_BF16, DFLASH_KV_DENSE, nullptr));
         auto paged = cache.attend(qn, 1.f / 16.f);
         attnOk = attnOk && paged.has_value() && host<uint16_t>(*paged) == host<uint16_t>(dense);
         // commit: keep accepted + 1 rows of the block

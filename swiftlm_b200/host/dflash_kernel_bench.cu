@@ -178,7 +178,7 @@ static void bench_sdpa(const Args& a) {
     char label[64];
     snprintf(label, sizeof label, "nKV=%d", n);
     print_result(label, measure(a, [&](int i) {
-                   DF(dflash_verify_sdpa(q, k[i % nc], v[i % nc], nullptr, nullptr, nullptr, out, ws, ws_bytes, B, Hq, Hk, T, D, n, 0, 0, scale,
+                   DF(dflash_verify_sdpa(q, k[i % nc], v[i % nc], nullptr, nullptr, nullptr, out, ws, ws_bytes, B, Hq, Hk, T, D, n, 0, 0, 0, scale,
                                          DFLASH_BF16, DFLASH_KV_DENSE, nullptr));
                  }), bytes);
     for (int c = 0; c < nc; ++c) { CK(cudaFree(k[c])); CK(cudaFree(v[c])); }

@@ -149,12 +149,12 @@ def batched_sdpa_2pass(queries, keys, values, scale: float, mask=None, kv_len=No
     if kv_len is not None:
         kv_len = torch.as_tensor(kv_len, device=q.device).to(torch.int32).contiguous()
     if page_table is None:
-        N, page_tokens, max_pages = keys.shape[2], 0, 0
+        N, page_tokens, max_pages, num_pages = keys.shape[2], 0, 0, 0
     else:
         if kv_len is None:
             raise ValueError("paged KV needs kv_len")
         page_table = page_table.to(torch.int32).contiguous()
-        page_tokens, max_pages = keys.shape[2], page_table.shape[1]
+        page_tokens, max_pages, num_pages = keys.shape[2], page_table.shape[1], keys.shape[0]
         # n_max avoids a host read of kv_len on the hot path
         N = int(n_max) if n_max is not None else int(kv_len.max())
     if mask is not None:
@@ -167,7 +167,7 @@ def batched_sdpa_2pass(queries, keys, values, scale: float, mask=None, kv_len=No
         _lib.check(L.dflash_verify_sdpa(
             _ptr(q), _ptr(k), _ptr(v), _ptr(page_table), _ptr(kv_len), _ptr(mask), _ptr(out),
             _ptr(ws), 0 if ws is None else ws.numel(), B, Hq, Hkv, T, D, N, page_tokens, max_pages,
-            float(scale), _DT[dt], _lib.KV_DENSE, _stream()))
+            num_pages, float(scale), _DT[dt], _lib.KV_DENSE, _stream()))
     except _lib.DFlashUnsupported:
         return None
     return out
@@ -202,6 +202,19 @@ def accept_lengths(posterior: torch.Tensor, verify_ids: torch.Tensor):
     _lib.check(_lib.lib().dflash_accept_lengths(_ptr(posterior), _ptr(verify_ids), _ptr(acc), _ptr(nxt),
                                                _ptr(rep), B, T, _stream()))
     return acc, nxt, rep
+
+
+def gather_logits_rows(logits: torch.Tensor, row_per_seq: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """logits [B,T,V], row_per_seq int32 [B] (the accepted count) -> [B,V]: each sequence's logits row at its accepted
+    position, the row whose argmax is the next staged token (Sources/DFlash/DFlashRuntime.swift:547)."""
+    _need_cuda(logits, row_per_seq)
+    B, T, V = logits.shape
+    logits = logits.contiguous()
+    if out is None:
+        out = torch.empty(B, V, dtype=logits.dtype, device=logits.device)
+    _lib.check(_lib.lib().dflash_gather_logits_rows(_ptr(logits), _ptr(row_per_seq.to(torch.int32).contiguous()), _ptr(out),
+                                                   B, T, V, _DT[logits.dtype], _stream()))
+    return out
 
 
 def turbo_decode_into(packed, signs, norm, rnorm, out: torch.Tensor) -> None:
@@ -294,7 +307,7 @@ def batched_sdpa_turbo_kv(queries, k_enc, v_enc, n_cold: int, scale: float, k_ho
     desc = _lib.TurboKV(_ptr(kp), _ptr(ks), _ptr(kn), _ptr(kr), _ptr(vp), _ptr(vn), _ptr(kh), _ptr(vh), n_cold, n_hot)
     try:
         _lib.check(L.dflash_verify_sdpa(_ptr(q), C.cast(C.pointer(desc), C.c_void_p), None, None, None, None, _ptr(out),
-                                        _ptr(ws), ws.numel(), B, Hq, Hkv, T, D, n_keys, 0, 0, float(scale), _DT[dt],
+                                        _ptr(ws), ws.numel(), B, Hq, Hkv, T, D, n_keys, 0, 0, 0, float(scale), _DT[dt],
                                         _lib.KV_TURBO3, _stream()))
     except _lib.DFlashUnsupported:
         return None

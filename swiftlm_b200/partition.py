@@ -2,8 +2,8 @@
 
 Both kernels shard without any exchange on the data path: the replay by sequence (a GPU owns
 every layer and head of its sequences, states never move), the verify attention by
-(sequence, KV head) pair.  The only collective is an all-gather of the per-sequence acceptance
-results (and, for the caller that wants them, logits slices) after the step.
+(sequence, KV head) pair.  The only collectives are all-gathers after the step: the per-sequence
+acceptance results and one logits row per sequence (the row at the accepted position).
 The reference is single-device; there is nothing to cite.
 """
 from __future__ import annotations
@@ -31,11 +31,14 @@ def kv_pairs_for_rank(n_sequences: int, n_kv_heads: int, rank: int, world: int) 
     return [(p // n_kv_heads, p % n_kv_heads) for p in range(lo, hi)]
 
 
-def all_gather_acceptance(accept_local, next_local, n_sequences: int, group=None):
-    """All-gather of the acceptance results of a sequence-sharded step.  accept_local and
-    next_local are int32 tensors holding this rank's contiguous range of plan(n_sequences, world);
-    returns (accept [n_sequences], next_token [n_sequences]) on every rank.  Ranges may differ in
-    length by one, so shards are padded to the longest range for the collective."""
+def all_gather_acceptance(accept_local, next_local, n_sequences: int, group=None, logits_rows_local=None):
+    """All-gather of the results of a sequence-sharded step.  accept_local and next_local are int32 tensors holding
+    this rank's contiguous range of plan(n_sequences, world); returns (accept [n_sequences], next_token
+    [n_sequences]) on every rank.  With logits_rows_local [n_local, V] (the verify-logits row at each sequence's
+    accepted position, kernels.gather_logits_rows) a second all-gather returns those rows as [n_sequences, V] too:
+    the posterior row is what a consumer on another rank needs beyond the token itself (sampling with a temperature,
+    log-probabilities), at V values per sequence instead of the block's T x V.  Ranges may differ in length by one,
+    so shards are padded to the longest range for the collectives (one all_gather_into_tensor each)."""
     import torch
     import torch.distributed as dist
 
@@ -50,4 +53,18 @@ def all_gather_acceptance(accept_local, next_local, n_sequences: int, group=None
     dist.all_gather_into_tensor(recv.view(-1), send.view(-1), group=group)
     acc = torch.cat([recv[r, 0, :e - b] for r, (b, e) in enumerate(ranges)])
     nxt = torch.cat([recv[r, 1, :e - b] for r, (b, e) in enumerate(ranges)])
-    return acc, nxt
+    if logits_rows_local is None:
+        return acc, nxt
+    V = logits_rows_local.shape[1]
+    if n == longest:
+        lsend = logits_rows_local.contiguous()
+    else:
+        lsend = torch.zeros(longest, V, dtype=logits_rows_local.dtype, device=logits_rows_local.device)
+        lsend[:n] = logits_rows_local
+    lrecv = torch.empty(world, longest, V, dtype=lsend.dtype, device=lsend.device)
+    dist.all_gather_into_tensor(lrecv.view(-1), lsend.view(-1), group=group)
+    if all(e - b == longest for b, e in ranges):
+        rows = lrecv.view(world * longest, V)
+    else:
+        rows = torch.cat([lrecv[r, :e - b] for r, (b, e) in enumerate(ranges)])
+    return acc, nxt, rows

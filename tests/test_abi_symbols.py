@@ -47,7 +47,7 @@ def test_argument_validation_needs_no_device():
     # SDPA eligibility mirrors the reference's nil-return guards
     def sdpa(T=16, D=256, Hq=16, Hkv=2, dtype=_lib.BF16, N=64):
         return L.dflash_verify_sdpa(fake, fake, fake, None, None, None, fake, None, 0, 1, Hq, Hkv, T, D, N,
-                                    0, 0, 0.0625, dtype, 0, None)
+                                    0, 0, 0, 0.0625, dtype, 0, None)
     assert sdpa(T=8) == _lib.ERR_UNSUPPORTED
     assert sdpa(D=64) == _lib.ERR_UNSUPPORTED
     assert sdpa(Hq=15) == _lib.ERR_UNSUPPORTED
@@ -55,7 +55,7 @@ def test_argument_validation_needs_no_device():
     assert sdpa(N=8) == _lib.ERR_UNSUPPORTED
     # misaligned base pointer
     assert L.dflash_verify_sdpa(fake + 2, fake, fake, None, None, None, fake, None, 0, 1, 16, 2, 16, 256, 64,
-                                0, 0, 0.0625, _lib.BF16, 0, None) == _lib.ERR_INVALID_ARG
+                                0, 0, 0, 0.0625, _lib.BF16, 0, None) == _lib.ERR_INVALID_ARG
 
 
 @pytest.mark.parametrize("units,gpus", [(64, 8), (16, 8), (10, 4), (3, 8), (0, 2), (73, 1)])

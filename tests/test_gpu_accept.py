@@ -55,3 +55,28 @@ def test_accept_lengths_bit_exact():
     np.testing.assert_array_equal(p.cpu().numpy().astype(np.uint32), pc)
     np.testing.assert_array_equal(a2.cpu().numpy(), ac)
     np.testing.assert_array_equal(n2.cpu().numpy(), nc)
+
+
+@pytest.mark.parametrize("dtype,V", [(torch.bfloat16, 151936), (torch.float32, 1003), (torch.float16, 4096)])
+def test_gather_logits_rows_is_exact(dtype, V):
+    """The logits row at each sequence's accepted position, picked on the device: exact bytes, and its argmax is the
+    next staged token."""
+    from swiftlm_b200 import kernels
+    B, T = 5, 16
+    g = torch.Generator(device="cuda").manual_seed(77)
+    logits = torch.randn(B, T, V, device="cuda", generator=g).to(dtype)
+    post = kernels.greedy_tokens_with_mask(logits)
+    ids = torch.zeros(B, T, dtype=torch.int32, device="cuda")
+    ids[:, 1:] = post[:, :-1]
+    ids[1, 4] += 1
+    ids[3, 1] += 1
+    acc, nxt, _ = kernels.accept_lengths(post, ids)
+    rows = kernels.gather_logits_rows(logits, acc)
+    torch.cuda.synchronize()
+    want = torch.stack([logits[b, int(acc[b])] for b in range(B)])
+    assert torch.equal(rows, want)
+    assert torch.equal(rows.float().argmax(dim=-1).int(), nxt)
+    # out-of-range row indices are clamped, never dereferenced
+    bad = torch.tensor([-3, 0, 99, 15, 16], dtype=torch.int32, device="cuda")
+    rows = kernels.gather_logits_rows(logits, bad)
+    assert torch.equal(rows[0], logits[0, 0]) and torch.equal(rows[2], logits[2, 15]) and torch.equal(rows[4], logits[4, 15])

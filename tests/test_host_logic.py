@@ -71,6 +71,15 @@ def _gloo_worker(rank, world, port, n_seq, out_dir):
                                                torch.tensor(nxt_local, dtype=torch.int32), n_seq)
     want = [O.accept_block(ids[b], post[b]) for b in range(n_seq)]
     assert acc.tolist() == [w[0] for w in want] and nxt.tolist() == [w[2] for w in want]
+    # with the logits rows: every rank ends up with each sequence's logits row at its accepted position
+    V = 50
+    logits = np.random.default_rng(7).standard_normal((n_seq, 16, V)).astype(np.float32)
+    rows_local = torch.from_numpy(np.stack([logits[b, acc_local[b - lo]] for b in range(lo, hi)]).reshape(hi - lo, V))
+    acc2, nxt2, rows = partition.all_gather_acceptance(torch.tensor(acc_local, dtype=torch.int32),
+                                                       torch.tensor(nxt_local, dtype=torch.int32), n_seq,
+                                                       logits_rows_local=rows_local)
+    assert torch.equal(acc2, acc) and torch.equal(nxt2, nxt) and rows.shape == (n_seq, V)
+    np.testing.assert_array_equal(rows.numpy(), np.stack([logits[b, want[b][0]] for b in range(n_seq)]))
     dist.barrier()
     dist.destroy_process_group()
     open(os.path.join(out_dir, f"ok{rank}"), "w").close()

@@ -30,10 +30,10 @@ def _both(L, _lib, x, kv_len=None):
     got = torch.full_like(q, float("nan"))
     scale = float(x["scale"])
     st = L.dflash_verify_sdpa(q.data_ptr(), k.data_ptr(), v.data_ptr(), None, lp, None, ref.data_ptr(), ws.data_ptr(),
-                              ws.numel(), B, Hq, Hkv, T, D, N, 0, 0, scale, _lib.BF16, _lib.KV_DENSE, None)
+                              ws.numel(), B, Hq, Hkv, T, D, N, 0, 0, 0, scale, _lib.BF16, _lib.KV_DENSE, None)
     assert st == 0, L.dflash_last_error_string()
     st = L.dflash_verify_sdpa_noalloc(q.data_ptr(), k.data_ptr(), v.data_ptr(), None, lp, None, got.data_ptr(),
-                                      B, Hq, Hkv, T, D, N, 0, 0, scale, _lib.BF16, _lib.KV_DENSE, None)
+                                      B, Hq, Hkv, T, D, N, 0, 0, 0, scale, _lib.BF16, _lib.KV_DENSE, None)
     assert st == 0, L.dflash_last_error_string()
     torch.cuda.synchronize()
     assert L.dflash_device_status(None) == 0
@@ -61,8 +61,28 @@ def test_noalloc_entry_validates_like_the_regular_one():
     L = _lib.lib()
     q = torch.zeros(1, 16, 16, 64, dtype=torch.bfloat16, device="cuda")
     st = L.dflash_verify_sdpa_noalloc(q.data_ptr(), q.data_ptr(), q.data_ptr(), None, None, None, q.data_ptr(),
-                                      1, 16, 2, 16, 64, 64, 0, 0, 0.1, _lib.BF16, _lib.KV_DENSE, None)
+                                      1, 16, 2, 16, 64, 64, 0, 0, 0, 0.1, _lib.BF16, _lib.KV_DENSE, None)
     assert st == _lib.ERR_UNSUPPORTED      # head_dim 64 is outside the supported set
-    st = L.dflash_verify_sdpa_noalloc(None, None, None, None, None, None, None, 0, 16, 2, 16, 256, 64, 0, 0, 0.1,
+    st = L.dflash_verify_sdpa_noalloc(None, None, None, None, None, None, None, 0, 16, 2, 16, 256, 64, 0, 0, 0, 0.1,
                                       _lib.BF16, _lib.KV_DENSE, None)
     assert st == _lib.ERR_INVALID_ARG
+
+
+def test_noalloc_entry_refuses_compressed_kv_before_any_launch():
+    """KV in the compressed format is expanded into scratch by the regular entry (B*Hkv*N*D*4 bytes), which the
+    built-in array cannot hold: the no-alloc entry refuses the format up front, launches nothing and leaves
+    the device status clean.  (Its DFLASH_ERR_WORKSPACE answer needs a GPU with more than 158 SMs to show:
+    on 148 SMs every dense or paged call fits the array.)"""
+    import ctypes as C
+
+    from swiftlm_b200 import _lib
+    L = _lib.lib()
+    B, Hq, Hkv, D, N = 4, 16, 2, 256, 64
+    q = torch.zeros(B, Hq, 16, D, dtype=torch.bfloat16, device="cuda")
+    desc = _lib.TurboKV()   # never read: the format is refused first
+    launches = L.dflash_launch_count()
+    st = L.dflash_verify_sdpa_noalloc(q.data_ptr(), C.cast(C.pointer(desc), C.c_void_p), None, None, None, None, q.data_ptr(),
+                                      B, Hq, Hkv, 16, D, N, 0, 0, 0, 0.0625, _lib.BF16, _lib.KV_TURBO3, None)
+    assert st == _lib.ERR_UNSUPPORTED and b"TurboQuant" in L.dflash_last_error_string()
+    assert L.dflash_launch_count() == launches
+    assert L.dflash_device_status(None) == 0
