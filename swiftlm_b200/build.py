@@ -43,6 +43,11 @@ def build(force: bool = False, verbose: bool = False) -> str:
     os.makedirs(LIBDIR, exist_ok=True)
     os.makedirs(OBJDIR, exist_ok=True)
     nvcc = _nvcc()
+    # the SwiftPM C target carries a copy of the header: keep it in step with include/
+    hdr = os.path.join(os.path.dirname(PKG), "include", "dflash_cuda.h")
+    hdr_copy = os.path.join(PKG, "swift", "Sources", "CDFlashCUDA", "include", "dflash_cuda.h")
+    if os.path.isdir(os.path.dirname(hdr_copy)) and (not os.path.exists(hdr_copy) or open(hdr).read() != open(hdr_copy).read()):
+        shutil.copyfile(hdr, hdr_copy)
     sources = sorted(glob.glob(os.path.join(CSRC, "*.cu")))
     headers = sorted(glob.glob(os.path.join(CSRC, "*.cuh"))) + \
         [os.path.join(os.path.dirname(PKG), "include", "dflash_cuda.h"), os.path.abspath(__file__)]

@@ -64,7 +64,7 @@ def check_replay(x, label, state_bound, y_bound):
     e_tape, e_y = max_norm_rel(tape, to), max_norm_rel(y, yo)
     print(f"\n[{label}] state: max-norm rel {e_max:.3e}, element-wise rel {e_elem:.3e}; tape max-norm rel {e_tape:.3e}; "
           f"y max-norm rel {e_y:.3e}")
-    assert e_max < state_bound and e_elem < 1e-4 and e_elem < 4 * state_bound
+    assert e_max < state_bound and e_elem < 1e-4 and e_elem < 5 * state_bound
     assert e_tape < 1e-4 and e_y < y_bound
     # tape-slot indexing and the accepted length: exact
     np.testing.assert_array_equal(tape == 0, to == 0)
@@ -86,7 +86,8 @@ def test_config0_fp32_single_sequence():
 def test_config1_full_size_bf16():
     torch.cuda.set_device(0)
     x = gdn_inputs(64, 36, torch.bfloat16, SEED + 1000)
-    check_replay(x, "configs[1] 64 seq x 36 layers x 32 heads", state_bound=2e-5, y_bound=1.0 / 128)
+    # measured: max-norm 3.7e-7, element-wise 1.7e-6 (the two-term bf16 split of the state is good to 2^-17)
+    check_replay(x, "configs[1] 64 seq x 36 layers x 32 heads", state_bound=2e-6, y_bound=1.0 / 128)
 
 
 def sdpa_inputs(B, Hq, Hkv, N, D, seed):
@@ -116,7 +117,7 @@ def test_config2_full_size_every_sequence():
     want = oracle_sdpa_by_sequence(q, k, v, 1.0 / 16.0)
     err = float(np.abs(out.float().cpu().numpy() - want).max())
     print(f"\n[configs[2] B=32 N=4112] max abs error {err:.3e}")
-    assert err < 2e-2 and err < 4e-3
+    assert err < 2e-2 and err < 2e-3      # measured 5.8e-4
 
 
 @pytest.mark.parametrize("n_ctx", [40960, 102400])
@@ -149,4 +150,4 @@ def test_config3_long_context_paged(n_ctx):
     e_dense = float(np.abs(dense.float().cpu().numpy() - want).max())
     e_paged = float(np.abs(paged.float().cpu().numpy() - want).max())
     print(f"\n[configs[3] B=8 N={N}] max abs error dense {e_dense:.3e}, paged {e_paged:.3e}")
-    assert e_dense < 2e-2 and e_paged < 2e-2 and max(e_dense, e_paged) < 4e-3
+    assert e_dense < 2e-2 and e_paged < 2e-2 and max(e_dense, e_paged) < 1e-3      # measured 1.5e-4 / 8.2e-5
