@@ -237,6 +237,63 @@ int32_t dflash_turbo_decode(const uint8_t* packed, const uint8_t* signs, const u
                             int32_t out_dtype, void* stream);
 
 /* ---------------------------------------------------------------------------------------------
+ * One DFlash verify step over a hybrid stack, a handful of launches in all.
+ * Composes, below the ABI, what the reference's runtime does per speculative cycle between
+ * Sources/DFlash/DFlashRuntime.swift:499 and :579: the verify forward of every gated-delta layer with
+ * its tape recorded (:502, through the provider, DFlashKernelProvider.swift:9-13), the block-verify
+ * attention of every attention layer, the greedy posterior and the accepted length (:513-533), the
+ * commit arithmetic (:544-547) and the rollback of every gated-delta layer to the accepted length
+ * (restoreTargetCacheAfterAcceptance :188-223 -> RecurrentRollbackCache.rollback,
+ * RecurrentRollbackCache.swift:95-131, tape replay plus conv-window rebuild).  The reference issues one
+ * kernel per layer and reads the accepted length on the host (:525-530); here the layers of a kind are
+ * stacked into the batch of ONE launch (item = sequence * layers + layer, sequence-major, so a GPU owns
+ * whole sequences) and the accepted length stays on the device.  Layer weights are not part of the
+ * path: the per-layer tensors are the caller's.
+ *
+ * Launches: gated-delta forward (1), attention (1, plus its merge kernel where the split needs it),
+ * greedy tokens (1), accept lengths (1), logits rows (1, optional), tape replay (1), conv windows (1).
+ * Every pointer is a device pointer; outputs are written in place; `workspace` as for
+ * dflash_verify_sdpa with B * attn_layers sequences (dflash_verify_step_workspace_bytes).
+ */
+typedef struct {
+  int32_t B;                 /* sequences on this GPU */
+  int32_t T;                 /* block length: 16 */
+  /* ---- gated-delta layers: arrays over B * gdn_layers items ---- */
+  int32_t gdn_layers, Hk, Hv, Dk, Dv, g_is_vector, in_dtype;
+  const void *q, *k, *v, *g, *beta;   /* as dflash_gated_delta_tape */
+  const float* state;                 /* committed states [B*gdn_layers,Hv,Dv,Dk] */
+  void* y;                            /* [B*gdn_layers,T,Hv,Dv] in_dtype: the verify forward's outputs */
+  float* state_verify;                /* state after all T steps (what a fully accepted block keeps) */
+  float* tape;                        /* [B*gdn_layers,T,Hv,Dv] */
+  float* state_rolled;                /* state replayed to replay_len[b] steps; may alias state */
+  /* conv windows of the rollback cache (may all be NULL: skipped) */
+  const void* conv_snapshot;          /* [B*gdn_layers,conv_keep,C] or NULL (zeros) */
+  const void* qkv;                    /* [B*gdn_layers,T,C] */
+  void* conv_out;                     /* [B*gdn_layers,conv_keep,C] */
+  int32_t conv_keep;
+  int64_t conv_row_bytes;
+  /* ---- attention layers: arrays over B * attn_layers items (0 layers: skipped) ---- */
+  int32_t attn_layers, Hq, Hkv, D, N, attn_dtype, kv_format;
+  const void* attn_q;                 /* [B*attn_layers,Hq,16,D] */
+  const void* attn_k;                 /* dense: [B*attn_layers,Hkv,N,D]; DFLASH_KV_TURBO3: host pointer to a dflash_turbo_kv */
+  const void* attn_v;
+  void* attn_out;                     /* [B*attn_layers,Hq,16,D] */
+  float scale;
+  /* ---- acceptance ---- */
+  const void* logits;                 /* [B,T,V] logits_dtype */
+  const uint8_t* suppress;            /* uint8[V] or NULL */
+  const int32_t* verify_ids;          /* [B,T] */
+  int32_t V, logits_dtype;
+  uint32_t* posterior;                /* [B,T] */
+  int32_t *accept, *next_token, *replay_len;   /* [B] each */
+  void* logits_rows;                  /* [B,V] logits_dtype or NULL: the row at each accepted position */
+} dflash_verify_step_desc;
+
+size_t dflash_verify_step_workspace_bytes(const dflash_verify_step_desc* desc_host);
+int32_t dflash_verify_step(const dflash_verify_step_desc* desc_host, void* workspace, size_t workspace_bytes,
+                           void* stream);
+
+/* ---------------------------------------------------------------------------------------------
  * Host-side helpers.
  */
 /* Splits `units` independent work units (sequences for replay, (sequence, KV head) pairs for

@@ -33,6 +33,8 @@ SIGNATURES = {
     "dflash_kv_commit": (_i32, [_vp, _vp, _i32, _i32, _vp]),
     "dflash_turbo_encode": (_i32, [_vp] * 5 + [C.c_int64, _i32, _i32, _vp]),
     "dflash_turbo_decode": (_i32, [_vp] * 5 + [C.c_int64, _i32, _i32, _vp]),
+    "dflash_verify_step_workspace_bytes": (_sz, [_vp]),
+    "dflash_verify_step": (_i32, [_vp, _vp, _sz, _vp]),
     "dflash_partition_plan": (_i32, [_i32, _i32, C.POINTER(_i32)]),
     "dflash_device_status": (_i32, [_vp]),
     "dflash_selftest_bounded_wait": (_i32, [C.c_uint32, _vp, _vp]),
@@ -48,6 +50,26 @@ class TurboKV(C.Structure):
     _fields_ = [("k_packed", C.c_void_p), ("k_signs", C.c_void_p), ("k_norm", C.c_void_p), ("k_rnorm", C.c_void_p),
                 ("v_packed", C.c_void_p), ("v_norm", C.c_void_p), ("k_hot", C.c_void_p), ("v_hot", C.c_void_p),
                 ("n_cold", C.c_int32), ("n_hot", C.c_int32)]
+
+
+class VerifyStepDesc(C.Structure):
+    """dflash_verify_step_desc of include/dflash_cuda.h (field order and types must match the header)."""
+    _fields_ = [("B", C.c_int32), ("T", C.c_int32),
+                ("gdn_layers", C.c_int32), ("Hk", C.c_int32), ("Hv", C.c_int32), ("Dk", C.c_int32), ("Dv", C.c_int32),
+                ("g_is_vector", C.c_int32), ("in_dtype", C.c_int32),
+                ("q", C.c_void_p), ("k", C.c_void_p), ("v", C.c_void_p), ("g", C.c_void_p), ("beta", C.c_void_p),
+                ("state", C.c_void_p), ("y", C.c_void_p), ("state_verify", C.c_void_p), ("tape", C.c_void_p),
+                ("state_rolled", C.c_void_p),
+                ("conv_snapshot", C.c_void_p), ("qkv", C.c_void_p), ("conv_out", C.c_void_p),
+                ("conv_keep", C.c_int32), ("conv_row_bytes", C.c_int64),
+                ("attn_layers", C.c_int32), ("Hq", C.c_int32), ("Hkv", C.c_int32), ("D", C.c_int32), ("N", C.c_int32),
+                ("attn_dtype", C.c_int32), ("kv_format", C.c_int32),
+                ("attn_q", C.c_void_p), ("attn_k", C.c_void_p), ("attn_v", C.c_void_p), ("attn_out", C.c_void_p),
+                ("scale", C.c_float),
+                ("logits", C.c_void_p), ("suppress", C.c_void_p), ("verify_ids", C.c_void_p),
+                ("V", C.c_int32), ("logits_dtype", C.c_int32),
+                ("posterior", C.c_void_p), ("accept", C.c_void_p), ("next_token", C.c_void_p), ("replay_len", C.c_void_p),
+                ("logits_rows", C.c_void_p)]
 
 
 class DFlashError(RuntimeError):

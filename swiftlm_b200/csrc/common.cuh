@@ -75,10 +75,10 @@ __device__ __forceinline__ bool mask_on(const void* mask, int mask_dtype, int id
 
 // Bit t set <=> step t of sequence b runs.  T <= 64.
 __device__ __forceinline__ unsigned long long step_bits(const void* mask, int mask_dtype,
-                                                        const int32_t* n_per_seq, int b, int T) {
+                                                        const int32_t* n_per_seq, int b, int T, int n_div = 1) {
   unsigned long long bits = T >= 64 ? ~0ull : ((1ull << T) - 1ull);
   if (n_per_seq) {
-    int n = n_per_seq[b];
+    int n = n_per_seq[(unsigned)b / (unsigned)n_div];
     n = n < 0 ? 0 : (n > T ? T : n);
     bits &= n >= 64 ? ~0ull : ((1ull << n) - 1ull);
   }
@@ -104,6 +104,7 @@ struct GdnArgs {
   int B, T, Hk, Hv, Dk, Dv;
   int g_is_vector, in_dtype, mask_dtype;
   bool replay;        // true: S <- S g + tape (x) k ; false: full forward
+  int n_div = 1;      // item b reads n_per_seq[b / n_div]: n_div stacked layers of a sequence share its length
 };
 
 int32_t launch_gdn_generic(const GdnArgs& a, cudaStream_t stream);
@@ -146,6 +147,10 @@ int32_t launch_accept_lengths(const uint32_t* posterior, const int32_t* verify_i
 
 int32_t launch_gather_rows(const void* logits, const int32_t* row, void* out, int B, int T, long long row_bytes,
                            cudaStream_t stream);
+
+// steps_div: row b reads steps_per_seq[b / steps_div] (stacked layers of a sequence share its step count)
+int32_t launch_conv_window(const void* conv_snapshot, const void* qkv, const int32_t* steps_per_seq, int steps_all, void* out,
+                           int B, int T, int keep, long long row_bytes, int32_t* rows_out, int steps_div, cudaStream_t stream);
 
 int32_t launch_turbo_encode(const void* x, uint8_t* packed, uint8_t* signs, uint16_t* norm, uint16_t* rnorm,
                             long long n, int is_key, int in_dtype, cudaStream_t stream);

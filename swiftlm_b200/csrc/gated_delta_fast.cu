@@ -176,7 +176,7 @@ gdn_fast_kernel(const __grid_constant__ CUtensorMap state_map, const GdnArgs a, 
   };
   auto step_on = [&](int b, int t) -> bool {
     bool on = true;
-    if (a.n_per_seq) on = t < a.n_per_seq[b];
+    if (a.n_per_seq) on = t < a.n_per_seq[(unsigned)b / (unsigned)a.n_div];
     if (on && a.mask) on = mask_on(a.mask, a.mask_dtype, b * T + t);
     return on;
   };

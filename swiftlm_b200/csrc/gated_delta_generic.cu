@@ -32,7 +32,7 @@ gdn_generic_kernel(GdnArgs a) {
   const int b = head / a.Hv, hv = head % a.Hv;
   const int hk = hv / (a.Hv / a.Hk);
   const int npt = a.Dk >> 5;
-  const unsigned long long bits = step_bits(a.mask, a.mask_dtype, a.n_per_seq, b, a.T);
+  const unsigned long long bits = step_bits(a.mask, a.mask_dtype, a.n_per_seq, b, a.T, a.n_div);
 
   const float* s_in = a.state_in + row * a.Dk;
   float* s_out = a.state_out + row * a.Dk;

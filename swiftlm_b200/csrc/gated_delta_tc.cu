@@ -142,7 +142,7 @@ gdn_tc_kernel(const __grid_constant__ TcMaps maps, const GdnArgs a, int* status)
   };
   auto step_on = [&](int b, int t) -> bool {
     bool on = t < T;
-    if (on && a.n_per_seq) on = t < a.n_per_seq[b];
+    if (on && a.n_per_seq) on = t < a.n_per_seq[(unsigned)b / (unsigned)a.n_div];
     if (on && a.mask) on = mask_on(a.mask, a.mask_dtype, b * T + t);
     return on;
   };
@@ -289,7 +289,7 @@ gdn_tc_kernel(const __grid_constant__ TcMaps maps, const GdnArgs a, int* status)
         const long long bt = (long long)b1 * T + (lane < T ? lane : 0);
         h_g = gg[bt * a.Hv + hv1];
         h_b = gbeta[bt * a.Hv + hv1];
-        h_n = a.n_per_seq ? a.n_per_seq[b1] : T;
+        h_n = a.n_per_seq ? a.n_per_seq[(unsigned)b1 / (unsigned)a.n_div] : T;
         h_m = lane < T && (!a.mask || mask_on(a.mask, a.mask_dtype, b1 * T + lane));
       }
       failed = !ptx::mbar_wait(&bars[2], 0);
@@ -452,7 +452,7 @@ gdn_tc_kernel(const __grid_constant__ TcMaps maps, const GdnArgs a, int* status)
         const long long bt = (long long)b2 * T + (lane < T ? lane : 0);
         h_g = gg[bt * a.Hv + hv2];
         h_b = gbeta[bt * a.Hv + hv2];
-        h_n = a.n_per_seq ? a.n_per_seq[b2] : T;
+        h_n = a.n_per_seq ? a.n_per_seq[(unsigned)b2 / (unsigned)a.n_div] : T;
         h_m = lane < T && (!a.mask || mask_on(a.mask, a.mask_dtype, b2 * T + lane));
       }
       PH(8);

@@ -13,9 +13,9 @@ namespace {
 
 __global__ void conv_window_kernel(const uint8_t* __restrict__ prefix, const uint8_t* __restrict__ qkv,
                                    const int32_t* __restrict__ steps_per_seq, int steps_all, uint8_t* __restrict__ out,
-                                   int T, int keep, int rows_out, long long row_bytes) {
+                                   int T, int keep, int rows_out, long long row_bytes, int steps_div) {
   const int b = blockIdx.x / rows_out, j = blockIdx.x % rows_out;
-  int start = steps_per_seq ? steps_per_seq[b] : steps_all;
+  int start = steps_per_seq ? steps_per_seq[b / steps_div] : steps_all;
   if (start < 0) start = 0;
   if (steps_per_seq && start > T) start = T;                 // keep rows must exist: the last window is qkv's tail
   const int src_row = start + j;                              // row of concat(prefix, qkv)
@@ -31,10 +31,9 @@ __global__ void conv_window_kernel(const uint8_t* __restrict__ prefix, const uin
 }  // namespace
 }  // namespace dflash
 
-extern "C" int32_t dflash_rebuild_conv_state(const void* conv_snapshot, const void* qkv, const int32_t* steps_per_seq,
-                                             int32_t steps_all, void* out, int32_t B, int32_t T, int32_t keep,
-                                             int64_t row_bytes, int32_t* rows_out, void* stream) {
-  using namespace dflash;
+namespace dflash {
+int32_t launch_conv_window(const void* conv_snapshot, const void* qkv, const int32_t* steps_per_seq, int steps_all, void* out,
+                           int B, int T, int keep, long long row_bytes, int32_t* rows_out, int steps_div, cudaStream_t stream) {
   if (!qkv || !out || B <= 0 || T <= 0 || keep <= 0 || row_bytes <= 0) {
     set_error("rebuild_conv_state: invalid argument");
     return DFLASH_ERR_INVALID_ARG;
@@ -52,10 +51,18 @@ extern "C" int32_t dflash_rebuild_conv_state(const void* conv_snapshot, const vo
   }
   if (rows_out) *rows_out = rows;
   if (rows == 0) return DFLASH_OK;
-  conv_window_kernel<<<(unsigned)(B * rows), 128, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+  conv_window_kernel<<<(unsigned)(B * rows), 128, 0, stream>>>(
       reinterpret_cast<const uint8_t*>(conv_snapshot), reinterpret_cast<const uint8_t*>(qkv), steps_per_seq, steps_all,
-      reinterpret_cast<uint8_t*>(out), T, keep, rows, (long long)row_bytes);
+      reinterpret_cast<uint8_t*>(out), T, keep, rows, (long long)row_bytes, steps_div < 1 ? 1 : steps_div);
   DFLASH_LAUNCH_CHECK();
   count_launch();
   return DFLASH_OK;
+}
+}  // namespace dflash
+
+extern "C" int32_t dflash_rebuild_conv_state(const void* conv_snapshot, const void* qkv, const int32_t* steps_per_seq,
+                                             int32_t steps_all, void* out, int32_t B, int32_t T, int32_t keep,
+                                             int64_t row_bytes, int32_t* rows_out, void* stream) {
+  return dflash::launch_conv_window(conv_snapshot, qkv, steps_per_seq, steps_all, out, B, T, keep, (long long)row_bytes, rows_out, 1,
+                                    reinterpret_cast<cudaStream_t>(stream));
 }

@@ -69,3 +69,26 @@ def test_partition_plan(units, gpus):
     assert all(spans[i][1] == spans[i + 1][0] for i in range(gpus - 1))
     assert max(sizes) - min(sizes) <= 1 and sizes == sorted(sizes, reverse=True)
     assert L.dflash_partition_plan(4, 0, arr) == _lib.ERR_INVALID_ARG
+
+
+def test_verify_step_descriptor_layout_matches_the_header(tmp_path):
+    """The ctypes mirror of dflash_verify_step_desc against the C compiler's layout of the header's struct."""
+    import ctypes as C
+    import subprocess
+
+    from swiftlm_b200 import _lib
+    fields = [name for name, _ in _lib.VerifyStepDesc._fields_]
+    src = tmp_path / "layout.c"
+    lines = ['#include <stdio.h>', '#include <stddef.h>', f'#include "{os.path.join(ROOT, "include", "dflash_cuda.h")}"',
+             'int main(void) {', '  printf("%zu\\n", sizeof(dflash_verify_step_desc));']
+    lines += [f'  printf("%zu\\n", offsetof(dflash_verify_step_desc, {name}));' for name in fields]
+    lines += ['  printf("%zu %zu\\n", sizeof(dflash_turbo_kv), offsetof(dflash_turbo_kv, n_cold));', '  return 0;', '}']
+    src.write_text("\n".join(lines))
+    exe = tmp_path / "layout"
+    subprocess.run(["gcc", str(src), "-o", str(exe)], check=True)
+    out = subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout.split("\n")
+    assert int(out[0]) == C.sizeof(_lib.VerifyStepDesc)
+    for name, line in zip(fields, out[1:]):
+        assert int(line) == getattr(_lib.VerifyStepDesc, name).offset, name
+    size, off = map(int, out[1 + len(fields)].split())
+    assert size == C.sizeof(_lib.TurboKV) and off == _lib.TurboKV.n_cold.offset
