@@ -44,8 +44,8 @@ typedef enum { DFLASH_KV_DENSE = 0, DFLASH_KV_TURBO3 = 1 } dflash_kv_format;
  * window (docs/turboquant_hybrid_architecture.md:49-53 of the SwiftLM tree): the oldest n_cold
  * tokens of every (sequence, KV head) are compressed, the newest n_hot tokens (the verify block
  * among them) stay in the attention dtype; attention sees [decoded cold | hot], N = n_cold + n_hot.
- * Compressed arrays are device arrays over [B,Hkv,n_cold, D/128 blocks]; hot arrays are
- * [B,Hkv,n_hot,D] (NULL when n_hot == 0).  With kv_format == DFLASH_KV_TURBO3 the `k` argument of
+ * Compressed arrays are device arrays over [B,Hkv,n_cold, D/128 blocks], each 16-byte aligned; hot
+ * arrays are [B,Hkv,n_hot,D] (NULL when n_hot == 0).  With kv_format == DFLASH_KV_TURBO3 the `k` argument of
  * dflash_verify_sdpa points at one of these (in host memory) and `v` is ignored. */
 typedef struct {
   const uint8_t* k_packed;   /* [blocks,48] */
@@ -129,10 +129,17 @@ int32_t dflash_verify_sdpa(const void* q, const void* k, const void* v, const in
                            int32_t kv_format, void* stream);
 
 size_t dflash_verify_sdpa_workspace_bytes(int32_t B, int32_t Hq, int32_t Hkv, int32_t D, int32_t N);
-/* The same for a given kv_format: DFLASH_KV_TURBO3 adds room for K and V expanded to `dtype`
- * (2 * B*Hkv*N*D elements of 2 bytes), which the call decodes into before attending (dense KV
- * only, no page table).  The expanded KV makes a round trip through HBM: correct, not yet fused. */
+/* The same for a given kv_format.  DFLASH_KV_TURBO3 takes one of two routes (no page table either way):
+ *   fused   - cold history a multiple of 128 keys, no kv_len_per_seq, no mask, scale > 0: the query rows are
+ *             rotated once, the attention kernel expands packed indices and sign bits into its tensor-core
+ *             operands tile by tile, the output rows are rotated back; no decoded key or value reaches
+ *             global memory.  Workspace: three query-sized arrays, the hot window twice, the partials.
+ *   expand  - anything else: K and V are decoded into the workspace (2 * B*Hkv*N*D elements of 2 bytes) and
+ *             the dense kernel attends over the copy.
+ * _ex returns a size good for either route whatever n_cold is; _turbo_workspace_bytes returns what the route
+ * a given (n_cold, n_hot) takes needs, which for the fused route is far less. */
 size_t dflash_verify_sdpa_workspace_bytes_ex(int32_t B, int32_t Hq, int32_t Hkv, int32_t D, int32_t N, int32_t kv_format);
+size_t dflash_verify_sdpa_turbo_workspace_bytes(int32_t B, int32_t Hq, int32_t Hkv, int32_t D, int32_t n_cold, int32_t n_hot);
 
 /* Same computation as dflash_verify_sdpa for a caller that cannot supply scratch memory (a host
  * whose device-memory budget is fixed and whose allocator is closed to plug-ins, or a request path

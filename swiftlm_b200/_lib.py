@@ -24,6 +24,7 @@ SIGNATURES = {
     "dflash_verify_sdpa": (_i32, [_vp] * 8 + [_sz] + [_i32] * 9 + [_f32, _i32, _i32, _vp]),
     "dflash_verify_sdpa_workspace_bytes_ex": (_sz, [_i32] * 6),
     "dflash_verify_sdpa_workspace_bytes": (_sz, [_i32] * 5),
+    "dflash_verify_sdpa_turbo_workspace_bytes": (_sz, [_i32] * 6),
     "dflash_verify_sdpa_noalloc": (_i32, [_vp] * 7 + [_i32] * 9 + [_f32, _i32, _i32, _vp]),
     "dflash_greedy_tokens": (_i32, [_vp, _vp, _vp, _i32, _i32, _i32, _vp]),
     "dflash_accept_lengths": (_i32, [_vp] * 5 + [_i32, _i32, _vp]),

@@ -102,6 +102,18 @@ int32_t check_gdn_shape(int B, int T, int Hk, int Hv, int Dk, int Dv, int dtype,
 
 }  // namespace
 
+size_t align256(size_t x) { return (x + 255) / 256 * 256; }
+
+// The fused attention over compressed KV takes: a cold history of whole 128-key tiles, uniform lengths, no additive mask,
+// a positive scale.
+bool turbo_fused_applies(const dflash_turbo_kv* t, const int32_t* kv_len_per_seq, const void* mask, float scale) {
+  return t->n_cold > 0 && t->n_cold % 128 == 0 && !kv_len_per_seq && !mask && scale > 0.f;
+}
+// rotated queries (two tiles) + rotated-domain output + the hot window in the rotated domain + the split-KV partials
+size_t turbo_fused_workspace_bytes(int B, int Hq, int Hkv, int D, int n_hot) {
+  return 3 * align256((size_t)B * Hq * 16 * D * 2) + 2 * align256((size_t)B * Hkv * n_hot * D * 2) + sdpa_tc_scratch_bytes(D) + 256;
+}
+
 // Everything dflash_verify_sdpa can reject before it touches the device; shared with the entry point
 // that brings its own scratch so that both answer a bad call the same way.
 int32_t sdpa_check_args(const void* q, const void* k, const void* v, const int32_t* page_table, const void* out,
@@ -169,12 +181,41 @@ int32_t dflash_verify_sdpa(const void* q, const void* k, const void* v, const in
                            float scale, int32_t dtype, int32_t kv_format, void* stream) {
   if (int32_t st = sdpa_check_args(q, k, v, page_table, out, B, Hq, Hkv, T, D, N, page_tokens, max_pages, num_pages, dtype, kv_format)) return st;
   if (kv_format == DFLASH_KV_TURBO3) {
-    // expand K and V into the front of the workspace, then attend over the expanded copy
     if (page_table) { set_error("TurboQuant KV behind a page table is not supported"); return DFLASH_ERR_UNSUPPORTED; }
     const dflash_turbo_kv* t = reinterpret_cast<const dflash_turbo_kv*>(k);
     if (t->n_cold < 0 || t->n_hot < 0 || t->n_cold + t->n_hot != N) return bad("TurboQuant KV: n_cold + n_hot must equal N");
     if (t->n_cold > 0 && (!t->k_packed || !t->k_signs || !t->k_norm || !t->k_rnorm || !t->v_packed || !t->v_norm)) return bad("null TurboQuant array");
     if (t->n_hot > 0 && (!t->k_hot || !t->v_hot || !aligned16(t->k_hot) || !aligned16(t->v_hot))) return bad("TurboQuant KV: hot window arrays missing or misaligned");
+    if (!aligned16(q) || !aligned16(out)) return bad("tensor base pointers must be 16-byte aligned");
+    if (turbo_fused_applies(t, kv_len_per_seq, mask, scale)) {
+      // Fused: no key or value is decoded to global memory.  The query rows are rotated once (Q1 = R q, Q2 = Rq^T q), the
+      // hot window is brought into the rotated domain, the attention kernel expands the packed indices and sign bits
+      // into tensor-core operands tile by tile, and the output rows are rotated back.
+      const size_t need = turbo_fused_workspace_bytes(B, Hq, Hkv, D, t->n_hot);
+      if (!workspace || workspace_bytes < need) {
+        set_error("verify_sdpa (TurboQuant KV): workspace of %zu bytes needed, %zu given", need, workspace_bytes);
+        return DFLASH_ERR_WORKSPACE;
+      }
+      if (!aligned16(workspace)) return bad("tensor base pointers must be 16-byte aligned");
+      if (!aligned16(t->k_packed) || !aligned16(t->k_signs) || !aligned16(t->k_norm) || !aligned16(t->k_rnorm) ||
+          !aligned16(t->v_packed) || !aligned16(t->v_norm))
+        return bad("TurboQuant arrays must be 16-byte aligned");
+      uint8_t* ws = reinterpret_cast<uint8_t*>(workspace);
+      const size_t q_bytes = align256((size_t)B * Hq * 16 * D * 2), hot_bytes = align256((size_t)B * Hkv * t->n_hot * D * 2);
+      void *q1 = ws, *q2 = ws + q_bytes, *o_rot = ws + 2 * q_bytes, *k_rot = ws + 3 * q_bytes, *v_rot = ws + 3 * q_bytes + hot_bytes;
+      uint8_t* scratch = ws + 3 * q_bytes + 2 * hot_bytes;
+      cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+      if (int32_t st = launch_turbo_rotate_inputs(q, q1, q2, (long long)B * Hq * 16 * (D / 128), t->k_hot, k_rot, t->v_hot, v_rot,
+                                                  (long long)B * Hkv * t->n_hot * (D / 128), dtype, s))
+        return st;
+      SdpaArgs a{q1, t->n_hot > 0 ? k_rot : nullptr, t->n_hot > 0 ? v_rot : nullptr, nullptr, nullptr, nullptr, o_rot, scratch,
+                 workspace_bytes - (size_t)(scratch - ws), B, Hq, Hkv, D, N, 0, 0, 0, scale, dtype};
+      TurboKvArgs ta{t->k_packed, t->k_signs, t->v_packed, t->k_norm, t->k_rnorm, t->v_norm, q2, t->n_cold, t->n_hot};
+      if (int32_t st = launch_sdpa_tc_turbo(a, ta, s)) return st;
+      return launch_turbo_unrotate_output(o_rot, out, (long long)B * Hq * 16 * (D / 128), dtype, s);
+    }
+    // otherwise (history not a multiple of 128 keys, ragged lengths, additive mask): expand K and V into the front of the
+    // workspace, then attend over the expanded copy
     const size_t kv_elems = (size_t)B * Hkv * N * D, kv_bytes = (kv_elems * 2 + 255) / 256 * 256;
     const size_t need = 2 * kv_bytes + sdpa_workspace_bytes(B, Hq, Hkv, D, N);
     if (!workspace || workspace_bytes < need) {
@@ -215,8 +256,21 @@ size_t dflash_verify_sdpa_workspace_bytes(int32_t B, int32_t Hq, int32_t Hkv, in
 size_t dflash_verify_sdpa_workspace_bytes_ex(int32_t B, int32_t Hq, int32_t Hkv, int32_t D, int32_t N, int32_t kv_format) {
   const size_t base = dflash_verify_sdpa_workspace_bytes(B, Hq, Hkv, D, N);
   if (!base || kv_format != DFLASH_KV_TURBO3) return base;
-  const size_t kv_bytes = ((size_t)B * Hkv * N * D * 2 + 255) / 256 * 256;
-  return base + 2 * kv_bytes;
+  // enough for either route whatever the split into cold and hot keys: the expanded copy (2 x N keys) or the fused
+  // route's rotated queries and hot window (at most N keys)
+  const size_t kv_bytes = align256((size_t)B * Hkv * N * D * 2);
+  const size_t fused = turbo_fused_workspace_bytes(B, Hq, Hkv, D, N);
+  const size_t expand = base + 2 * kv_bytes;
+  return fused > expand ? fused : expand;
+}
+
+size_t dflash_verify_sdpa_turbo_workspace_bytes(int32_t B, int32_t Hq, int32_t Hkv, int32_t D, int32_t n_cold, int32_t n_hot) {
+  if (B <= 0 || Hq <= 0 || Hkv <= 0 || D <= 0 || n_cold < 0 || n_hot < 0 || n_cold + n_hot <= 0) return 0;
+  dflash_turbo_kv t{};
+  t.n_cold = n_cold;
+  t.n_hot = n_hot;
+  if (turbo_fused_applies(&t, nullptr, nullptr, 1.f)) return turbo_fused_workspace_bytes(B, Hq, Hkv, D, n_hot);
+  return dflash_verify_sdpa_workspace_bytes_ex(B, Hq, Hkv, D, n_cold + n_hot, DFLASH_KV_TURBO3);
 }
 
 int32_t dflash_greedy_tokens(const void* logits, const uint8_t* suppress, uint32_t* posterior,

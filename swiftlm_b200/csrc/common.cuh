@@ -129,6 +129,19 @@ struct SdpaArgs {
   int dtype;
 };
 
+// KV in the TurboQuant 3-bit format for the fused attention (sdpa_tc.cu, TURBO instantiation)
+struct TurboKvArgs {
+  const uint8_t *kp, *ks, *vp;        // packed indices / sign bits of the cold history
+  const uint16_t *kn, *kr, *vn;       // fp16 bits of the norms
+  const void* q2;                     // Rq^T q, laid out as q
+  int n_cold, n_hot;
+};
+int32_t launch_sdpa_tc_turbo(const SdpaArgs& a, const TurboKvArgs& t, cudaStream_t stream);
+size_t sdpa_tc_scratch_bytes(int D);
+int32_t launch_turbo_rotate_inputs(const void* q, void* q1, void* q2, long long q_blocks, const void* k_hot, void* k_rot,
+                                   const void* v_hot, void* v_rot, long long hot_blocks, int dtype, cudaStream_t stream);
+int32_t launch_turbo_unrotate_output(const void* o_rot, void* out, long long blocks, int dtype, cudaStream_t stream);
+
 size_t sdpa_workspace_bytes(int B, int Hq, int Hkv, int D, int N);
 // Scratch of the kernel a call will actually run on, given a workspace at least this large.
 size_t sdpa_scratch_bytes_for_call(int B, int Hq, int D, float scale, bool ragged);

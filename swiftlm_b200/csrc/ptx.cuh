@@ -32,6 +32,9 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(void* bar, uint32_t bytes)
 __device__ __forceinline__ void mbar_arrive(void* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
+__device__ __forceinline__ void mbar_arrive_n(void* bar, uint32_t n) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(n) : "memory");
+}
 __device__ __forceinline__ bool mbar_try_wait(void* bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
@@ -91,6 +94,12 @@ __device__ __forceinline__ void tma_load_4d(void* dst, const CUtensorMap* m, int
       "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];"
       ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(x), "r"(y), "r"(z), "r"(w), "r"(smem_u32(bar))
       : "memory");
+}
+
+// Untiled bulk copy global -> shared (both addresses 16-byte aligned, size a multiple of 16), completion on an mbarrier.
+__device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t bytes, void* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
 }
 
 // Tiled store shared -> global; completion is tracked by the issuing thread's bulk async-groups.

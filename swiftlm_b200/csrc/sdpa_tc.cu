@@ -46,6 +46,7 @@
 
 #include "common.cuh"
 #include "ptx.cuh"
+#include "turbo_tables.cuh"
 
 // Optional timeline instrumentation (compile with -DDFLASH_SDPA_TRACE; never part of the shipped
 // library): per CTA 64 words of %globaltimer stamps and clock64 wait accumulators.
@@ -79,6 +80,8 @@ constexpr int kBlockN = 128;            // keys per tile
 constexpr int kRowsM = 128;             // query rows per unit tile
 constexpr int kChunkBytes = 128 * 128;  // one TMA box: 128 rows x 64 16-bit elements
 constexpr int kThreads = 320;          // TMA warp, MMA warp, 8 softmax warps
+constexpr int kUnpackThreads = 128;    // compressed KV only: 4 more warps expand packed keys and values into the ring
+template <bool TURBO> struct ThreadsOf { static constexpr int value = TURBO ? kThreads + kUnpackThreads : kThreads; };
 constexpr float kRescaleThreshold = 8.f;   // in log2 units
 constexpr int kFusedMax = 4;               // a unit cut into at most this many ranges is merged by its last finisher
 
@@ -100,15 +103,38 @@ struct TcParams {
   float* part_m;           // [2 * gridDim.x][128]  (reference maximum, log2 units)
   float* part_l;           // [2 * gridDim.x][128]
   int* status;
+  // ---- KV in the TurboQuant 3-bit format (the TURBO instantiation; see the unpack role in the kernel) ----
+  // cold history, arrays over [B, Hkv, n_cold, D / 128 blocks]; a.q is then Q1 = R q, map_q2 covers Q2 = Rq^T q, a.k / a.v
+  // are the hot window's keys and values in the rotated domain [B, Hkv, n_hot, D], and a.out receives the output in
+  // the rotated domain
+  const uint8_t* t_kp;     // [.., 48] 3-bit centroid indices of the keys
+  const uint8_t* t_ks;     // [.., 16] sign bits of the keys' rotated residuals
+  const uint16_t* t_kn;    // fp16 bits: ||k||
+  const uint16_t* t_kr;    // fp16 bits: ||residual||
+  const uint8_t* t_vp;     // [.., 48]
+  const uint16_t* t_vn;    // fp16 bits: ||v|| / ||centroid vector||
+  int n_cold;              // compressed keys per (sequence, KV head): a multiple of 128
+  int tiles_cold;          // n_cold / 128; tiles at or beyond it come from the hot window
 };
 
-template <int D>
+template <int D, bool TURBO>
 struct Smem {
   static constexpr int kQChunks = D / 64;
-  static constexpr int kStages = (D == 256) ? 10 : 12;   // even: V chunks are consumed in pairs
+  // even: V chunks are consumed in pairs.  Compressed KV: the second query tile takes the room of most of the ring;
+  // four stages are enough there because chunks are produced by the CTA itself, a few hundred clocks ahead of their use
+  static constexpr int kStages = TURBO ? 4 : ((D == 256) ? 10 : 12);
   static constexpr uint32_t q = 0;
-  static constexpr uint32_t ring = kQChunks * kChunkBytes;
-  static constexpr uint32_t bars = ring + kStages * kChunkBytes;
+  static constexpr uint32_t q2 = kQChunks * kChunkBytes;                     // TURBO: Q2 = Rq^T q
+  static constexpr uint32_t ring = (TURBO ? 2 : 1) * kQChunks * kChunkBytes;
+  // TURBO: landing areas of the packed arrays of one 128-key tile
+  static constexpr uint32_t stg_a = ring + kStages * kChunkBytes;            // kp [128][D/128][48] | kn [128][D/128] | kr [128][D/128]
+  static constexpr uint32_t stg_a_kn = stg_a + 48 * D;
+  static constexpr uint32_t stg_a_kr = stg_a_kn + 2 * D;
+  static constexpr uint32_t stg_b = stg_a + 52 * D;                          // ks [128][D/128][16]
+  static constexpr uint32_t stg_c = stg_b + 16 * D;                          // vp [128][D/128][48] | vn [128][D/128]
+  static constexpr uint32_t stg_c_vn = stg_c + 48 * D;
+  static constexpr uint32_t stg_end = stg_c + 50 * D;
+  static constexpr uint32_t bars = TURBO ? stg_end : ring + kStages * kChunkBytes;
   // barrier slots (8 bytes each)
   static constexpr int b_q_full = 0, b_q_empty = 1, b_pv_done = 2, b_o_free = 3;
   static constexpr int b_s_full = 4;                 // 2
@@ -117,12 +143,15 @@ struct Smem {
   static constexpr int b_kv_empty = 8 + kStages;     // kStages
   static constexpr int b_peer_ready = 8 + 2 * kStages;   // the cluster partner has stopped using its ring
   static constexpr int b_peer_data = 9 + 2 * kStages;    // the partner's columns have landed here (256 arrivals)
-  static constexpr int n_bars = 10 + 2 * kStages;
+  static constexpr int b_stg_full = 10 + 2 * kStages;    // 3 (TURBO): a landing area holds its tile
+  static constexpr int b_stg_empty = 13 + 2 * kStages;   // 3 (TURBO): the unpack warps have read it (4 arrivals)
+  static constexpr int n_bars = 16 + 2 * kStages;
   static constexpr uint32_t misc = bars + 8 * n_bars;   // tmem base, abort flag, range info, group counter, merge decision
   static constexpr uint32_t xseq = misc + 64;            // exchange sequence numbers [2][2][4]
   static constexpr uint32_t xch = xseq + 64;             // exchange values [2 slots][2 halves][128 rows]
   static constexpr uint32_t total = xch + 2 * 2 * 128 * 4;
   static constexpr uint32_t alloc = total;               // the dynamic shared window starts 1024-byte aligned (checked)
+  static_assert(total <= 232448, "shared memory of one CTA");
 };
 
 // ---- work decomposition -------------------------------------------------------------------
@@ -314,11 +343,78 @@ template <typename InT> __device__ __forceinline__ float mask_floor();
 template <> __device__ __forceinline__ float mask_floor<__nv_bfloat16>() { return -3.3895313892515355e38f; }
 template <> __device__ __forceinline__ float mask_floor<__half>() { return -65504.f; }
 
-template <typename InT, int D, bool MASK>
-__global__ void __launch_bounds__(kThreads, 1)
-sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-               const __grid_constant__ CUtensorMap map_v, const TcParams p) {
-  using SL = Smem<D>;
+// ---- compressed KV: expanding one key's 64 dimensions into a row of an operand chunk -------------------------------
+// A chunk is what a TMA box of the dense path is: 128 keys x 64 16-bit elements, 128 bytes per key, the eight 16-byte
+// pieces of a row XOR-swizzled with the row index (CU_TENSOR_MAP_SWIZZLE_128B).  One thread writes one row.
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
+  uint32_t r;
+  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(sel));
+  return r;
+}
+__device__ __forceinline__ float f16_bits_to_float(uint16_t h) { return __half2float(__ushort_as_half(h)); }
+
+template <typename InT> __device__ __forceinline__ uint32_t pack2_rn(float a, float b);
+template <> __device__ __forceinline__ uint32_t pack2_rn<__nv_bfloat16>(float a, float b) {
+  const __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
+template <> __device__ __forceinline__ uint32_t pack2_rn<__half>(float a, float b) {
+  const __half2 v = __floats2half2_rn(a, b);
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
+
+// 64 three-bit centroid indices (24 bytes at `src`, 8-byte aligned) -> 64 values scale * centroid in the attention
+// dtype.  The eight scaled centroids are split into a table of their low bytes and one of their high bytes; four
+// indices at a time select from both with byte permutes.
+template <typename InT>
+__device__ __forceinline__ void unpack_centroid_row(uint8_t* chunk, int row, const uint8_t* src, float scale) {
+  const uint2 a = *reinterpret_cast<const uint2*>(src), b = *reinterpret_cast<const uint2*>(src + 8), c = *reinterpret_cast<const uint2*>(src + 16);
+  const uint32_t w[7] = {a.x, a.y, b.x, b.y, c.x, c.y, 0u};
+  const uint32_t p0 = pack2_rn<InT>(TURBO_C3[0] * scale, TURBO_C3[1] * scale), p1 = pack2_rn<InT>(TURBO_C3[2] * scale, TURBO_C3[3] * scale);
+  const uint32_t p2 = pack2_rn<InT>(TURBO_C3[4] * scale, TURBO_C3[5] * scale), p3 = pack2_rn<InT>(TURBO_C3[6] * scale, TURBO_C3[7] * scale);
+  const uint32_t lo_a = prmt(p0, p1, 0x6420), lo_b = prmt(p2, p3, 0x6420), hi_a = prmt(p0, p1, 0x7531), hi_b = prmt(p2, p3, 0x7531);
+  uint8_t* dst = chunk + row * 128;
+  const int sw = row & 7;
+#pragma unroll
+  for (int piece = 0; piece < 8; ++piece) {      // 8 indices = 24 bits -> 8 values = 16 bytes
+    const int bit = piece * 24, word = bit >> 5, off = bit & 31;
+    const uint32_t x = off ? __funnelshift_r(w[word], w[word + 1], off) : w[word];
+    uint32_t o[4];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const uint32_t y = x >> (12 * h);
+      const uint32_t sel = (y & 0x7u) | ((y << 1) & 0x70u) | ((y << 2) & 0x700u) | ((y << 3) & 0x7000u);
+      const uint32_t lo4 = prmt(lo_a, lo_b, sel), hi4 = prmt(hi_a, hi_b, sel);
+      o[2 * h] = prmt(lo4, hi4, 0x5140);
+      o[2 * h + 1] = prmt(lo4, hi4, 0x7362);
+    }
+    *reinterpret_cast<uint4*>(dst + ((piece ^ sw) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+  }
+}
+// 64 sign bits (8 bytes at `src`) -> 64 values +-mag: bit set = +mag (tests/test_turbo_quant.cpp:97 of the SwiftLM tree)
+template <typename InT>
+__device__ __forceinline__ void unpack_sign_row(uint8_t* chunk, int row, const uint8_t* src, float mag) {
+  const uint2 a = *reinterpret_cast<const uint2*>(src);
+  const uint32_t nw[2] = {~a.x, ~a.y};          // set bit = negative
+  const uint32_t m2 = pack2_rn<InT>(mag, mag);
+  uint8_t* dst = chunk + row * 128;
+  const int sw = row & 7;
+#pragma unroll
+  for (int piece = 0; piece < 8; ++piece) {      // 8 bits -> 8 values = 16 bytes
+    const uint32_t t = nw[piece >> 2] >> ((piece & 3) * 8);
+    uint32_t o[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) o[k] = m2 ^ ((t << (15 - 2 * k)) & 0x8000u) ^ ((t << (30 - 2 * k)) & 0x80000000u);
+    *reinterpret_cast<uint4*>(dst + ((piece ^ sw) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+  }
+}
+
+template <typename InT, int D, bool MASK, bool TURBO>
+__global__ void __launch_bounds__(ThreadsOf<TURBO>::value, 1)
+sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_q2,
+               const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, const TcParams p) {
+  using SL = Smem<D, TURBO>;
+  constexpr int kNumThreads = ThreadsOf<TURBO>::value;
   constexpr int kStages = SL::kStages;
   constexpr int kQChunks = SL::kQChunks;            // 64-element chunks of the head dimension
   constexpr uint32_t kFmt = sizeof(InT) == 2 && std::is_same<InT, __nv_bfloat16>::value ? 1u : 0u;
@@ -363,11 +459,15 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
 
   if (threadIdx.x == 0) {
     ptx::prefetch_tensormap(&map_q);
+    if (TURBO) ptx::prefetch_tensormap(&map_q2);
     ptx::prefetch_tensormap(&map_k);
     ptx::prefetch_tensormap(&map_v);
     for (int i = 0; i < SL::n_bars; ++i) {
-      const bool four = (i == SL::b_o_free) || (i == SL::b_p_full) || (i == SL::b_p_full + 1);
-      ptx::mbar_init(&bars[i], i == SL::b_peer_data ? 256 : (four ? 8 : 1));
+      const bool eight = (i == SL::b_o_free) || (i == SL::b_p_full) || (i == SL::b_p_full + 1);
+      // compressed KV: a ring stage is filled either by the four unpack warps (one arrival each) or by a TMA load
+      // (the producer arrives four times); a landing area is released by the four unpack warps
+      const bool four = TURBO && ((i >= SL::b_kv_full && i < SL::b_kv_full + kStages) || (i >= SL::b_stg_empty && i < SL::b_stg_empty + 3));
+      ptx::mbar_init(&bars[i], i == SL::b_peer_data ? 256 : (eight ? 8 : (four ? 4 : 1)));
     }
     *abort_flag = 0;
     reinterpret_cast<volatile uint32_t*>(sm + SL::misc)[4] = 0;   // group counter
@@ -409,10 +509,10 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
   if (warp == 0) {
     __syncwarp();
     __threadfence_block();
-    asm volatile("bar.arrive 1, %0;" ::"n"(kThreads) : "memory");
+    asm volatile("bar.arrive 1, %0;" ::"n"(kNumThreads) : "memory");
   } else {
     ptx::tc_fence_before();
-    asm volatile("bar.sync 1, %0;" ::"n"(kThreads) : "memory");
+    asm volatile("bar.sync 1, %0;" ::"n"(kNumThreads) : "memory");
     ptx::tc_fence_after();
     tmem_base = *tmem_base_slot;
   }
@@ -439,6 +539,14 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
           TR_ACC(16);
         }
         ptx::mbar_arrive_expect_tx(&bars[SL::b_kv_full + stage], kChunkBytes);
+        if (TURBO) {
+          // a tile of the uncompressed hot window (rotated domain), [B, Hkv, n_hot, D]; the stage's barrier counts four arrivals
+          ptx::mbar_arrive_n(&bars[SL::b_kv_full + stage], 3);
+          ptx::tma_load_4d(sm + SL::ring + stage * kChunkBytes, map, c * 64, (tile - p.tiles_cold) * kBlockN, sg.kvh, sg.b,
+                           &bars[SL::b_kv_full + stage]);
+          ++fill;
+          return true;
+        }
         const int n0 = tile * kBlockN;
         if (a.page_table) {
           if (c == 0) {
@@ -458,18 +566,57 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         ++fill;
         return true;
       };
+      // Compressed KV: the packed arrays of a 128-key tile of the cold history land in three areas (A: key indices and
+      // norms, B: key sign bits, C: value indices and norms), each refilled as soon as the unpack warps have read it; the
+      // unpack warps, not this lane, fill the ring for those tiles.
+      uint32_t n_stg[3] = {0, 0, 0};
+      auto stage_area = [&](int area) -> bool {       // wait until the area's previous tile has been read, then expect the new one
+        if (n_stg[area] > 0 && !wait_or_abort(&bars[SL::b_stg_empty + area], (n_stg[area] - 1) & 1, abort_flag, p.status)) return false;
+        ptx::mbar_arrive_expect_tx(&bars[SL::b_stg_full + area], (area == 0 ? 52u : area == 1 ? 16u : 50u) * D);
+        ++n_stg[area];
+        return true;
+      };
+      auto cold_blocks = [&](const Segment& sg, int tile) -> long long {   // first 128-dimension block of the tile's keys
+        return (((long long)sg.b * a.Hkv + sg.kvh) * p.n_cold + (long long)tile * kBlockN) * (D / 128);
+      };
+      auto stage_cold_k = [&](const Segment& sg, int tile) -> bool {
+        const long long blk = cold_blocks(sg, tile);
+        if (!stage_area(0)) return false;
+        ptx::bulk_load(sm + SL::stg_a, p.t_kp + blk * 48, 48 * D, &bars[SL::b_stg_full + 0]);
+        ptx::bulk_load(sm + SL::stg_a_kn, p.t_kn + blk, 2 * D, &bars[SL::b_stg_full + 0]);
+        ptx::bulk_load(sm + SL::stg_a_kr, p.t_kr + blk, 2 * D, &bars[SL::b_stg_full + 0]);
+        if (!stage_area(1)) return false;
+        ptx::bulk_load(sm + SL::stg_b, p.t_ks + blk * 16, 16 * D, &bars[SL::b_stg_full + 1]);
+        fill += 2 * kQChunks;
+        return true;
+      };
+      auto stage_cold_v = [&](const Segment& sg, int tile) -> bool {
+        const long long blk = cold_blocks(sg, tile);
+        if (!stage_area(2)) return false;
+        ptx::bulk_load(sm + SL::stg_c, p.t_vp + blk * 48, 48 * D, &bars[SL::b_stg_full + 2]);
+        ptx::bulk_load(sm + SL::stg_c_vn, p.t_vn + blk, 2 * D, &bars[SL::b_stg_full + 2]);
+        fill += kQChunks;
+        return true;
+      };
       while (ok && it.next(s)) {
         // Q tile of this unit: wait until the previous segment's S = Q K^T products are done with it
         if (seg_idx > 0 && !wait_or_abort(&bars[SL::b_q_empty], (seg_idx - 1) & 1, abort_flag, p.status)) break;
-        ptx::mbar_arrive_expect_tx(&bars[SL::b_q_full], kQChunks * kChunkBytes);
+        ptx::mbar_arrive_expect_tx(&bars[SL::b_q_full], (TURBO ? 2 : 1) * kQChunks * kChunkBytes);
         for (int c = 0; c < kQChunks; ++c)
           ptx::tma_load_3d(sm + SL::q + c * kChunkBytes, &map_q, c * 64, s.mt * kRowsM, s.b * a.Hkv + s.kvh, &bars[SL::b_q_full]);
+        if (TURBO)
+          for (int c = 0; c < kQChunks; ++c)
+            ptx::tma_load_3d(sm + SL::q2 + c * kChunkBytes, &map_q2, c * 64, s.mt * kRowsM, s.b * a.Hkv + s.kvh, &bars[SL::b_q_full]);
         // K_lo, then (K_{j+1}, V_j) pairs, then V_last: the order the MMA warp consumes them
         for (int j = s.tile_lo; ok && j <= s.tile_hi; ++j) {
-          if (j < s.tile_hi)
-            for (int c = 0; ok && c < kQChunks; ++c) ok = load_chunk(&map_k, ref_k, s, j, c);
-          if (j > s.tile_lo)
-            for (int c = 0; ok && c < kQChunks; ++c) ok = load_chunk(&map_v, ref_v, s, j - 1, c);
+          if (j < s.tile_hi) {
+            if (TURBO && j < p.tiles_cold) ok = stage_cold_k(s, j);
+            else for (int c = 0; ok && c < kQChunks; ++c) ok = load_chunk(&map_k, ref_k, s, j, c);
+          }
+          if (ok && j > s.tile_lo) {
+            if (TURBO && j - 1 < p.tiles_cold) ok = stage_cold_v(s, j - 1);
+            else for (int c = 0; ok && c < kQChunks; ++c) ok = load_chunk(&map_v, ref_v, s, j - 1, c);
+          }
         }
         ++seg_idx;
       }
@@ -493,7 +640,9 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
             // ---- S[buf] = Q K_j^T ----
             const uint32_t t = tile_ctr + jj, buf = t & 1;
             const uint32_t d_tmem = tmem_base + kColS + buf * kBlockN;
-            for (int c = 0; ok && c < kQChunks; ++c) {
+            // compressed keys: the scaled centroids against Q1, then the scaled residual signs against Q2, one accumulator
+            const int n_kc = (TURBO && s.tile_lo + jj < p.tiles_cold) ? 2 * kQChunks : kQChunks;
+            for (int c = 0; ok && c < n_kc; ++c) {
               const uint32_t stage = drain % kStages;
               {
                 TR_T0();
@@ -504,7 +653,7 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
               if (!ok) break;
               ptx::tc_fence_after();
               // descriptors differ only in the start-address field: +2 (32 bytes) per 16-element step
-              const uint64_t da0 = make_desc(q_addr + c * kChunkBytes, 16, 1024);
+              const uint64_t da0 = make_desc(q_addr + (c < kQChunks ? c * kChunkBytes : SL::q2 + (c - kQChunks) * kChunkBytes), 16, 1024);
               const uint64_t db0 = make_desc(ptx::smem_u32(sm + SL::ring + stage * kChunkBytes), 16, 1024);
               {
                 TR_T0();
@@ -574,6 +723,95 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         }
         tile_ctr += ntiles;
         ++seg_idx;
+      }
+    }
+  } else if (TURBO && warp >= kThreads / 32) {
+    // ====================================== unpack =======================================
+    // Compressed KV: thread t of these four warps owns key row t of every operand chunk of a cold tile.  Per tile it
+    // expands, from the landing areas, the key's centroid indices into D / 64 chunks scaled by the key block's norm,
+    // its residual sign bits into D / 64 chunks of +-(norm * QJL_C / 128 * rnorm), and (one tile behind, as the MMA
+    // warp consumes them) the value's centroid indices scaled by the value block's norm - the operands the dense
+    // path gets by TMA, in the same swizzled layout, so that no decoded key or value ever exists in global memory.
+    if (begin < end) {
+      const int t = (int)threadIdx.x - kThreads;
+      constexpr int NB = D / 128;
+      SegmentIter it(p, begin, end, unit0, tile0);
+      Segment s;
+      uint32_t fill = 0, n_stg[3] = {0, 0, 0};
+      bool ok = true;
+      float nrm[NB], mag[NB];
+      auto wait_all = [&](void* bar, uint32_t parity) -> bool {
+        return __all_sync(0xffffffffu, wait_or_abort(bar, parity, abort_flag, p.status));
+      };
+      auto ring_slot = [&](uint8_t*& chunk) -> bool {            // the next stage, once the MMA warp has released it
+        const uint32_t stage = fill % kStages;
+        if (fill >= (uint32_t)kStages && !wait_all(&bars[SL::b_kv_empty + stage], ((fill / kStages) - 1) & 1)) return false;
+        chunk = sm + SL::ring + stage * kChunkBytes;
+        return true;
+      };
+      auto publish = [&]() {                                     // this warp's 32 rows of the stage are written
+        ptx::fence_proxy_async();
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(&bars[SL::b_kv_full + fill % kStages]);
+        ++fill;
+      };
+      auto release = [&](int area) {
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(&bars[SL::b_stg_empty + area]);
+        ++n_stg[area];
+      };
+      auto unpack_k = [&]() -> bool {
+        if (!wait_all(&bars[SL::b_stg_full + 0], n_stg[0] & 1)) return false;
+        const uint16_t* kn = reinterpret_cast<const uint16_t*>(sm + SL::stg_a_kn);
+        const uint16_t* kr = reinterpret_cast<const uint16_t*>(sm + SL::stg_a_kr);
+#pragma unroll
+        for (int j = 0; j < NB; ++j) {
+          nrm[j] = f16_bits_to_float(kn[t * NB + j]);
+          mag[j] = nrm[j] * ((TURBO_QJL_C / 128.f) * f16_bits_to_float(kr[t * NB + j]));
+        }
+#pragma unroll 1
+        for (int c = 0; c < kQChunks; ++c) {
+          uint8_t* chunk;
+          if (!ring_slot(chunk)) return false;
+          unpack_centroid_row<InT>(chunk, t, sm + SL::stg_a + (t * NB + (c >> 1)) * 48 + (c & 1) * 24, nrm[c >> 1]);
+          publish();
+        }
+        release(0);
+        if (!wait_all(&bars[SL::b_stg_full + 1], n_stg[1] & 1)) return false;
+#pragma unroll 1
+        for (int c = 0; c < kQChunks; ++c) {
+          uint8_t* chunk;
+          if (!ring_slot(chunk)) return false;
+          unpack_sign_row<InT>(chunk, t, sm + SL::stg_b + (t * NB + (c >> 1)) * 16 + (c & 1) * 8, mag[c >> 1]);
+          publish();
+        }
+        release(1);
+        return true;
+      };
+      auto unpack_v = [&]() -> bool {
+        if (!wait_all(&bars[SL::b_stg_full + 2], n_stg[2] & 1)) return false;
+        const uint16_t* vn = reinterpret_cast<const uint16_t*>(sm + SL::stg_c_vn);
+#pragma unroll 1
+        for (int c = 0; c < kQChunks; ++c) {
+          uint8_t* chunk;
+          if (!ring_slot(chunk)) return false;
+          unpack_centroid_row<InT>(chunk, t, sm + SL::stg_c + (t * NB + (c >> 1)) * 48 + (c & 1) * 24, f16_bits_to_float(vn[t * NB + (c >> 1)]));
+          publish();
+        }
+        release(2);
+        return true;
+      };
+      while (ok && it.next(s)) {
+        for (int j = s.tile_lo; ok && j <= s.tile_hi; ++j) {
+          if (j < s.tile_hi) {
+            if (j < p.tiles_cold) ok = unpack_k();
+            else fill += kQChunks;                      // a hot tile: the producer's TMA loads fill these stages
+          }
+          if (ok && j > s.tile_lo) {
+            if (j - 1 < p.tiles_cold) ok = unpack_v();
+            else fill += kQChunks;
+          }
+        }
       }
     }
   } else {
@@ -1126,9 +1364,9 @@ unsigned long long next_epoch() {
   return e ? e : counter.fetch_add(1);
 }
 
-template <typename InT, int D, bool MASK>
-int32_t launch_typed(const SdpaArgs& a, cudaStream_t stream) {
-  using SL = Smem<D>;
+template <typename InT, int D, bool MASK, bool TURBO>
+int32_t launch_typed(const SdpaArgs& a, const TurboKvArgs* turbo, cudaStream_t stream) {
+  using SL = Smem<D, TURBO>;
   EncodeTiledFn encode = tensor_map_encoder();
   if (!encode) { set_error("cuTensorMapEncodeTiled is not available from this driver"); return DFLASH_ERR_CUDA; }
   int* status = device_status_word();
@@ -1150,6 +1388,14 @@ int32_t launch_typed(const SdpaArgs& a, cudaStream_t stream) {
   p.inv_scale = 1.f / a.scale;
   p.mask_vec = (a.mask && (reinterpret_cast<uintptr_t>(a.mask) & 15u) == 0 && a.N % 8 == 0) ? 1 : 0;
   p.status = status;
+  p.t_kp = p.t_ks = p.t_vp = nullptr;
+  p.t_kn = p.t_kr = p.t_vn = nullptr;
+  p.n_cold = p.tiles_cold = 0;
+  if (TURBO) {
+    p.t_kp = turbo->kp; p.t_ks = turbo->ks; p.t_kn = turbo->kn; p.t_kr = turbo->kr; p.t_vp = turbo->vp; p.t_vn = turbo->vn;
+    p.n_cold = turbo->n_cold;
+    p.tiles_cold = turbo->n_cold / kBlockN;
+  }
   const int n_sm = sm_count();
   long long grid = p.total_tiles < n_sm ? p.total_tiles : n_sm;   // upper bound also for ragged lengths
   if (grid < 1) grid = 1;
@@ -1166,7 +1412,7 @@ int32_t launch_typed(const SdpaArgs& a, cudaStream_t stream) {
     if (mode != 0 && c >= 1 && c <= kFusedMax && tiles_per_unit >= c && (long long)p.units * c * 5 >= (long long)n_sm * 4 &&
         (mode > 0 || idle_tiles < 10.0)) {
       p.split = c;
-      p.pair = c == 2 ? 1 : 0;
+      p.pair = (c == 2 && !TURBO) ? 1 : 0;   // compressed KV: the two ranges of a unit meet through the partials instead
       grid = (long long)p.units * c;
       need_merge_kernel = false;
     } else {
@@ -1190,15 +1436,19 @@ int32_t launch_typed(const SdpaArgs& a, cudaStream_t stream) {
   p.part_l = p.part_m + slots * kRowsM;
 
   const CUtensorMapDataType dt = std::is_same<InT, __nv_bfloat16>::value ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
-  CUtensorMap mq, mk, mv;
-  {
+  CUtensorMap mq, mq2, mk, mv;
+  auto encode_q = [&](CUtensorMap* m, const void* base) -> CUresult {
     // Q as (d, row in (b,kvh) group, b*Hkv+kvh): rows past the group read as zeros
     const cuuint64_t dims[3] = {(cuuint64_t)D, (cuuint64_t)p.R, (cuuint64_t)a.B * a.Hkv};
     const cuuint64_t strides[2] = {(cuuint64_t)D * 2, (cuuint64_t)p.R * D * 2};
     const cuuint32_t box[3] = {64, (cuuint32_t)kRowsM, 1};
     const cuuint32_t es[3] = {1, 1, 1};
-    const CUresult r = encode(&mq, dt, 3, const_cast<void*>(a.q), dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return encode(m, dt, 3, const_cast<void*>(base), dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  };
+  {
+    CUresult r = encode_q(&mq, a.q);
+    if (r == CUDA_SUCCESS) r = encode_q(&mq2, TURBO ? turbo->q2 : a.q);
     if (r != CUDA_SUCCESS) { set_error("cuTensorMapEncodeTiled(q) failed with CUresult %d", (int)r); return DFLASH_ERR_CUDA; }
   }
   auto encode_kv = [&](CUtensorMap* m, const void* base) -> CUresult {
@@ -1207,6 +1457,11 @@ int32_t launch_typed(const SdpaArgs& a, cudaStream_t stream) {
       // pool [num_pages, Hkv, page_tokens, D]: a page coordinate at or beyond num_pages is filled with zeros
       dims[0] = D; dims[1] = a.page_tokens; dims[2] = a.Hkv; dims[3] = (cuuint64_t)a.num_pages;
       strides[0] = (cuuint64_t)D * 2; strides[1] = (cuuint64_t)a.page_tokens * D * 2; strides[2] = (cuuint64_t)a.Hkv * a.page_tokens * D * 2;
+    } else if (TURBO) {
+      // the hot window in the rotated domain, [B, Hkv, n_hot, D]; rows at or beyond n_hot read as zeros
+      const cuuint64_t n_hot = turbo->n_hot > 0 ? turbo->n_hot : 1;
+      dims[0] = D; dims[1] = n_hot; dims[2] = a.Hkv; dims[3] = a.B;
+      strides[0] = (cuuint64_t)D * 2; strides[1] = n_hot * D * 2; strides[2] = (cuuint64_t)a.Hkv * n_hot * D * 2;
     } else {
       dims[0] = D; dims[1] = a.N; dims[2] = a.Hkv; dims[3] = a.B;
       strides[0] = (cuuint64_t)D * 2; strides[1] = (cuuint64_t)a.N * D * 2; strides[2] = (cuuint64_t)a.Hkv * a.N * D * 2;
@@ -1216,16 +1471,19 @@ int32_t launch_typed(const SdpaArgs& a, cudaStream_t stream) {
     return encode(m, dt, 4, const_cast<void*>(base), dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   };
-  CUresult r = encode_kv(&mk, a.k);
-  if (r == CUDA_SUCCESS) r = encode_kv(&mv, a.v);
+  // compressed KV without a hot window: no tile ever uses these two maps; they cover the first query tile instead
+  const bool no_hot = TURBO && turbo->n_hot <= 0;
+  CUresult r = no_hot ? encode_q(&mk, a.q) : encode_kv(&mk, a.k);
+  if (r == CUDA_SUCCESS) r = no_hot ? encode_q(&mv, a.q) : encode_kv(&mv, a.v);
   if (r != CUDA_SUCCESS) { set_error("cuTensorMapEncodeTiled(k/v) failed with CUresult %d", (int)r); return DFLASH_ERR_CUDA; }
 
-  auto kernel = sdpa_tc_kernel<InT, D, MASK>;
+  auto kernel = sdpa_tc_kernel<InT, D, MASK, TURBO>;
+  constexpr int kNumThreads = ThreadsOf<TURBO>::value;
   DFLASH_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SL::alloc));
   if (p.pair) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)grid);
-    cfg.blockDim = dim3(kThreads);
+    cfg.blockDim = dim3(kNumThreads);
     cfg.dynamicSmemBytes = SL::alloc;
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
@@ -1235,9 +1493,9 @@ int32_t launch_typed(const SdpaArgs& a, cudaStream_t stream) {
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    DFLASH_CUDA_CHECK(cudaLaunchKernelEx(&cfg, kernel, mq, mk, mv, p));
+    DFLASH_CUDA_CHECK(cudaLaunchKernelEx(&cfg, kernel, mq, mq2, mk, mv, p));
   } else {
-    kernel<<<(unsigned)grid, kThreads, SL::alloc, stream>>>(mq, mk, mv, p);
+    kernel<<<(unsigned)grid, kNumThreads, SL::alloc, stream>>>(mq, mq2, mk, mv, p);
   }
   DFLASH_LAUNCH_CHECK();
   count_launch();
@@ -1250,6 +1508,8 @@ int32_t launch_typed(const SdpaArgs& a, cudaStream_t stream) {
 }
 
 }  // namespace
+
+size_t sdpa_tc_scratch_bytes(int D) { return tc_workspace_bytes(D); }
 
 size_t sdpa_workspace_bytes(int B, int Hq, int Hkv, int D, int N) {
   (void)Hkv; (void)N;
@@ -1278,7 +1538,15 @@ size_t sdpa_scratch_bytes_for_call(int B, int Hq, int D, float scale, bool ragge
 
 template <typename InT, int D>
 static int32_t launch_dims(const SdpaArgs& a, cudaStream_t stream) {
-  return a.mask ? launch_typed<InT, D, true>(a, stream) : launch_typed<InT, D, false>(a, stream);
+  return a.mask ? launch_typed<InT, D, true, false>(a, nullptr, stream) : launch_typed<InT, D, false, false>(a, nullptr, stream);
+}
+
+// Attention over KV in the TurboQuant 3-bit format without decoding it to global memory: a.q = Q1 = R q, t.q2 = Rq^T q,
+// a.k / a.v = the hot window in the rotated domain (or null), a.out = the output in the rotated domain.
+int32_t launch_sdpa_tc_turbo(const SdpaArgs& a, const TurboKvArgs& t, cudaStream_t stream) {
+  if (a.dtype == DFLASH_BF16)
+    return a.D == 256 ? launch_typed<__nv_bfloat16, 256, false, true>(a, &t, stream) : launch_typed<__nv_bfloat16, 128, false, true>(a, &t, stream);
+  return a.D == 256 ? launch_typed<__half, 256, false, true>(a, &t, stream) : launch_typed<__half, 128, false, true>(a, &t, stream);
 }
 
 int32_t launch_sdpa_tc(const SdpaArgs& a, cudaStream_t stream) {

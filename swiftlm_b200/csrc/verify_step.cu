@@ -23,6 +23,10 @@ using namespace dflash;
 
 extern "C" size_t dflash_verify_step_workspace_bytes(const dflash_verify_step_desc* d) {
   if (!d || d->attn_layers <= 0) return 0;
+  if (d->kv_format == DFLASH_KV_TURBO3 && d->attn_k) {
+    const dflash_turbo_kv* t = reinterpret_cast<const dflash_turbo_kv*>(d->attn_k);
+    return dflash_verify_sdpa_turbo_workspace_bytes(d->B * d->attn_layers, d->Hq, d->Hkv, d->D, t->n_cold, t->n_hot);
+  }
   return dflash_verify_sdpa_workspace_bytes_ex(d->B * d->attn_layers, d->Hq, d->Hkv, d->D, d->N, d->kv_format);
 }
 

@@ -284,9 +284,10 @@ def gated_delta_into(q, k, v, g, beta, state, n_per_seq, y, state_out, tape=None
 def batched_sdpa_turbo_kv(queries, k_enc, v_enc, n_cold: int, scale: float, k_hot=None, v_hot=None, out=None) -> Optional[torch.Tensor]:
     """Block-verify attention over KV held in the TurboQuant 3-bit format with a hot window: k_enc = (packed, signs,
     norm, rnorm) and v_enc = (packed, norm) as returned by turbo_encode for the cold history [B,Hkv,n_cold,D]; k_hot,
-    v_hot [B,Hkv,n_hot,D] in the attention dtype are the newest tokens (the verify block among them).  The library
-    expands the cold history into its workspace, appends the hot window and attends over the copy (dflash_verify_sdpa
-    with DFLASH_KV_TURBO3)."""
+    v_hot [B,Hkv,n_hot,D] in the attention dtype are the newest tokens (the verify block among them).  With a cold
+    history of whole 128-key tiles the library attends in the codec's rotated domain without decoding a key or value
+    to global memory; otherwise it expands the cold history into its workspace and attends over the copy
+    (dflash_verify_sdpa with DFLASH_KV_TURBO3)."""
     _need_cuda(queries, k_enc[0], v_enc[0])
     B, Hq, T, D = queries.shape
     dt = queries.dtype
@@ -299,7 +300,7 @@ def batched_sdpa_turbo_kv(queries, k_enc, v_enc, n_cold: int, scale: float, k_ho
     n_hot = 0 if k_hot is None else k_hot.shape[2]
     n_keys = n_cold + n_hot
     L = _lib.lib()
-    ws = _workspace(q.device, L.dflash_verify_sdpa_workspace_bytes_ex(B, Hq, Hkv, D, n_keys, _lib.KV_TURBO3))
+    ws = _workspace(q.device, L.dflash_verify_sdpa_turbo_workspace_bytes(B, Hq, Hkv, D, n_cold, n_hot))
     kp, ks, kn, kr = (t.contiguous() for t in k_enc)
     vp, vn = (t.contiguous() for t in v_enc)
     kh = None if k_hot is None else k_hot.to(dt).contiguous()
