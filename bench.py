@@ -400,6 +400,7 @@ def run_gpu(args):
 
     variants = guarded(lambda: run_replay_variants(torch, kernels, device, x, y, state_out, heads, n_sum_heads, peaks, max_over_ranks))
     sd_long = guarded(lambda: run_sdpa_long(torch, kernels, device, rank, world, peaks, max_over_ranks))
+    sd_turbo = guarded(lambda: run_sdpa_turbo(torch, kernels, device, peaks))
     # ---- the composed verify step, configs[4]: 64 sequences sharded by sequence over the ranks ----
     del x
     torch.cuda.empty_cache()
@@ -446,6 +447,7 @@ def run_gpu(args):
         "sdpa": sd,
         "replay_variants": variants,
         "sdpa_long": sd_long,
+        "sdpa_turbo": sd_turbo,
         "verify_step": vstep,
     }
     print(json.dumps(line))
@@ -536,6 +538,64 @@ def run_sdpa(torch, kernels, device, args, peaks):
                          "frac_of_bf16_peak": tflops / peaks["bf16_tflops"],
                          "note": "arithmetic intensity 128 FLOP/B is below the ridge (~252): the HBM roofline "
                                  "caps this shape at ~49% of dense bf16 peak"}}
+
+
+def make_turbo_layer(torch, kernels, device, B, n_cold, seed):
+    """One attention layer of configs[4]: Hq=16, Hkv=2, D=256, a cold history of n_cold keys in the TurboQuant 3-bit format
+    (encoded from seeded N(0,1) K/V) and the block's own 16 tokens as the uncompressed hot window."""
+    Hq, Hkv, D, T = 16, 2, 256, 16
+    g = torch.Generator(device=device).manual_seed(seed)
+    q = torch.randn(B, Hq, T, D, device=device, generator=g).bfloat16()
+    enc = dict(kp=[], ks=[], kn=[], kr=[], vp=[], vn=[], kh=[], vh=[])
+    for lo in range(0, B, 16):
+        n = min(16, B - lo)
+        k = torch.randn(n, Hkv, n_cold + T, D, device=device, generator=g).bfloat16()
+        v = torch.randn(n, Hkv, n_cold + T, D, device=device, generator=g).bfloat16()
+        kp, ks, kn, kr = kernels.turbo_encode(k[:, :, :n_cold].contiguous(), True)
+        vp, _, vn, _ = kernels.turbo_encode(v[:, :, :n_cold].contiguous(), False)
+        for name, t in (("kp", kp), ("ks", ks), ("kn", kn), ("kr", kr), ("vp", vp), ("vn", vn),
+                        ("kh", k[:, :, n_cold:].contiguous()), ("vh", v[:, :, n_cold:].contiguous())):
+            enc[name].append(t)
+        del k, v
+    e = {name: torch.cat(ts) for name, ts in enc.items()}
+    blocks = B * Hkv * n_cold * (D // 128)
+    alg = blocks * (48 + 16 + 2 + 2 + 48 + 2) + 2 * B * Hkv * T * D * 2 + 2 * B * Hq * T * D * 2
+    return q, e, float(alg), 4.0 * B * Hq * T * (n_cold + T) * D
+
+
+def run_sdpa_turbo(torch, kernels, device, peaks):
+    """One attention layer of configs[4] (B=64, context 8192 in the TurboQuant 3-bit format, the block as the hot window):
+    the fused kernel, against the HBM time of the packed bytes and against the tensor peak (at 118 bytes per 128-dimension
+    key/value block pair the arithmetic intensity is ~550 FLOP/B, above the ridge)."""
+    B, n_cold = 64, 8192
+    sets = [make_turbo_layer(torch, kernels, device, B, n_cold, SEED + 4100 + i) for i in range(2)]   # 2 x 0.25 GB packed: beyond L2
+    out = torch.empty_like(sets[0][0])
+    scale = 1.0 / 16.0
+
+    def call(i):
+        q, e, _, _ = sets[i % 2]
+        kernels.batched_sdpa_turbo_kv(q, (e["kp"], e["ks"], e["kn"], e["kr"]), (e["vp"], e["vn"]), n_cold, scale,
+                                      k_hot=e["kh"], v_hot=e["vh"], out=out)
+    for i in range(4):
+        call(i)
+    torch.cuda.synchronize()
+    reps = []
+    for _ in range(5):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(6):
+            call(i)
+        e1.record()
+        torch.cuda.synchronize()
+        reps.append(e0.elapsed_time(e1) / 6)
+    kernels.device_status()
+    ms = statistics.median(reps)
+    alg, flops = sets[0][2], sets[0][3]
+    return {"config": "one attention layer of configs[4]: B=64, Hq=16, Hkv=2, D=256, 8192 compressed keys + the 16 block tokens; "
+                      "rotate in, fused attention, rotate out; 2 rotating KV sets; median of 5 bursts of 6 calls",
+            "ms_per_call": ms, "tflops": flops / (ms * 1e-3) / 1e12, "algorithmic_bytes_per_call": alg,
+            "gbs": alg / (ms * 1e-3) / 1e9, "frac_of_hbm_peak": alg / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
+            "frac_of_bf16_peak": flops / (ms * 1e-3) / 1e12 / peaks["bf16_tflops"]}
 
 
 def run_sdpa_long(torch, kernels, device, rank, world, peaks, max_over_ranks):
@@ -679,6 +739,15 @@ def run_case(args):
             kernels.turbo_decode_into(packed, signs, norm, rnorm, dec)
         blocks = kv.numel() // 128
         info = {"case": args.case, "blocks": blocks, "algorithmic_bytes_per_launch": blocks * ((68 if is_key else 50) + 256)}
+    elif args.case == "sdpa_turbo_small":
+        # a quarter of one attention layer of configs[4] (16 sequences, 0.06 GB packed; two sets so that the second call misses L2)
+        sets = [make_turbo_layer(torch, kernels, device, 16, 8192, SEED + 4100 + i) for i in range(3)]
+        out = torch.empty_like(sets[0][0])
+        for i in range(args.warmup + args.steps):
+            q, e, _, _ = sets[i % 3]
+            kernels.batched_sdpa_turbo_kv(q, (e["kp"], e["ks"], e["kn"], e["kr"]), (e["vp"], e["vn"]), 8192, 1.0 / 16.0,
+                                          k_hot=e["kh"], v_hot=e["vh"], out=out)
+        info = {"case": args.case, "flops_per_launch": sets[0][3], "algorithmic_bytes_per_launch": sets[0][2]}
     elif args.case == "sdpa_single_long":
         # one sequence with 102 400 + 16 keys (the reference's own serving shape at configs[3]'s context): two
         # (sequence, KV head) units, so every unit is cut into one key range per SM and the merge kernel combines them
@@ -712,7 +781,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--case", default=None, choices=["replay_small", "replay_vec_small", "delta_replay_small", "sdpa_small", "sdpa_single_long", "turbo_decode_k_small", "turbo_decode_v_small"],
+    ap.add_argument("--case", default=None, choices=["replay_small", "replay_vec_small", "delta_replay_small", "sdpa_small", "sdpa_turbo_small", "sdpa_single_long", "turbo_decode_k_small", "turbo_decode_v_small"],
                     help="run one small single-kernel case (for profiler captures) instead of the benchmark")
     args = ap.parse_args()
     if args.case:

@@ -32,9 +32,6 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(void* bar, uint32_t bytes)
 __device__ __forceinline__ void mbar_arrive(void* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
-__device__ __forceinline__ void mbar_arrive_n(void* bar, uint32_t n) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(n) : "memory");
-}
 __device__ __forceinline__ bool mbar_try_wait(void* bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(

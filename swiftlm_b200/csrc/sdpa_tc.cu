@@ -539,14 +539,6 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
           TR_ACC(16);
         }
         ptx::mbar_arrive_expect_tx(&bars[SL::b_kv_full + stage], kChunkBytes);
-        if (TURBO) {
-          // a tile of the uncompressed hot window (rotated domain), [B, Hkv, n_hot, D]; the stage's barrier counts four arrivals
-          ptx::mbar_arrive_n(&bars[SL::b_kv_full + stage], 3);
-          ptx::tma_load_4d(sm + SL::ring + stage * kChunkBytes, map, c * 64, (tile - p.tiles_cold) * kBlockN, sg.kvh, sg.b,
-                           &bars[SL::b_kv_full + stage]);
-          ++fill;
-          return true;
-        }
         const int n0 = tile * kBlockN;
         if (a.page_table) {
           if (c == 0) {
@@ -567,8 +559,10 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         return true;
       };
       // Compressed KV: the packed arrays of a 128-key tile of the cold history land in three areas (A: key indices and
-      // norms, B: key sign bits, C: value indices and norms), each refilled as soon as the unpack warps have read it; the
-      // unpack warps, not this lane, fill the ring for those tiles.
+      // norms, B: key sign bits, C: value indices and norms), each refilled as soon as the unpack warps have read it.  This
+      // lane never touches the ring then: the unpack warps fill it, for hot tiles by issuing the TMA loads themselves.  (A
+      // role that passed over some uses of a ring stage without waiting for them could get two phases ahead of the stage's
+      // barrier, and a parity wait cannot tell "released" from "two uses behind".)
       uint32_t n_stg[3] = {0, 0, 0};
       auto stage_area = [&](int area) -> bool {       // wait until the area's previous tile has been read, then expect the new one
         if (n_stg[area] > 0 && !wait_or_abort(&bars[SL::b_stg_empty + area], (n_stg[area] - 1) & 1, abort_flag, p.status)) return false;
@@ -587,7 +581,6 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         ptx::bulk_load(sm + SL::stg_a_kr, p.t_kr + blk, 2 * D, &bars[SL::b_stg_full + 0]);
         if (!stage_area(1)) return false;
         ptx::bulk_load(sm + SL::stg_b, p.t_ks + blk * 16, 16 * D, &bars[SL::b_stg_full + 1]);
-        fill += 2 * kQChunks;
         return true;
       };
       auto stage_cold_v = [&](const Segment& sg, int tile) -> bool {
@@ -595,7 +588,6 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         if (!stage_area(2)) return false;
         ptx::bulk_load(sm + SL::stg_c, p.t_vp + blk * 48, 48 * D, &bars[SL::b_stg_full + 2]);
         ptx::bulk_load(sm + SL::stg_c_vn, p.t_vn + blk, 2 * D, &bars[SL::b_stg_full + 2]);
-        fill += kQChunks;
         return true;
       };
       while (ok && it.next(s)) {
@@ -610,11 +602,11 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         // K_lo, then (K_{j+1}, V_j) pairs, then V_last: the order the MMA warp consumes them
         for (int j = s.tile_lo; ok && j <= s.tile_hi; ++j) {
           if (j < s.tile_hi) {
-            if (TURBO && j < p.tiles_cold) ok = stage_cold_k(s, j);
+            if (TURBO) { if (j < p.tiles_cold) ok = stage_cold_k(s, j); }
             else for (int c = 0; ok && c < kQChunks; ++c) ok = load_chunk(&map_k, ref_k, s, j, c);
           }
           if (ok && j > s.tile_lo) {
-            if (TURBO && j - 1 < p.tiles_cold) ok = stage_cold_v(s, j - 1);
+            if (TURBO) { if (j - 1 < p.tiles_cold) ok = stage_cold_v(s, j - 1); }
             else for (int c = 0; ok && c < kQChunks; ++c) ok = load_chunk(&map_v, ref_v, s, j - 1, c);
           }
         }
@@ -801,16 +793,31 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         release(2);
         return true;
       };
+      // A tile of the uncompressed hot window (rotated domain, [B, Hkv, n_hot, D]): the same stages, in the same order,
+      // filled by TMA.  Every warp waits for the stage and arrives once (the stage's barrier counts four arrivals); the
+      // first warp's arrival carries the byte count and its lane 0 issues the load.
+      auto load_hot = [&](const CUtensorMap* map, int tile) -> bool {
+#pragma unroll 1
+        for (int c = 0; c < kQChunks; ++c) {
+          uint8_t* chunk;
+          if (!ring_slot(chunk)) return false;
+          if (lane == 0) {
+            void* bar = &bars[SL::b_kv_full + fill % kStages];
+            if (t == 0) {
+              ptx::mbar_arrive_expect_tx(bar, kChunkBytes);
+              ptx::tma_load_4d(chunk, map, c * 64, (tile - p.tiles_cold) * kBlockN, s.kvh, s.b, bar);
+            } else {
+              ptx::mbar_arrive(bar);
+            }
+          }
+          ++fill;
+        }
+        return true;
+      };
       while (ok && it.next(s)) {
         for (int j = s.tile_lo; ok && j <= s.tile_hi; ++j) {
-          if (j < s.tile_hi) {
-            if (j < p.tiles_cold) ok = unpack_k();
-            else fill += kQChunks;                      // a hot tile: the producer's TMA loads fill these stages
-          }
-          if (ok && j > s.tile_lo) {
-            if (j - 1 < p.tiles_cold) ok = unpack_v();
-            else fill += kQChunks;
-          }
+          if (j < s.tile_hi) ok = j < p.tiles_cold ? unpack_k() : load_hot(&map_k, j);
+          if (ok && j > s.tile_lo) ok = j - 1 < p.tiles_cold ? unpack_v() : load_hot(&map_v, j - 1);
         }
       }
     }
