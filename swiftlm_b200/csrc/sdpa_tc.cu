@@ -1417,7 +1417,7 @@ int32_t launch_typed(const SdpaArgs& a, const TurboKvArgs* turbo, cudaStream_t s
     // (measured: about ten key tiles' worth of time): B=60, N=16400 runs 12 % faster as stream-K, B=64, N=4112 4 % slower.
     const double idle_tiles = c >= 1 ? (double)tiles_per_unit / c * (1.0 - (double)p.units * c / n_sm) : 0.0;
     if (mode != 0 && c >= 1 && c <= kFusedMax && tiles_per_unit >= c && (long long)p.units * c * 5 >= (long long)n_sm * 4 &&
-        (mode > 0 || idle_tiles < 10.0)) {
+        (mode > 0 || idle_tiles < (TURBO ? 3.0 : 10.0))) {   // a compressed tile costs ~4x a dense one: idle SMs cost more than partials
       p.split = c;
       p.pair = (c == 2 && !TURBO) ? 1 : 0;   // compressed KV: the two ranges of a unit meet through the partials instead
       grid = (long long)p.units * c;
