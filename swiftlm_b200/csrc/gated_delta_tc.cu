@@ -307,7 +307,7 @@ gdn_tc_kernel(const __grid_constant__ TcMaps maps, const GdnArgs a, int* status)
 
   // previous item's finished state: tensor memory -> staging tile -> TMA store (compute warps)
   auto flush_state = [&](int dbuf, int b, int hv, uint32_t ek_parity) -> bool {
-    if (tid == 0) ptx::bulk_wait_read_all();          // the staging tile's previous store has been read
+    if (tid < 4) ptx::bulk_wait_read_all();           // the staging tile's previous store (this lane's box) has been read
     bool ok = ptx::mbar_wait(&bars[4], ek_parity);
     ptx::tc_fence_after();
     asm volatile("bar.sync 1, %0;" ::"n"(kComputeThreads) : "memory");
@@ -324,10 +324,9 @@ gdn_tc_kernel(const __grid_constant__ TcMaps maps, const GdnArgs a, int* status)
     ptx::fence_proxy_async();
     ptx::tc_fence_before();
     asm volatile("bar.sync 1, %0;" ::"n"(kComputeThreads) : "memory");
-    if (tid == 0) {
+    if (tid < 4) {   // one box per lane: a single lane takes a few hundred clocks per box
       const int row0 = (b * a.Hv + hv) * kD;
-#pragma unroll
-      for (int box = 0; box < 4; ++box) ptx::tma_store_2d(&maps.state_out, box * 32, row0, sm + kY + box * 16384);
+      ptx::tma_store_2d(&maps.state_out, tid * 32, row0, sm + kY + tid * 16384);
       ptx::bulk_commit_group();
     }
     return ok;
@@ -642,7 +641,7 @@ gdn_tc_kernel(const __grid_constant__ TcMaps maps, const GdnArgs a, int* status)
 
   PH_FLUSH();
   if (failed && lane == 0) atomicExch(status, kStatusGdnWait);
-  if (tid == 0) ptx::bulk_wait_all();   // shared memory must outlive the last store
+  if (tid < 4) ptx::bulk_wait_all();    // shared memory must outlive the last stores
   ptx::tc_fence_before();
   __syncthreads();
   if (aux) {

@@ -1287,16 +1287,23 @@ __global__ void __launch_bounds__(128) sdpa_tc_merge_kernel(const TcParams p, in
   // per CTA of the main kernel, so kMaxRanges covers every GPU with up to 320 SMs; more is reported, not dropped.
   constexpr int kMaxRanges = 320;
   __shared__ int s_slots[kMaxRanges];
-  __shared__ float s_f[kMaxRanges][32];    // per range and row: exp2(m - max over the ranges)
+  __shared__ int s_raw[2 * kMaxRanges];    // copy of the slot table (two slots per CTA of the main kernel)
+  __shared__ float s_f[kMaxRanges][32];    // per range and row: the range's maximum, then exp2(m - max over the ranges)
+  __shared__ float s_red[4][32];           // per warp and row: partial maximum, then partial denominator
   __shared__ int s_count;
   const int unit = blockIdx.x, rgrp = blockIdx.y, cgrp = blockIdx.z;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  // Every global load of the set-up below is issued together with its neighbours (a chain of dependent loads, one
+  // L2 round trip each, used to take most of this kernel's time): the slot table first, then the maxima, then the sums.
+  const int n_scan = n_slots < 2 * kMaxRanges ? n_slots : 2 * kMaxRanges;
+  for (int i = threadIdx.x; i < n_scan; i += 128) s_raw[i] = p.slot_unit[i];
+  __syncthreads();
   // slots of this unit, in slot order (a fixed summation order keeps results bit-reproducible)
   if (threadIdx.x < 32) {
     int count = 0;
-    for (int base = 0; base < n_slots; base += 32) {
+    for (int base = 0; base < n_scan; base += 32) {
       const int i = base + threadIdx.x;
-      const bool hit = i < n_slots && p.slot_unit[i] == unit;
+      const bool hit = i < n_scan && s_raw[i] == unit;
       const unsigned m = __ballot_sync(0xffffffffu, hit);
       const int pos = count + __popc(m & ((1u << threadIdx.x) - 1u));
       if (hit && pos < kMaxRanges) s_slots[pos] = i;
@@ -1304,7 +1311,7 @@ __global__ void __launch_bounds__(128) sdpa_tc_merge_kernel(const TcParams p, in
     }
     if (threadIdx.x == 0) {
       s_count = count;
-      if (count > kMaxRanges) atomicExch(p.status, kStatusMergeRanges);
+      if (count > kMaxRanges || n_slots > n_scan) atomicExch(p.status, kStatusMergeRanges);
     }
   }
   __syncthreads();
@@ -1315,30 +1322,75 @@ __global__ void __launch_bounds__(128) sdpa_tc_merge_kernel(const TcParams p, in
   const int b = unit / per_b, kvh = (unit / p.MT) % a.Hkv, mt = unit % p.MT;
   const int r = rgrp * 32 + lane;                        // row of the 128-row tile
   const int rr = mt * kRowsM + r;
-  // per-row weights once per CTA: warp w takes ranges w, w + 4, ...
+  // per-row weights once per CTA: warp w takes ranges w, w + 4, ...; partial results meet in shared memory and are
+  // combined in warp order by everybody (the same bits in every warp and in every CTA of the unit)
   {
-    float mmax = -INFINITY;
-    for (int i = 0; i < cnt; ++i) mmax = fmaxf(mmax, p.part_m[(long long)s_slots[i] * kRowsM + r]);
-    for (int i = warp; i < cnt; i += 4) {
-      const float m = p.part_m[(long long)s_slots[i] * kRowsM + r];
-      s_f[i][lane] = (m == -INFINITY) ? 0.f : exp2f(m - mmax);
+    float pm = -INFINITY;
+    int i = warp;
+    for (; i + 12 < cnt; i += 16) {
+      float m[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) m[u] = __ldcg(p.part_m + (long long)s_slots[i + 4 * u] * kRowsM + r);
+#pragma unroll
+      for (int u = 0; u < 4; ++u) { s_f[i + 4 * u][lane] = m[u]; pm = fmaxf(pm, m[u]); }
     }
+    for (; i < cnt; i += 4) {
+      const float m = __ldcg(p.part_m + (long long)s_slots[i] * kRowsM + r);
+      s_f[i][lane] = m;
+      pm = fmaxf(pm, m);
+    }
+    s_red[warp][lane] = pm;
+  }
+  __syncthreads();
+  const float mmax = fmaxf(fmaxf(s_red[0][lane], s_red[1][lane]), fmaxf(s_red[2][lane], s_red[3][lane]));
+  __syncthreads();
+  {
+    float pd = 0.f;
+    int i = warp;
+    for (; i + 12 < cnt; i += 16) {
+      float l[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) l[u] = __ldcg(p.part_l + (long long)s_slots[i + 4 * u] * kRowsM + r);
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const float m = s_f[i + 4 * u][lane];
+        const float f = (m == -INFINITY) ? 0.f : exp2f(m - mmax);
+        s_f[i + 4 * u][lane] = f;
+        pd += f * l[u];
+      }
+    }
+    for (; i < cnt; i += 4) {
+      const float m = s_f[i][lane];
+      const float f = (m == -INFINITY) ? 0.f : exp2f(m - mmax);
+      s_f[i][lane] = f;
+      pd += f * __ldcg(p.part_l + (long long)s_slots[i] * kRowsM + r);
+    }
+    s_red[warp][lane] = pd;
   }
   __syncthreads();
   if (rr >= p.R) return;
-  float den = 0.f;
-  for (int i = 0; i < cnt; ++i) den += s_f[i][lane] * p.part_l[(long long)s_slots[i] * kRowsM + r];   // same order in every warp
+  const float den = (s_red[0][lane] + s_red[1][lane]) + (s_red[2][lane] + s_red[3][lane]);
   const float inv = den == 0.f ? 1.f : 1.f / den;
   const int c4 = cgrp * 4 + warp;                        // float4 index inside the row
   float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
   const float* src = p.part_o + ((long long)c4 * kRowsM + r) * 4;
   int i = 0;
-  for (; i + 8 <= cnt; i += 8) {                          // eight independent loads in flight
-    float4 v[8];
+  for (; i + 16 <= cnt; i += 16) {                        // sixteen independent loads in flight
+    float4 v[16];
 #pragma unroll
-    for (int u = 0; u < 8; ++u) v[u] = __ldcg(reinterpret_cast<const float4*>(src + (long long)s_slots[i + u] * kRowsM * D));
+    for (int u = 0; u < 16; ++u) v[u] = __ldcg(reinterpret_cast<const float4*>(src + (long long)s_slots[i + u] * kRowsM * D));
 #pragma unroll
-    for (int u = 0; u < 8; ++u) {
+    for (int u = 0; u < 16; ++u) {
+      const float f = s_f[i + u][lane];
+      acc.x += f * v[u].x; acc.y += f * v[u].y; acc.z += f * v[u].z; acc.w += f * v[u].w;
+    }
+  }
+  for (; i + 4 <= cnt; i += 4) {
+    float4 v[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) v[u] = __ldcg(reinterpret_cast<const float4*>(src + (long long)s_slots[i + u] * kRowsM * D));
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
       const float f = s_f[i + u][lane];
       acc.x += f * v[u].x; acc.y += f * v[u].y; acc.z += f * v[u].z; acc.w += f * v[u].w;
     }
