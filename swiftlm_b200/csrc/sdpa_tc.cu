@@ -81,7 +81,8 @@ constexpr int kRowsM = 128;             // query rows per unit tile
 constexpr int kChunkBytes = 128 * 128;  // one TMA box: 128 rows x 64 16-bit elements
 constexpr int kThreads = 320;          // TMA warp, MMA warp, 8 softmax warps
 constexpr int kUnpackThreads = 128;    // compressed KV only: 4 more warps expand packed keys and values into the ring
-template <bool TURBO> struct ThreadsOf { static constexpr int value = TURBO ? kThreads + kUnpackThreads : kThreads; };
+constexpr int kPvThreads = 32;         // dense KV only: one more warp whose lane 0 issues the P V products
+template <bool TURBO> struct ThreadsOf { static constexpr int value = kThreads + (TURBO ? kUnpackThreads : kPvThreads); };
 constexpr float kRescaleThreshold = 8.f;   // in log2 units
 constexpr int kFusedMax = 4;               // a unit cut into at most this many ranges is merged by its last finisher
 
@@ -123,6 +124,11 @@ struct Smem {
   // even: V chunks are consumed in pairs.  Compressed KV: the second query tile takes the room of most of the ring;
   // four stages are enough there because chunks are produced by the CTA itself, a few hundred clocks ahead of their use
   static constexpr int kStages = TURBO ? 4 : ((D == 256) ? 10 : 12);
+  // dense KV: the ring is two rings, K chunks (consumed by the Q K^T issuer as they land) in the first kStagesK stages,
+  // V chunks (consumed by the P V issuer once the probabilities exist) in the rest; each ring has one producer cursor and
+  // one consumer, so no role ever passes over a use of a stage
+  static constexpr int kStagesK = TURBO ? kStages : 4;
+  static constexpr int kStagesV = kStages - kStagesK;
   static constexpr uint32_t q = 0;
   static constexpr uint32_t q2 = kQChunks * kChunkBytes;                     // TURBO: Q2 = Rq^T q
   static constexpr uint32_t ring = (TURBO ? 2 : 1) * kQChunks * kChunkBytes;
@@ -145,7 +151,8 @@ struct Smem {
   static constexpr int b_peer_data = 9 + 2 * kStages;    // the partner's columns have landed here (256 arrivals)
   static constexpr int b_stg_full = 10 + 2 * kStages;    // 3 (TURBO): a landing area holds its tile
   static constexpr int b_stg_empty = 13 + 2 * kStages;   // 3 (TURBO): the unpack warps have read it (4 arrivals)
-  static constexpr int n_bars = 16 + 2 * kStages;
+  static constexpr int b_s_free = 16 + 2 * kStages;      // 2 (dense): the product that read P from this score buffer has retired
+  static constexpr int n_bars = 18 + 2 * kStages;
   static constexpr uint32_t misc = bars + 8 * n_bars;   // tmem base, abort flag, range info, group counter, merge decision
   static constexpr uint32_t xseq = misc + 64;            // exchange sequence numbers [2][2][4]
   static constexpr uint32_t xch = xseq + 64;             // exchange values [2 slots][2 halves][128 rows]
@@ -522,99 +529,204 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
   if (warp == 0) {
     // =================================== TMA producer ===================================
     if (lane == 0 && begin < end) {
-      SegmentIter it(p, begin, end, unit0, tile0);
-      Segment s;
-      uint32_t fill = 0;        // ring slots filled so far
-      uint32_t seg_idx = 0;
-      bool ok = true;
-      // Paged KV: the page of a tile is looked up once per stream (K runs one tile ahead of V), not once per chunk.
-      struct PageRef { int b, index, page; };
-      PageRef ref_k{-1, -1, 0}, ref_v{-1, -1, 0};
-      auto load_chunk = [&](const CUtensorMap* map, PageRef& ref, const Segment& sg, int tile, int c) -> bool {
-        const uint32_t stage = fill % kStages;
-        {
-          TR_T0();
-          if (fill >= (uint32_t)kStages && !wait_or_abort(&bars[SL::b_kv_empty + stage], ((fill / kStages) - 1) & 1, abort_flag, p.status))
-            return false;
-          TR_ACC(16);
-        }
-        ptx::mbar_arrive_expect_tx(&bars[SL::b_kv_full + stage], kChunkBytes);
-        const int n0 = tile * kBlockN;
-        if (a.page_table) {
-          if (c == 0) {
-            const int index = n0 / a.page_tokens;
-            if (index != ref.index || sg.b != ref.b) {
-              // index < max_pages because n0 < N <= max_pages * page_tokens (host check, lengths clamped to N).
-              // A page id outside the pool reads as zeros (the tensor map ends at num_pages) and is reported.
-              ref = PageRef{sg.b, index, a.page_table[(long long)sg.b * a.max_pages + index]};
-              if ((unsigned)ref.page >= (unsigned)a.num_pages) { ref.page = a.num_pages; atomicExch(p.status, kStatusKvRange); }
-            }
-          }
-          ptx::tma_load_4d(sm + SL::ring + stage * kChunkBytes, map, c * 64, n0 - ref.index * a.page_tokens, sg.kvh, ref.page,
-                           &bars[SL::b_kv_full + stage]);
-        } else {
-          ptx::tma_load_4d(sm + SL::ring + stage * kChunkBytes, map, c * 64, n0, sg.kvh, sg.b, &bars[SL::b_kv_full + stage]);
-        }
-        ++fill;
-        return true;
-      };
-      // Compressed KV: the packed arrays of a 128-key tile of the cold history land in three areas (A: key indices and
-      // norms, B: key sign bits, C: value indices and norms), each refilled as soon as the unpack warps have read it.  This
-      // lane never touches the ring then: the unpack warps fill it, for hot tiles by issuing the TMA loads themselves.  (A
-      // role that passed over some uses of a ring stage without waiting for them could get two phases ahead of the stage's
-      // barrier, and a parity wait cannot tell "released" from "two uses behind".)
-      uint32_t n_stg[3] = {0, 0, 0};
-      auto stage_area = [&](int area) -> bool {       // wait until the area's previous tile has been read, then expect the new one
-        if (n_stg[area] > 0 && !wait_or_abort(&bars[SL::b_stg_empty + area], (n_stg[area] - 1) & 1, abort_flag, p.status)) return false;
-        ptx::mbar_arrive_expect_tx(&bars[SL::b_stg_full + area], (area == 0 ? 52u : area == 1 ? 16u : 50u) * D);
-        ++n_stg[area];
-        return true;
-      };
-      auto cold_blocks = [&](const Segment& sg, int tile) -> long long {   // first 128-dimension block of the tile's keys
-        return (((long long)sg.b * a.Hkv + sg.kvh) * p.n_cold + (long long)tile * kBlockN) * (D / 128);
-      };
-      auto stage_cold_k = [&](const Segment& sg, int tile) -> bool {
-        const long long blk = cold_blocks(sg, tile);
-        if (!stage_area(0)) return false;
-        ptx::bulk_load(sm + SL::stg_a, p.t_kp + blk * 48, 48 * D, &bars[SL::b_stg_full + 0]);
-        ptx::bulk_load(sm + SL::stg_a_kn, p.t_kn + blk, 2 * D, &bars[SL::b_stg_full + 0]);
-        ptx::bulk_load(sm + SL::stg_a_kr, p.t_kr + blk, 2 * D, &bars[SL::b_stg_full + 0]);
-        if (!stage_area(1)) return false;
-        ptx::bulk_load(sm + SL::stg_b, p.t_ks + blk * 16, 16 * D, &bars[SL::b_stg_full + 1]);
-        return true;
-      };
-      auto stage_cold_v = [&](const Segment& sg, int tile) -> bool {
-        const long long blk = cold_blocks(sg, tile);
-        if (!stage_area(2)) return false;
-        ptx::bulk_load(sm + SL::stg_c, p.t_vp + blk * 48, 48 * D, &bars[SL::b_stg_full + 2]);
-        ptx::bulk_load(sm + SL::stg_c_vn, p.t_vn + blk, 2 * D, &bars[SL::b_stg_full + 2]);
-        return true;
-      };
-      while (ok && it.next(s)) {
-        // Q tile of this unit: wait until the previous segment's S = Q K^T products are done with it
-        if (seg_idx > 0 && !wait_or_abort(&bars[SL::b_q_empty], (seg_idx - 1) & 1, abort_flag, p.status)) break;
-        ptx::mbar_arrive_expect_tx(&bars[SL::b_q_full], (TURBO ? 2 : 1) * kQChunks * kChunkBytes);
-        for (int c = 0; c < kQChunks; ++c)
-          ptx::tma_load_3d(sm + SL::q + c * kChunkBytes, &map_q, c * 64, s.mt * kRowsM, s.b * a.Hkv + s.kvh, &bars[SL::b_q_full]);
-        if (TURBO)
+      if constexpr (TURBO) {
+        // Compressed KV: the packed arrays of a 128-key tile of the cold history land in three areas (A: key indices
+        // and norms, B: key sign bits, C: value indices and norms), each refilled as soon as the unpack warps have read
+        // it.  This lane never touches the ring: the unpack warps fill it, for hot tiles by issuing the TMA loads
+        // themselves.  (A role that passed over some uses of a ring stage without waiting for them could get two phases
+        // ahead of the stage's barrier, and a parity wait cannot tell "released" from "two uses behind".)
+        SegmentIter it(p, begin, end, unit0, tile0);
+        Segment s;
+        uint32_t seg_idx = 0;
+        bool ok = true;
+        uint32_t n_stg[3] = {0, 0, 0};
+        auto stage_area = [&](int area) -> bool {       // wait until the area's previous tile has been read, then expect the new one
+          if (n_stg[area] > 0 && !wait_or_abort(&bars[SL::b_stg_empty + area], (n_stg[area] - 1) & 1, abort_flag, p.status)) return false;
+          ptx::mbar_arrive_expect_tx(&bars[SL::b_stg_full + area], (area == 0 ? 52u : area == 1 ? 16u : 50u) * D);
+          ++n_stg[area];
+          return true;
+        };
+        auto cold_blocks = [&](const Segment& sg, int tile) -> long long {   // first 128-dimension block of the tile's keys
+          return (((long long)sg.b * a.Hkv + sg.kvh) * p.n_cold + (long long)tile * kBlockN) * (D / 128);
+        };
+        auto stage_cold_k = [&](const Segment& sg, int tile) -> bool {
+          const long long blk = cold_blocks(sg, tile);
+          if (!stage_area(0)) return false;
+          ptx::bulk_load(sm + SL::stg_a, p.t_kp + blk * 48, 48 * D, &bars[SL::b_stg_full + 0]);
+          ptx::bulk_load(sm + SL::stg_a_kn, p.t_kn + blk, 2 * D, &bars[SL::b_stg_full + 0]);
+          ptx::bulk_load(sm + SL::stg_a_kr, p.t_kr + blk, 2 * D, &bars[SL::b_stg_full + 0]);
+          if (!stage_area(1)) return false;
+          ptx::bulk_load(sm + SL::stg_b, p.t_ks + blk * 16, 16 * D, &bars[SL::b_stg_full + 1]);
+          return true;
+        };
+        auto stage_cold_v = [&](const Segment& sg, int tile) -> bool {
+          const long long blk = cold_blocks(sg, tile);
+          if (!stage_area(2)) return false;
+          ptx::bulk_load(sm + SL::stg_c, p.t_vp + blk * 48, 48 * D, &bars[SL::b_stg_full + 2]);
+          ptx::bulk_load(sm + SL::stg_c_vn, p.t_vn + blk, 2 * D, &bars[SL::b_stg_full + 2]);
+          return true;
+        };
+        while (ok && it.next(s)) {
+          // Q tiles of this unit: wait until the previous segment's S = Q K^T products are done with them
+          if (seg_idx > 0 && !wait_or_abort(&bars[SL::b_q_empty], (seg_idx - 1) & 1, abort_flag, p.status)) break;
+          ptx::mbar_arrive_expect_tx(&bars[SL::b_q_full], 2 * kQChunks * kChunkBytes);
+          for (int c = 0; c < kQChunks; ++c)
+            ptx::tma_load_3d(sm + SL::q + c * kChunkBytes, &map_q, c * 64, s.mt * kRowsM, s.b * a.Hkv + s.kvh, &bars[SL::b_q_full]);
           for (int c = 0; c < kQChunks; ++c)
             ptx::tma_load_3d(sm + SL::q2 + c * kChunkBytes, &map_q2, c * 64, s.mt * kRowsM, s.b * a.Hkv + s.kvh, &bars[SL::b_q_full]);
-        // K_lo, then (K_{j+1}, V_j) pairs, then V_last: the order the MMA warp consumes them
-        for (int j = s.tile_lo; ok && j <= s.tile_hi; ++j) {
-          if (j < s.tile_hi) {
-            if (TURBO) { if (j < p.tiles_cold) ok = stage_cold_k(s, j); }
-            else for (int c = 0; ok && c < kQChunks; ++c) ok = load_chunk(&map_k, ref_k, s, j, c);
+          // K_lo, then (K_{j+1}, V_j) pairs, then V_last: the order the unpack warps and the MMA warp follow
+          for (int j = s.tile_lo; ok && j <= s.tile_hi; ++j) {
+            if (j < s.tile_hi && j < p.tiles_cold) ok = stage_cold_k(s, j);
+            if (ok && j > s.tile_lo && j - 1 < p.tiles_cold) ok = stage_cold_v(s, j - 1);
           }
-          if (ok && j > s.tile_lo) {
-            if (TURBO) { if (j - 1 < p.tiles_cold) ok = stage_cold_v(s, j - 1); }
-            else for (int c = 0; ok && c < kQChunks; ++c) ok = load_chunk(&map_v, ref_v, s, j - 1, c);
+          ++seg_idx;
+        }
+      } else {
+        // Dense KV: two cursors over the CTA's tiles, one feeding K chunks (and each unit's Q tile) to the Q K^T issuer
+        // through the K ring, one feeding V chunks to the P V issuer through the V ring.  Neither blocks the other: a
+        // cursor that finds its ring full (or the Q tile still in use) yields, and the lane sleeps only when both are stuck.
+        constexpr int kSK = SL::kStagesK, kSV = SL::kStagesV;
+        struct PageRef { int b, index, page; };
+        struct Cursor {
+          SegmentIter it;
+          Segment s;
+          bool have, done;
+          int j, c;
+          uint32_t fill, seg;
+          PageRef ref;
+        };
+        Cursor ck{SegmentIter(p, begin, end, unit0, tile0), Segment{}, false, false, 0, 0, 0u, 0u, PageRef{-1, -1, 0}};
+        Cursor cv{SegmentIter(p, begin, end, unit0, tile0), Segment{}, false, false, 0, 0, 0u, 0u, PageRef{-1, -1, 0}};
+        bool q_pending = false;
+        // one 16 KiB box of tile `tile`, head-dimension chunk c, into ring stage `stage`; paged KV: the page of a tile is
+        // looked up once per cursor, not once per chunk
+        auto issue_chunk = [&](const CUtensorMap* map, Cursor& cur, int stage) {
+          ptx::mbar_arrive_expect_tx(&bars[SL::b_kv_full + stage], kChunkBytes);
+          const int n0 = cur.j * kBlockN;
+          if (a.page_table) {
+            if (cur.c == 0) {
+              const int index = n0 / a.page_tokens;
+              if (index != cur.ref.index || cur.s.b != cur.ref.b) {
+                // index < max_pages because n0 < N <= max_pages * page_tokens (host check, lengths clamped to N).
+                // A page id outside the pool reads as zeros (the tensor map ends at num_pages) and is reported.
+                cur.ref = PageRef{cur.s.b, index, a.page_table[(long long)cur.s.b * a.max_pages + index]};
+                if ((unsigned)cur.ref.page >= (unsigned)a.num_pages) { cur.ref.page = a.num_pages; atomicExch(p.status, kStatusKvRange); }
+              }
+            }
+            ptx::tma_load_4d(sm + SL::ring + stage * kChunkBytes, map, cur.c * 64, n0 - cur.ref.index * a.page_tokens, cur.s.kvh,
+                             cur.ref.page, &bars[SL::b_kv_full + stage]);
+          } else {
+            ptx::tma_load_4d(sm + SL::ring + stage * kChunkBytes, map, cur.c * 64, n0, cur.s.kvh, cur.s.b, &bars[SL::b_kv_full + stage]);
+          }
+        };
+        // advances a cursor by one chunk if its ring has room: 1 progressed, 0 has to wait, -1 finished
+        auto step = [&](Cursor& cur, bool is_k) -> int {
+          if (cur.done) return -1;
+          if (!cur.have) {
+            if (!cur.it.next(cur.s)) { cur.done = true; return -1; }
+            cur.have = true;
+            cur.j = cur.s.tile_lo;
+            cur.c = 0;
+            if (is_k) q_pending = true;
+          }
+          if (is_k && q_pending) {
+            // Q tile of this unit: the previous segment's S = Q K^T products must be done with it
+            if (cur.seg > 0 && !ptx::mbar_try_wait(&bars[SL::b_q_empty], (cur.seg - 1) & 1)) return 0;
+            ptx::mbar_arrive_expect_tx(&bars[SL::b_q_full], kQChunks * kChunkBytes);
+            for (int c = 0; c < kQChunks; ++c)
+              ptx::tma_load_3d(sm + SL::q + c * kChunkBytes, &map_q, c * 64, cur.s.mt * kRowsM, cur.s.b * a.Hkv + cur.s.kvh, &bars[SL::b_q_full]);
+            q_pending = false;
+            return 1;
+          }
+          const int ring_n = is_k ? kSK : kSV, ring_0 = is_k ? 0 : kSK;
+          const int stage = ring_0 + (int)(cur.fill % (uint32_t)ring_n);
+          if (cur.fill >= (uint32_t)ring_n && !ptx::mbar_try_wait(&bars[SL::b_kv_empty + stage], ((cur.fill / (uint32_t)ring_n) - 1) & 1)) return 0;
+          issue_chunk(is_k ? &map_k : &map_v, cur, stage);
+          ++cur.fill;
+          if (++cur.c == kQChunks) {
+            cur.c = 0;
+            if (++cur.j == cur.s.tile_hi) { cur.have = false; ++cur.seg; }
+          }
+          return 1;
+        };
+        uint32_t idle = 0;
+        while (!(ck.done && cv.done)) {
+          const int rk = step(ck, true), rv = step(cv, false);
+          if (rk > 0 || rv > 0) { idle = 0; continue; }
+          if (ck.done && cv.done) break;
+          if ((++idle & 63u) == 63u) {
+            if (*abort_flag) break;
+            __nanosleep(40);
+          }
+          if (idle >= ptx::kWaitPolls) {   // neither ring has released a stage for the whole poll budget
+            *abort_flag = 1;
+            atomicExch(p.status, kStatusMbarWait);
+            break;
           }
         }
-        ++seg_idx;
       }
     }
   } else if (warp == 1) {
     // ==================================== MMA issuer ====================================
+    // Dense KV: this lane issues only S = Q K^T; a second lane (warp 10) issues O += P V.  One thread issuing both spent
+    // about 6 K clocks per key tile (32 products, a dozen barrier waits and commits) where the products themselves take 2 K:
+    // it, not HBM or the softmax, set the tile period.  The two issuers meet through barriers only: a score buffer may be
+    // overwritten once the product that read P from it has retired (s_free), and P V starts when P is there (p_full).
+    if constexpr (!TURBO) {
+      if (lane == 0 && begin < end) {
+        constexpr int kSK = SL::kStagesK;
+        SegmentIter it(p, begin, end, unit0, tile0);
+        Segment s;
+        uint32_t drain = 0, seg_idx = 0, tile_ctr = 0;
+        bool ok = true;
+        const uint32_t q_addr = ptx::smem_u32(sm + SL::q);
+        while (ok && it.next(s)) {
+          if (!wait_or_abort(&bars[SL::b_q_full], seg_idx & 1, abort_flag, p.status)) break;
+          ptx::tc_fence_after();
+          const int ntiles = s.tile_hi - s.tile_lo;
+          for (int jj = 0; ok && jj < ntiles; ++jj) {
+            const uint32_t t = tile_ctr + jj, buf = t & 1;
+            const uint32_t d_tmem = tmem_base + kColS + buf * kBlockN;
+            if (t >= 2) {   // P of tile t - 2 lived in this buffer: its product must have retired
+              TR_T0();
+              ok = wait_or_abort(&bars[SL::b_s_free + buf], ((t >> 1) - 1) & 1, abort_flag, p.status);
+              TR_ACC(19);
+              if (!ok) break;
+            }
+            for (int c = 0; ok && c < kQChunks; ++c) {
+              const uint32_t stage = drain % kSK;
+              {
+                TR_T0();
+                ok = wait_or_abort(&bars[SL::b_kv_full + stage], (drain / kSK) & 1, abort_flag, p.status);
+                TR_ACC(17);
+                if (drain == 0) TR_STAMP(2);
+              }
+              if (!ok) break;
+              ptx::tc_fence_after();
+              // descriptors differ only in the start-address field: +2 (32 bytes) per 16-element step
+              const uint64_t da0 = make_desc(q_addr + c * kChunkBytes, 16, 1024);
+              const uint64_t db0 = make_desc(ptx::smem_u32(sm + SL::ring + stage * kChunkBytes), 16, 1024);
+              {
+                TR_T0();
+                if (c == 0) ptx::umma_ss_first(d_tmem, da0, db0, kIdescQK);
+                else ptx::umma_ss_acc(d_tmem, da0, db0, kIdescQK);
+                ptx::umma_ss_acc(d_tmem, da0 + 2, db0 + 2, kIdescQK);
+                ptx::umma_ss_acc(d_tmem, da0 + 4, db0 + 4, kIdescQK);
+                ptx::umma_ss_acc(d_tmem, da0 + 6, db0 + 6, kIdescQK);
+                ptx::umma_commit(&bars[SL::b_kv_empty + stage]);   // K chunk free once these products retire
+                TR_ACC(22);
+              }
+              ++drain;
+            }
+            if (!ok) break;
+            ptx::umma_commit(&bars[SL::b_s_full + buf]);
+            if (jj == ntiles - 1) ptx::umma_commit(&bars[SL::b_q_empty]);   // last use of this Q tile
+          }
+          tile_ctr += ntiles;
+          ++seg_idx;
+        }
+      }
+    } else
     if (lane == 0 && begin < end) {
       SegmentIter it(p, begin, end, unit0, tile0);
       Segment s;
@@ -712,6 +824,69 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
             if (!ok) break;
             ptx::umma_commit(&bars[SL::b_pv_done]);
           }
+        }
+        tile_ctr += ntiles;
+        ++seg_idx;
+      }
+    }
+  } else if (!TURBO && warp == kThreads / 32) {
+    // ================================== P V issuer (dense KV) ==================================
+    if constexpr (!TURBO) if (lane == 0 && begin < end) {
+      constexpr int kSK = SL::kStagesK, kSV = SL::kStagesV;
+      SegmentIter it(p, begin, end, unit0, tile0);
+      Segment s;
+      uint32_t drain = 0, seg_idx = 0, tile_ctr = 0;
+      bool ok = true;
+      while (ok && it.next(s)) {
+        const int ntiles = s.tile_hi - s.tile_lo;
+        for (int jj = 0; ok && jj < ntiles; ++jj) {
+          // ---- O += P_j V_j ----
+          const uint32_t t = tile_ctr + jj, buf = t & 1;
+          if (jj == 0 && seg_idx > 0) {
+            // first product of a segment overwrites O: the previous segment's epilogue must have read it
+            ok = wait_or_abort(&bars[SL::b_o_free], (seg_idx - 1) & 1, abort_flag, p.status);
+            if (!ok) break;
+          }
+          {
+            TR_T0();
+            ok = wait_or_abort(&bars[SL::b_p_full + buf], (t >> 1) & 1, abort_flag, p.status);
+            TR_ACC(19);
+          }
+          if (!ok) break;
+          ptx::tc_fence_after();
+          const uint32_t p_tmem = tmem_base + kColS + buf * kBlockN;   // P (16-bit pairs) aliases S
+          // Two 64-column V chunks per instruction (N = 128).  The pair sits in consecutive stages of the V ring (chunks come
+          // in groups of kQChunks and the ring has an even number of stages, so a pair never straddles the wrap); the
+          // descriptor's leading-dimension offset is the 16 KiB from one chunk to the next.
+          for (int cp = 0; ok && cp < kQChunks / 2; ++cp) {
+            const uint32_t stage = kSK + drain % kSV;
+            {
+              TR_T0();
+              ok = wait_or_abort(&bars[SL::b_kv_full + stage], (drain / kSV) & 1, abort_flag, p.status) &&
+                   wait_or_abort(&bars[SL::b_kv_full + stage + 1], (drain / kSV) & 1, abort_flag, p.status);
+              TR_ACC(18);
+            }
+            if (!ok) break;
+            ptx::tc_fence_after();
+            // 16 keys per instruction: +128 (2048 bytes) in the start-address field, +8 P columns
+            const uint64_t db0 = make_desc(ptx::smem_u32(sm + SL::ring + stage * kChunkBytes), kChunkBytes, 1024);
+            const uint32_t o_tmem = tmem_base + kColO + cp * 128;
+            {
+              TR_T0();
+              if (jj > 0) ptx::umma_ts_acc(o_tmem, p_tmem, db0, kIdescPV);
+              else ptx::umma_ts_first(o_tmem, p_tmem, db0, kIdescPV);
+#pragma unroll
+              for (int kk = 1; kk < kBlockN / 16; ++kk)
+                ptx::umma_ts_acc(o_tmem, p_tmem + kk * 8, db0 + (uint64_t)kk * 128, kIdescPV);
+              ptx::umma_commit(&bars[SL::b_kv_empty + stage]);
+              ptx::umma_commit(&bars[SL::b_kv_empty + stage + 1]);
+              TR_ACC(23);
+            }
+            drain += 2;
+          }
+          if (!ok) break;
+          ptx::umma_commit(&bars[SL::b_pv_done]);
+          ptx::umma_commit(&bars[SL::b_s_free + buf]);
         }
         tile_ctr += ntiles;
         ++seg_idx;
@@ -1267,7 +1442,8 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
   // wait above is bounded, so both always get here.
   if (p.pair) cluster_sync_all();
   if (threadIdx.x == 0) TR_FLUSH(16, 16);
-  if (threadIdx.x == 32) { TR_FLUSH(17, 19); TR_FLUSH(22, 23); }
+  if (threadIdx.x == 32) { TR_FLUSH(17, 17); TR_FLUSH(22, 22); if (TURBO) { TR_FLUSH(18, 19); TR_FLUSH(23, 23); } }
+  if (!TURBO && threadIdx.x == kThreads) { TR_FLUSH(18, 19); TR_FLUSH(23, 23); }
   if (threadIdx.x == 64) TR_FLUSH(20, 21);
   ptx::tc_fence_before();
   __syncthreads();
