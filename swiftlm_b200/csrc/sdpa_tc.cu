@@ -81,8 +81,8 @@ constexpr int kRowsM = 128;             // query rows per unit tile
 constexpr int kChunkBytes = 128 * 128;  // one TMA box: 128 rows x 64 16-bit elements
 constexpr int kThreads = 320;          // TMA warp, MMA warp, 8 softmax warps
 constexpr int kUnpackThreads = 128;    // compressed KV only: 4 more warps expand packed keys and values into the ring
-constexpr int kPvThreads = 32;         // dense KV only: one more warp whose lane 0 issues the P V products
-template <bool TURBO> struct ThreadsOf { static constexpr int value = kThreads + (TURBO ? kUnpackThreads : kPvThreads); };
+constexpr int kPvThreads = 32;         // one more warp whose lane 0 issues the P V products
+template <bool TURBO> struct ThreadsOf { static constexpr int value = kThreads + kPvThreads + (TURBO ? kUnpackThreads : 0); };
 constexpr float kRescaleThreshold = 8.f;   // in log2 units
 constexpr int kFusedMax = 4;               // a unit cut into at most this many ranges is merged by its last finisher
 
@@ -124,10 +124,10 @@ struct Smem {
   // even: V chunks are consumed in pairs.  Compressed KV: the second query tile takes the room of most of the ring;
   // four stages are enough there because chunks are produced by the CTA itself, a few hundred clocks ahead of their use
   static constexpr int kStages = TURBO ? 4 : ((D == 256) ? 10 : 12);
-  // dense KV: the ring is two rings, K chunks (consumed by the Q K^T issuer as they land) in the first kStagesK stages,
-  // V chunks (consumed by the P V issuer once the probabilities exist) in the rest; each ring has one producer cursor and
-  // one consumer, so no role ever passes over a use of a stage
-  static constexpr int kStagesK = TURBO ? kStages : 4;
+  // The ring is two rings: K chunks (consumed by the Q K^T issuer as they arrive) in the first kStagesK stages, V chunks
+  // (consumed by the P V issuer once the probabilities exist) in the rest; each ring has one producer and one consumer,
+  // so no role ever passes over a use of a stage
+  static constexpr int kStagesK = TURBO ? 2 : 4;
   static constexpr int kStagesV = kStages - kStagesK;
   static constexpr uint32_t q = 0;
   static constexpr uint32_t q2 = kQChunks * kChunkBytes;                     // TURBO: Q2 = Rq^T q
@@ -151,7 +151,7 @@ struct Smem {
   static constexpr int b_peer_data = 9 + 2 * kStages;    // the partner's columns have landed here (256 arrivals)
   static constexpr int b_stg_full = 10 + 2 * kStages;    // 3 (TURBO): a landing area holds its tile
   static constexpr int b_stg_empty = 13 + 2 * kStages;   // 3 (TURBO): the unpack warps have read it (4 arrivals)
-  static constexpr int b_s_free = 16 + 2 * kStages;      // 2 (dense): the product that read P from this score buffer has retired
+  static constexpr int b_s_free = 16 + 2 * kStages;      // 2: the product that read P from this score buffer has retired
   static constexpr int n_bars = 18 + 2 * kStages;
   static constexpr uint32_t misc = bars + 8 * n_bars;   // tmem base, abort flag, range info, group counter, merge decision
   static constexpr uint32_t xseq = misc + 64;            // exchange sequence numbers [2][2][4]
@@ -574,10 +574,10 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
             ptx::tma_load_3d(sm + SL::q + c * kChunkBytes, &map_q, c * 64, s.mt * kRowsM, s.b * a.Hkv + s.kvh, &bars[SL::b_q_full]);
           for (int c = 0; c < kQChunks; ++c)
             ptx::tma_load_3d(sm + SL::q2 + c * kChunkBytes, &map_q2, c * 64, s.mt * kRowsM, s.b * a.Hkv + s.kvh, &bars[SL::b_q_full]);
-          // K_lo, then (K_{j+1}, V_j) pairs, then V_last: the order the unpack warps and the MMA warp follow
+          // per step the unpack warps want the values of tile j - 1 first, then the keys of tile j
           for (int j = s.tile_lo; ok && j <= s.tile_hi; ++j) {
-            if (j < s.tile_hi && j < p.tiles_cold) ok = stage_cold_k(s, j);
-            if (ok && j > s.tile_lo && j - 1 < p.tiles_cold) ok = stage_cold_v(s, j - 1);
+            if (j > s.tile_lo && j - 1 < p.tiles_cold) ok = stage_cold_v(s, j - 1);
+            if (ok && j < s.tile_hi && j < p.tiles_cold) ok = stage_cold_k(s, j);
           }
           ++seg_idx;
         }
@@ -667,171 +667,69 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       }
     }
   } else if (warp == 1) {
-    // ==================================== MMA issuer ====================================
-    // Dense KV: this lane issues only S = Q K^T; a second lane (warp 10) issues O += P V.  One thread issuing both spent
-    // about 6 K clocks per key tile (32 products, a dozen barrier waits and commits) where the products themselves take 2 K:
+    // ================================ Q K^T issuer ================================
+    // This lane issues only S = Q K^T; a second lane (warp 10) issues O += P V.  One thread issuing both spent about
+    // 6 K clocks per key tile (32 products, a dozen barrier waits and commits) where the products themselves take 2 K:
     // it, not HBM or the softmax, set the tile period.  The two issuers meet through barriers only: a score buffer may be
     // overwritten once the product that read P from it has retired (s_free), and P V starts when P is there (p_full).
-    if constexpr (!TURBO) {
-      if (lane == 0 && begin < end) {
-        constexpr int kSK = SL::kStagesK;
-        SegmentIter it(p, begin, end, unit0, tile0);
-        Segment s;
-        uint32_t drain = 0, seg_idx = 0, tile_ctr = 0;
-        bool ok = true;
-        const uint32_t q_addr = ptx::smem_u32(sm + SL::q);
-        while (ok && it.next(s)) {
-          if (!wait_or_abort(&bars[SL::b_q_full], seg_idx & 1, abort_flag, p.status)) break;
-          ptx::tc_fence_after();
-          const int ntiles = s.tile_hi - s.tile_lo;
-          for (int jj = 0; ok && jj < ntiles; ++jj) {
-            const uint32_t t = tile_ctr + jj, buf = t & 1;
-            const uint32_t d_tmem = tmem_base + kColS + buf * kBlockN;
-            if (t >= 2) {   // P of tile t - 2 lived in this buffer: its product must have retired
-              TR_T0();
-              ok = wait_or_abort(&bars[SL::b_s_free + buf], ((t >> 1) - 1) & 1, abort_flag, p.status);
-              TR_ACC(19);
-              if (!ok) break;
-            }
-            for (int c = 0; ok && c < kQChunks; ++c) {
-              const uint32_t stage = drain % kSK;
-              {
-                TR_T0();
-                ok = wait_or_abort(&bars[SL::b_kv_full + stage], (drain / kSK) & 1, abort_flag, p.status);
-                TR_ACC(17);
-                if (drain == 0) TR_STAMP(2);
-              }
-              if (!ok) break;
-              ptx::tc_fence_after();
-              // descriptors differ only in the start-address field: +2 (32 bytes) per 16-element step
-              const uint64_t da0 = make_desc(q_addr + c * kChunkBytes, 16, 1024);
-              const uint64_t db0 = make_desc(ptx::smem_u32(sm + SL::ring + stage * kChunkBytes), 16, 1024);
-              {
-                TR_T0();
-                if (c == 0) ptx::umma_ss_first(d_tmem, da0, db0, kIdescQK);
-                else ptx::umma_ss_acc(d_tmem, da0, db0, kIdescQK);
-                ptx::umma_ss_acc(d_tmem, da0 + 2, db0 + 2, kIdescQK);
-                ptx::umma_ss_acc(d_tmem, da0 + 4, db0 + 4, kIdescQK);
-                ptx::umma_ss_acc(d_tmem, da0 + 6, db0 + 6, kIdescQK);
-                ptx::umma_commit(&bars[SL::b_kv_empty + stage]);   // K chunk free once these products retire
-                TR_ACC(22);
-              }
-              ++drain;
-            }
-            if (!ok) break;
-            ptx::umma_commit(&bars[SL::b_s_full + buf]);
-            if (jj == ntiles - 1) ptx::umma_commit(&bars[SL::b_q_empty]);   // last use of this Q tile
-          }
-          tile_ctr += ntiles;
-          ++seg_idx;
-        }
-      }
-    } else
     if (lane == 0 && begin < end) {
+      constexpr int kSK = SL::kStagesK;
       SegmentIter it(p, begin, end, unit0, tile0);
       Segment s;
-      uint32_t drain = 0;       // ring slots consumed so far
-      uint32_t seg_idx = 0;
-      uint32_t tile_ctr = 0;    // tiles issued so far (S buffer and barrier phases)
+      uint32_t drain = 0, seg_idx = 0, tile_ctr = 0;
       bool ok = true;
       const uint32_t q_addr = ptx::smem_u32(sm + SL::q);
       while (ok && it.next(s)) {
         if (!wait_or_abort(&bars[SL::b_q_full], seg_idx & 1, abort_flag, p.status)) break;
         ptx::tc_fence_after();
         const int ntiles = s.tile_hi - s.tile_lo;
-        for (int jj = 0; ok && jj <= ntiles; ++jj) {
-          if (jj < ntiles) {
-            // ---- S[buf] = Q K_j^T ----
-            const uint32_t t = tile_ctr + jj, buf = t & 1;
-            const uint32_t d_tmem = tmem_base + kColS + buf * kBlockN;
-            // compressed keys: the scaled centroids against Q1, then the scaled residual signs against Q2, one accumulator
-            const int n_kc = (TURBO && s.tile_lo + jj < p.tiles_cold) ? 2 * kQChunks : kQChunks;
-            for (int c = 0; ok && c < n_kc; ++c) {
-              const uint32_t stage = drain % kStages;
-              {
-                TR_T0();
-                ok = wait_or_abort(&bars[SL::b_kv_full + stage], (drain / kStages) & 1, abort_flag, p.status);
-                TR_ACC(17);
-                if (drain == 0) TR_STAMP(2);
-              }
-              if (!ok) break;
-              ptx::tc_fence_after();
-              // descriptors differ only in the start-address field: +2 (32 bytes) per 16-element step
-              const uint64_t da0 = make_desc(q_addr + (c < kQChunks ? c * kChunkBytes : SL::q2 + (c - kQChunks) * kChunkBytes), 16, 1024);
-              const uint64_t db0 = make_desc(ptx::smem_u32(sm + SL::ring + stage * kChunkBytes), 16, 1024);
-              {
-                TR_T0();
-                if (c == 0) ptx::umma_ss_first(d_tmem, da0, db0, kIdescQK);
-                else ptx::umma_ss_acc(d_tmem, da0, db0, kIdescQK);
-                ptx::umma_ss_acc(d_tmem, da0 + 2, db0 + 2, kIdescQK);
-                ptx::umma_ss_acc(d_tmem, da0 + 4, db0 + 4, kIdescQK);
-                ptx::umma_ss_acc(d_tmem, da0 + 6, db0 + 6, kIdescQK);
-                ptx::umma_commit(&bars[SL::b_kv_empty + stage]);   // K chunk free once these products retire
-                TR_ACC(22);
-              }
-              ++drain;
-            }
+        for (int jj = 0; ok && jj < ntiles; ++jj) {
+          const uint32_t t = tile_ctr + jj, buf = t & 1;
+          const uint32_t d_tmem = tmem_base + kColS + buf * kBlockN;
+          if (t >= 2) {   // P of tile t - 2 lived in this buffer: its product must have retired
+            TR_T0();
+            ok = wait_or_abort(&bars[SL::b_s_free + buf], ((t >> 1) - 1) & 1, abort_flag, p.status);
+            TR_ACC(19);
             if (!ok) break;
-            ptx::umma_commit(&bars[SL::b_s_full + buf]);
-            if (jj == ntiles - 1) ptx::umma_commit(&bars[SL::b_q_empty]);   // last use of this Q tile
           }
-          if (jj > 0) {
-            // ---- O += P_{j-1} V_{j-1} ----
-            const uint32_t t = tile_ctr + jj - 1, buf = t & 1;
-            if (jj == 1 && seg_idx > 0) {
-              // first product of a segment overwrites O: the previous segment's epilogue must have read it
-              ok = wait_or_abort(&bars[SL::b_o_free], (seg_idx - 1) & 1, abort_flag, p.status);
-              if (!ok) break;
-            }
+          // compressed keys: the scaled centroids against Q1, then the scaled residual signs against Q2, one accumulator
+          const int n_kc = (TURBO && s.tile_lo + jj < p.tiles_cold) ? 2 * kQChunks : kQChunks;
+          for (int c = 0; ok && c < n_kc; ++c) {
+            const uint32_t stage = drain % kSK;
             {
               TR_T0();
-              ok = wait_or_abort(&bars[SL::b_p_full + buf], (t >> 1) & 1, abort_flag, p.status);
-              TR_ACC(19);
+              ok = wait_or_abort(&bars[SL::b_kv_full + stage], (drain / kSK) & 1, abort_flag, p.status);
+              TR_ACC(17);
+              if (drain == 0) TR_STAMP(2);
             }
             if (!ok) break;
             ptx::tc_fence_after();
-            const uint32_t p_tmem = tmem_base + kColS + buf * kBlockN;   // P (16-bit pairs) aliases S
-            // Two 64-column V chunks per instruction (N = 128): an instruction costs about 100
-            // clocks whether N is 64 or 128.  The pair sits in consecutive ring stages (loads come
-            // in groups of kQChunks, kStages is even, so a pair never straddles the wrap); the
-            // descriptor's leading-dimension offset is the 16 KiB from one chunk to the next.
-            for (int cp = 0; ok && cp < kQChunks / 2; ++cp) {
-              const uint32_t stage = drain % kStages;
-              {
-                TR_T0();
-                ok = wait_or_abort(&bars[SL::b_kv_full + stage], (drain / kStages) & 1, abort_flag, p.status) &&
-                     wait_or_abort(&bars[SL::b_kv_full + stage + 1], (drain / kStages) & 1, abort_flag, p.status);
-                TR_ACC(18);
-              }
-              if (!ok) break;
-              ptx::tc_fence_after();
-              // 16 keys per instruction: +128 (2048 bytes) in the start-address field, +8 P columns
-              const uint64_t db0 = make_desc(ptx::smem_u32(sm + SL::ring + stage * kChunkBytes), kChunkBytes, 1024);
-              const uint32_t o_tmem = tmem_base + kColO + cp * 128;
-              {
-                TR_T0();
-                if (jj > 1) ptx::umma_ts_acc(o_tmem, p_tmem, db0, kIdescPV);
-                else ptx::umma_ts_first(o_tmem, p_tmem, db0, kIdescPV);
-#pragma unroll
-                for (int kk = 1; kk < kBlockN / 16; ++kk)
-                  ptx::umma_ts_acc(o_tmem, p_tmem + kk * 8, db0 + (uint64_t)kk * 128, kIdescPV);
-                ptx::umma_commit(&bars[SL::b_kv_empty + stage]);
-                ptx::umma_commit(&bars[SL::b_kv_empty + stage + 1]);
-                TR_ACC(23);
-              }
-              drain += 2;
+            // descriptors differ only in the start-address field: +2 (32 bytes) per 16-element step
+            const uint64_t da0 = make_desc(q_addr + (c < kQChunks ? c * kChunkBytes : SL::q2 + (c - kQChunks) * kChunkBytes), 16, 1024);
+            const uint64_t db0 = make_desc(ptx::smem_u32(sm + SL::ring + stage * kChunkBytes), 16, 1024);
+            {
+              TR_T0();
+              if (c == 0) ptx::umma_ss_first(d_tmem, da0, db0, kIdescQK);
+              else ptx::umma_ss_acc(d_tmem, da0, db0, kIdescQK);
+              ptx::umma_ss_acc(d_tmem, da0 + 2, db0 + 2, kIdescQK);
+              ptx::umma_ss_acc(d_tmem, da0 + 4, db0 + 4, kIdescQK);
+              ptx::umma_ss_acc(d_tmem, da0 + 6, db0 + 6, kIdescQK);
+              ptx::umma_commit(&bars[SL::b_kv_empty + stage]);   // K chunk free once these products retire
+              TR_ACC(22);
             }
-            if (!ok) break;
-            ptx::umma_commit(&bars[SL::b_pv_done]);
+            ++drain;
           }
+          if (!ok) break;
+          ptx::umma_commit(&bars[SL::b_s_full + buf]);
+          if (jj == ntiles - 1) ptx::umma_commit(&bars[SL::b_q_empty]);   // last use of this Q tile
         }
         tile_ctr += ntiles;
         ++seg_idx;
       }
     }
-  } else if (!TURBO && warp == kThreads / 32) {
-    // ================================== P V issuer (dense KV) ==================================
-    if constexpr (!TURBO) if (lane == 0 && begin < end) {
+  } else if (warp == kThreads / 32) {
+    // ================================== P V issuer ==================================
+    if (lane == 0 && begin < end) {
       constexpr int kSK = SL::kStagesK, kSV = SL::kStagesV;
       SegmentIter it(p, begin, end, unit0, tile0);
       Segment s;
@@ -892,7 +790,7 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         ++seg_idx;
       }
     }
-  } else if (TURBO && warp >= kThreads / 32) {
+  } else if (TURBO && warp > kThreads / 32) {
     // ====================================== unpack =======================================
     // Compressed KV: thread t of these four warps owns key row t of every operand chunk of a cold tile.  Per tile it
     // expands, from the landing areas, the key's centroid indices into D / 64 chunks scaled by the key block's norm,
@@ -900,34 +798,35 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     // warp consumes them) the value's centroid indices scaled by the value block's norm - the operands the dense
     // path gets by TMA, in the same swizzled layout, so that no decoded key or value ever exists in global memory.
     if (begin < end) {
-      const int t = (int)threadIdx.x - kThreads;
+      const int t = (int)threadIdx.x - kThreads - kPvThreads;   // key row of a chunk
       constexpr int NB = D / 128;
+      constexpr int kSK = SL::kStagesK, kSV = SL::kStagesV;
       SegmentIter it(p, begin, end, unit0, tile0);
       Segment s;
-      uint32_t fill = 0, n_stg[3] = {0, 0, 0};
+      uint32_t fill_k = 0, fill_v = 0, n_stg[3] = {0, 0, 0};
       bool ok = true;
       float nrm[NB], mag[NB];
       auto wait_all = [&](void* bar, uint32_t parity) -> bool {
         return __all_sync(0xffffffffu, wait_or_abort(bar, parity, abort_flag, p.status));
       };
-      auto ring_slot = [&](uint8_t*& chunk) -> bool {            // the next stage, once the MMA warp has released it
-        const uint32_t stage = fill % kStages;
-        if (fill >= (uint32_t)kStages && !wait_all(&bars[SL::b_kv_empty + stage], ((fill / kStages) - 1) & 1)) return false;
-        chunk = sm + SL::ring + stage * kChunkBytes;
-        return true;
+      // the next stage of the K ring or of the V ring, once its consumer has released it
+      auto ring_slot = [&](bool is_k, uint32_t& stage) -> bool {
+        const uint32_t fill = is_k ? fill_k : fill_v, n = is_k ? kSK : kSV;
+        stage = (is_k ? 0u : (uint32_t)kSK) + fill % n;
+        return fill < n || wait_all(&bars[SL::b_kv_empty + stage], ((fill / n) - 1) & 1);
       };
-      auto publish = [&]() {                                     // this warp's 32 rows of the stage are written
+      auto publish = [&](bool is_k, uint32_t stage) {            // this warp's 32 rows of the stage are written
         ptx::fence_proxy_async();
         __syncwarp();
-        if (lane == 0) ptx::mbar_arrive(&bars[SL::b_kv_full + fill % kStages]);
-        ++fill;
+        if (lane == 0) ptx::mbar_arrive(&bars[SL::b_kv_full + stage]);
+        if (is_k) ++fill_k; else ++fill_v;
       };
       auto release = [&](int area) {
         __syncwarp();
         if (lane == 0) ptx::mbar_arrive(&bars[SL::b_stg_empty + area]);
         ++n_stg[area];
       };
-      auto unpack_k = [&]() -> bool {
+      auto unpack_kc = [&]() -> bool {                           // area A: the scaled centroids of the keys
         if (!wait_all(&bars[SL::b_stg_full + 0], n_stg[0] & 1)) return false;
         const uint16_t* kn = reinterpret_cast<const uint16_t*>(sm + SL::stg_a_kn);
         const uint16_t* kr = reinterpret_cast<const uint16_t*>(sm + SL::stg_a_kr);
@@ -938,61 +837,72 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         }
 #pragma unroll 1
         for (int c = 0; c < kQChunks; ++c) {
-          uint8_t* chunk;
-          if (!ring_slot(chunk)) return false;
-          unpack_centroid_row<InT>(chunk, t, sm + SL::stg_a + (t * NB + (c >> 1)) * 48 + (c & 1) * 24, nrm[c >> 1]);
-          publish();
+          uint32_t stage;
+          if (!ring_slot(true, stage)) return false;
+          unpack_centroid_row<InT>(sm + SL::ring + stage * kChunkBytes, t, sm + SL::stg_a + (t * NB + (c >> 1)) * 48 + (c & 1) * 24, nrm[c >> 1]);
+          publish(true, stage);
         }
         release(0);
+        return true;
+      };
+      auto unpack_ks = [&]() -> bool {                           // area B: the scaled residual signs of the keys
         if (!wait_all(&bars[SL::b_stg_full + 1], n_stg[1] & 1)) return false;
 #pragma unroll 1
         for (int c = 0; c < kQChunks; ++c) {
-          uint8_t* chunk;
-          if (!ring_slot(chunk)) return false;
-          unpack_sign_row<InT>(chunk, t, sm + SL::stg_b + (t * NB + (c >> 1)) * 16 + (c & 1) * 8, mag[c >> 1]);
-          publish();
+          uint32_t stage;
+          if (!ring_slot(true, stage)) return false;
+          unpack_sign_row<InT>(sm + SL::ring + stage * kChunkBytes, t, sm + SL::stg_b + (t * NB + (c >> 1)) * 16 + (c & 1) * 8, mag[c >> 1]);
+          publish(true, stage);
         }
         release(1);
         return true;
       };
-      auto unpack_v = [&]() -> bool {
-        if (!wait_all(&bars[SL::b_stg_full + 2], n_stg[2] & 1)) return false;
+      auto unpack_v = [&](int c0, int c1) -> bool {              // area C: value chunks c0 .. c1-1 of the tile
+        if (c0 == 0 && !wait_all(&bars[SL::b_stg_full + 2], n_stg[2] & 1)) return false;
         const uint16_t* vn = reinterpret_cast<const uint16_t*>(sm + SL::stg_c_vn);
 #pragma unroll 1
-        for (int c = 0; c < kQChunks; ++c) {
-          uint8_t* chunk;
-          if (!ring_slot(chunk)) return false;
-          unpack_centroid_row<InT>(chunk, t, sm + SL::stg_c + (t * NB + (c >> 1)) * 48 + (c & 1) * 24, f16_bits_to_float(vn[t * NB + (c >> 1)]));
-          publish();
+        for (int c = c0; c < c1; ++c) {
+          uint32_t stage;
+          if (!ring_slot(false, stage)) return false;
+          unpack_centroid_row<InT>(sm + SL::ring + stage * kChunkBytes, t, sm + SL::stg_c + (t * NB + (c >> 1)) * 48 + (c & 1) * 24, f16_bits_to_float(vn[t * NB + (c >> 1)]));
+          publish(false, stage);
         }
-        release(2);
+        if (c1 == kQChunks) release(2);
         return true;
       };
-      // A tile of the uncompressed hot window (rotated domain, [B, Hkv, n_hot, D]): the same stages, in the same order,
-      // filled by TMA.  Every warp waits for the stage and arrives once (the stage's barrier counts four arrivals); the
-      // first warp's arrival carries the byte count and its lane 0 issues the load.
-      auto load_hot = [&](const CUtensorMap* map, int tile) -> bool {
+      // Chunks c0 .. c1-1 of a tile of the uncompressed hot window (rotated domain, [B, Hkv, n_hot, D]): the same
+      // stages, filled by TMA.  Every warp waits for the stage and arrives once (the stage's barrier counts one arrival
+      // per unpack warp); the first warp's arrival carries the byte count and its lane 0 issues the load.
+      auto load_hot = [&](bool is_k, int tile, int c0, int c1) -> bool {
 #pragma unroll 1
-        for (int c = 0; c < kQChunks; ++c) {
-          uint8_t* chunk;
-          if (!ring_slot(chunk)) return false;
+        for (int c = c0; c < c1; ++c) {
+          uint32_t stage;
+          if (!ring_slot(is_k, stage)) return false;
           if (lane == 0) {
-            void* bar = &bars[SL::b_kv_full + fill % kStages];
+            void* bar = &bars[SL::b_kv_full + stage];
             if (t == 0) {
               ptx::mbar_arrive_expect_tx(bar, kChunkBytes);
-              ptx::tma_load_4d(chunk, map, c * 64, (tile - p.tiles_cold) * kBlockN, s.kvh, s.b, bar);
+              ptx::tma_load_4d(sm + SL::ring + stage * kChunkBytes, is_k ? &map_k : &map_v, c * 64, (tile - p.tiles_cold) * kBlockN, s.kvh, s.b, bar);
             } else {
               ptx::mbar_arrive(bar);
             }
           }
-          ++fill;
+          if (is_k) ++fill_k; else ++fill_v;
         }
         return true;
       };
+      // Per step: the keys of tile j and, one tile behind, the values of tile j - 1.  The two rings are independent, so
+      // the value chunks are produced in two halves around the keys' centroid chunks: the P V issuer drains the first
+      // half while the keys are being expanded (the V ring holds half a tile at D = 256).
+      constexpr int kVHalf = kQChunks >= 4 ? kQChunks / 2 : kQChunks;
       while (ok && it.next(s)) {
         for (int j = s.tile_lo; ok && j <= s.tile_hi; ++j) {
-          if (j < s.tile_hi) ok = j < p.tiles_cold ? unpack_k() : load_hot(&map_k, j);
-          if (ok && j > s.tile_lo) ok = j - 1 < p.tiles_cold ? unpack_v() : load_hot(&map_v, j - 1);
+          const bool has_k = j < s.tile_hi, has_v = j > s.tile_lo;
+          const bool k_cold = j < p.tiles_cold, v_cold = j - 1 < p.tiles_cold;
+          if (has_v) ok = v_cold ? unpack_v(0, kVHalf) : load_hot(false, j - 1, 0, kVHalf);
+          if (ok && has_k) ok = k_cold ? unpack_kc() : load_hot(true, j, 0, kQChunks);
+          if (ok && has_v && kVHalf < kQChunks) ok = v_cold ? unpack_v(kVHalf, kQChunks) : load_hot(false, j - 1, kVHalf, kQChunks);
+          if (ok && has_k && k_cold) ok = unpack_ks();
         }
       }
     }
@@ -1442,8 +1352,8 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
   // wait above is bounded, so both always get here.
   if (p.pair) cluster_sync_all();
   if (threadIdx.x == 0) TR_FLUSH(16, 16);
-  if (threadIdx.x == 32) { TR_FLUSH(17, 17); TR_FLUSH(22, 22); if (TURBO) { TR_FLUSH(18, 19); TR_FLUSH(23, 23); } }
-  if (!TURBO && threadIdx.x == kThreads) { TR_FLUSH(18, 19); TR_FLUSH(23, 23); }
+  if (threadIdx.x == 32) { TR_FLUSH(17, 17); TR_FLUSH(22, 22); }
+  if (threadIdx.x == kThreads) { TR_FLUSH(18, 19); TR_FLUSH(23, 23); }
   if (threadIdx.x == 64) TR_FLUSH(20, 21);
   ptx::tc_fence_before();
   __syncthreads();
