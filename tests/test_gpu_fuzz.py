@@ -73,3 +73,31 @@ def test_verify_sdpa_fuzz(B, Hkv, G, D, n_ctx, dtype, ragged, seed):
     K().device_status()
     want = CO.verify_sdpa(x["q"], x["k"], x["v"], float(x["scale"]), kv_len=lens)
     assert np.abs(out.float().cpu().numpy() - want).max() < 2e-2
+
+
+@settings(max_examples=16, deadline=None, derandomize=True, suppress_health_check=list(HealthCheck))
+@given(B=st.integers(1, 5), Hkv=st.integers(1, 3), G=st.sampled_from([1, 4, 8, 16]), D=st.sampled_from([128, 256]),
+       cold_tiles=st.integers(1, 9), n_hot=st.sampled_from([0, 16, 40, 128, 272]), dtype=st.sampled_from(["bf16", "bf16", "fp16"]),
+       seed=st.integers(0, 10 ** 6))
+def test_attention_over_compressed_kv_fuzz(B, Hkv, G, D, cold_tiles, n_hot, dtype, seed):
+    """The fused attention over TurboQuant KV (cold history of whole 128-key tiles, any hot window) against the oracle's
+    decode-then-attend."""
+    Hq, n_cold = Hkv * G, 128 * cold_tiles
+    N = n_cold + n_hot
+    x = O.make_sdpa_inputs(B, Hq, Hkv, N, D, seed, dtype)
+    dt = TORCH_DT[dtype]
+    k, v, q = dev(x["k"], dt), dev(x["v"], dt), dev(x["q"], dt)
+    k_enc = K().turbo_encode(k[:, :, :n_cold].contiguous(), True)
+    vp, _, vn, _ = K().turbo_encode(v[:, :, :n_cold].contiguous(), False)
+    out = K().batched_sdpa_turbo_kv(q, k_enc, (vp, vn), n_cold, float(x["scale"]),
+                                    k_hot=k[:, :, n_cold:].contiguous() if n_hot else None,
+                                    v_hot=v[:, :, n_cold:].contiguous() if n_hot else None)
+    torch.cuda.synchronize()
+    K().device_status()
+    rnd = O.round_bf16 if dtype == "bf16" else (lambda a: a.astype(np.float16).astype(np.float32))
+    p, s_, n_, r_ = CO.turbo_encode_k(x["k"][:, :, :n_cold].reshape(-1, 128))
+    k_ref = np.concatenate([rnd(CO.turbo_decode_k(p, s_, n_, r_)).reshape(B, Hkv, n_cold, D), x["k"][:, :, n_cold:]], axis=2)
+    p, n_ = CO.turbo_encode_v(x["v"][:, :, :n_cold].reshape(-1, 128))
+    v_ref = np.concatenate([rnd(CO.turbo_decode_v(p, n_)).reshape(B, Hkv, n_cold, D), x["v"][:, :, n_cold:]], axis=2)
+    want = CO.verify_sdpa(x["q"], k_ref, v_ref, float(x["scale"]))
+    assert np.abs(out.float().cpu().numpy() - want).max() < 2e-2
