@@ -12,7 +12,11 @@
 //     [S0 K^T | S0 Q^T]   128 x 128 x 32        (tcgen05, S0 split into two bf16 terms)
 //     [K K^T  | K Q^T ]    16 x 128 x 32        (tcgen05, exact in fp32)
 //     E K                 128 x  16 x 128       (tcgen05, E = Gam delta split into three bf16 terms)
-// plus a 16-step triangular recurrence per state row that one thread solves in registers.  A
+// plus, per state row, a 16 x 16 unit-lower-triangular system (I + C) delta = r with
+// C[t][s] = beta_t Gam[s,t] (k_s . k_t) and r_t = beta_t (v_t - G_t (S0 k_t)).  C is the same for the
+// 128 rows of a head-state, so the scalar warp inverts it once (N = (I + C)^-1, and Z = Ckq N for the
+// outputs) and every row gets delta = N r and y = G (S0 q) + Z r as independent dot products: no
+// step of a row waits for the step before it.  A
 // step that does not run (beyond the accepted length, or masked) gets gate 1 and beta 0: its
 // delta is exactly 0, its y is forced to 0 and the state passes through it unchanged.
 //
@@ -30,13 +34,13 @@
 //   mma     issuing warp: [S0 K^T | S0 Q^T] into tensor memory; under it the compute warps move
 //           the PREVIOUS item's finished state from tensor memory to a staging tile, which a TMA
 //           store sends out
-//   solve   two threads per state row: warps 0-3 run the recurrence for delta four steps at a time,
-//           hand the deltas over through shared memory, write the tape and put E into tensor memory
-//           as the A operand of the last product; warps 4-7 form y from the deltas
+//   solve   two threads per state row, both from r: warps 0-3 form delta = N r, write the tape and put
+//           E into tensor memory as the A operand of the last product; warps 4-7 form y = G (S0 q) + Z r
 //   mma     issuing warp: the accumulator += E K, then the next item's Gram products
 //   tables  scalar warp: gates and betas of the item after the next fetched into registers, those of
 //           the next item published; the next item's Gram rows out of tensor memory, scaled by the
-//           gate products (and beta) into the other table slot
+//           gate products (and beta) into C and Ckq, then N (lanes 0-15, a column each) and Z (lanes
+//           16-31, a row each) by one right-looking substitution into the other table slot
 // Hand-offs that only one side waits for use named barriers (bar.arrive on the other side).
 // Every wait is bounded; a wait that gives up sets the device status word and the CTA leaves.
 //
@@ -65,8 +69,8 @@ constexpr uint32_t kKQ = kX + 2 * 32768;         // 2 x 8 KiB: [2 chunks][32 row
 constexpr uint32_t kV = kKQ + 2 * 8192;          // 2 x 4 KiB: [16 steps][128] bf16
 constexpr uint32_t kTab = kV + 2 * 4096;         // 2 slots of coefficient tables
 constexpr uint32_t kTabSlot = 2304;
-constexpr uint32_t kTabKK = 0;                   //   [t][s] beta_t Gam[s,t] k_s.k_t (s < t), fp32
-constexpr uint32_t kTabKQ = 1024;                //   [t][s] Gam[s,t] k_s.q_t (s <= t)
+constexpr uint32_t kTabKK = 0;                   //   [t][s] N = (I + C)^-1, C[t][s] = beta_t Gam[s,t] k_s.k_t (s < t), fp32
+constexpr uint32_t kTabKQ = 1024;                //   [t][s] Z = Ckq N, Ckq[t][s] = Gam[s,t] k_s.q_t (s <= t)
 constexpr uint32_t kTabGp = 2048;                //   [t] G_t
 constexpr uint32_t kTabGe = 2048 + 64;           //   [s] Gam[s,T]
 constexpr uint32_t kTabBG = 2048 + 128;          //   [t] beta_t G_t
@@ -74,8 +78,9 @@ constexpr uint32_t kScal = kTab + 2 * kTabSlot;  // 2 slots x { gate'[16], beta'
 constexpr uint32_t kScalSlot = 160;
 constexpr uint32_t kBars = kScal + 2 * kScalSlot;   // 7 mbarriers: state loads x 2, Gram, W, E K, K/Q/V loads x 2
 constexpr uint32_t kMisc = kBars + 64;              // tensor-memory base
+constexpr uint32_t kScratch = kMisc + 16;           // 1 KiB: C reversed in both indices, the scalar warp's own
 constexpr uint32_t kSmemBytes = 226 * 1024;         // the Gram product reads 16 KiB past each K/Q chunk (rows it ignores)
-static_assert(kMisc + 16 <= kSmemBytes, "shared memory map");
+static_assert(kScratch % 16 == 0 && kScratch + 1024 <= kSmemBytes, "shared memory map");
 static_assert(kKQ + 8192 + 4096 + 16384 <= kSmemBytes, "Gram operand over-read stays inside the allocation");
 
 constexpr uint32_t kStateBytes = 65536, kTokenBytes = 8192 + 4096;
@@ -199,7 +204,7 @@ gdn_tc_kernel(const __grid_constant__ TcMaps maps, const GdnArgs a, int* status)
     uint8_t* tab = sm + kTab + slot * kTabSlot;
     float* tkk = reinterpret_cast<float*>(tab + kTabKK);
     float* tkq = reinterpret_cast<float*>(tab + kTabKQ);
-    // lanes 0-15: row s of the scaled Gram tables; lanes 16-31: the prefix products G_t.
+    // lanes 0-15: column s of C and of Ckq (the scaled Gram blocks); lanes 16-31: the prefix products G_t.
     // The scalars go to registers first: the table stores below could alias them for the compiler.
     {
       float gt[kT], bt[kT];
@@ -220,13 +225,58 @@ gdn_tc_kernel(const __grid_constant__ TcMaps maps, const GdnArgs a, int* status)
         okk[t] = t > s ? bt[t] * gam * __uint_as_float(gr[t]) : 0.f;
         okq[t] = t >= s ? gam * __uint_as_float(gr[16 + t]) : 0.f;
       }
+      // C goes out in the two orders the substitution reads it in: by column into the N table's place
+      // (row j = column j of C) and reversed in both indices into the scratch tile; Ckq by row into Z's place.
+      float* crev = reinterpret_cast<float*>(sm + kScratch);
       if (!pre) {
 #pragma unroll
-        for (int t = 0; t < kT; ++t) { tkk[t * 16 + s] = okk[t]; tkq[t * 16 + s] = okq[t]; }
+        for (int q4 = 0; q4 < 4; ++q4)
+          reinterpret_cast<float4*>(tkk + s * 16)[q4] = make_float4(okk[4 * q4], okk[4 * q4 + 1], okk[4 * q4 + 2], okk[4 * q4 + 3]);
+#pragma unroll
+        for (int t = 0; t < kT; ++t) { crev[(15 - t) * 16 + 15 - s] = okk[t]; tkq[t * 16 + s] = okq[t]; }
         reinterpret_cast<float*>(tab + kTabGe)[s] = gam;
       } else {
         reinterpret_cast<float*>(tab + kTabGp)[s] = gam;
         reinterpret_cast<float*>(tab + kTabBG)[s] = bsel * gam;
+      }
+      __syncwarp();
+      // One right-looking substitution for both halves of the warp, acc[i] -= acc[j] vec_j[i] for i > j:
+      //   lanes 0-15, column u = s of N:  (I + C) N = I;  acc[t] = N[t][u], vec_j = column j of C
+      //   lanes 16-31, row t = s of Z:    Z (I + C) = Ckq;  acc[i] = Z[t][15-i], vec_j = row 15-j of C, reversed
+      // Once acc[j] is final only the first update of the next round waits for it.
+      float acc[kT];
+      if (!pre) {
+#pragma unroll
+        for (int i = 0; i < kT; ++i) acc[i] = i == s ? 1.f : 0.f;
+      } else {
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+          const float4 c = reinterpret_cast<const float4*>(tkq + s * 16)[q4];
+          acc[15 - 4 * q4] = c.x; acc[14 - 4 * q4] = c.y; acc[13 - 4 * q4] = c.z; acc[12 - 4 * q4] = c.w;
+        }
+      }
+      __syncwarp();   // every row of Ckq has been read before Z overwrites it below
+      const float* vec = pre ? crev : tkk;
+#pragma unroll
+      for (int j = 0; j < kT - 1; ++j) {
+        const float piv = acc[j];
+#pragma unroll
+        for (int q4 = (j + 1) / 4; q4 < 4; ++q4) {
+          const float4 c = reinterpret_cast<const float4*>(vec + j * 16)[q4];
+          const float cv[4] = {c.x, c.y, c.z, c.w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e)
+            if (4 * q4 + e > j) acc[4 * q4 + e] = fmaf(-piv, cv[e], acc[4 * q4 + e]);
+        }
+      }
+      __syncwarp();   // all of C has been read before N overwrites it
+      if (!pre) {
+#pragma unroll
+        for (int t = 0; t < kT; ++t) tkk[t * 16 + s] = acc[t];
+      } else {
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4)
+          reinterpret_cast<float4*>(tkq + s * 16)[q4] = make_float4(acc[15 - 4 * q4], acc[14 - 4 * q4], acc[13 - 4 * q4], acc[12 - 4 * q4]);
       }
     }
     ptx::tc_fence_before();
@@ -264,6 +314,11 @@ gdn_tc_kernel(const __grid_constant__ TcMaps maps, const GdnArgs a, int* status)
     if (mma) {
       issue_token_loads(b_cur, hv_cur, 0);
       issue_state_load(b_cur, hv_cur, 0);
+      if (item + G < n_items) {
+        int b1, hv1;
+        decode(item + G, b1, hv1);
+        issue_token_loads(b1, hv1, 1);
+      }
       failed = !ptx::mbar_wait(&bars[5], 0);
       if (lane == 0) { ptx::tc_fence_after(); issue_gram(tmem, 0); }
       __syncwarp();
@@ -402,15 +457,15 @@ gdn_tc_kernel(const __grid_constant__ TcMaps maps, const GdnArgs a, int* status)
     }
     ptx::tc_fence_before();
     PH(1);
-    // split -> products and next loads: the compute warps only signal, the helper warps wait (named barrier 3)
-    if (helper) asm volatile("bar.sync 3, %0;" ::"n"(kThreads) : "memory");
-    else asm volatile("bar.arrive 3, %0;" ::"n"(kThreads) : "memory");
+    // split -> products and next loads: the compute warps only signal, the issuing warp waits (named barrier 3);
+    // the scalar warp has no part in it: it only ever writes the table and scalar slots of the NEXT item
+    if (mma) asm volatile("bar.sync 3, %0;" ::"n"(kPairThreads) : "memory");
+    else if (!helper) asm volatile("bar.arrive 3, %0;" ::"n"(kPairThreads) : "memory");
     PH(2);
 
     if (mma) {
-      // ---- issuing warp: the next item's state load (its landing tile is free again), the second
-      //      chunk's products, then the next item's K, Q, V loads ----
-      if (has_next) issue_state_load(b_nxt, hv_nxt, buf ^ 1);
+      // ---- issuing warp: the second chunk's products, then the next item's state load (its landing
+      //      tile is free again) ----
       if (lane == 0) {
         ptx::tc_fence_after();
         const uint32_t kq_addr = ptx::smem_u32(KQ), x_addr = ptx::smem_u32(sm + kX);
@@ -425,8 +480,7 @@ gdn_tc_kernel(const __grid_constant__ TcMaps maps, const GdnArgs a, int* status)
         ptx::umma_commit(&bars[3]);
       }
       __syncwarp();
-      if (it > 0) failed = !ptx::mbar_wait(&bars[4], par ^ 1u);   // E K of the previous item no longer reads its K rows
-      if (has_next) issue_token_loads(b_nxt, hv_nxt, buf ^ 1);
+      if (has_next) issue_state_load(b_nxt, hv_nxt, buf ^ 1);
     } else if (aux) {
       // ---- scalar warp: the next item's gates, betas and step bits ----
       if (has_next) {
@@ -451,8 +505,9 @@ gdn_tc_kernel(const __grid_constant__ TcMaps maps, const GdnArgs a, int* status)
     }
     PH(3);
 
-    // ---- solve: two threads per state row.  Warps 0-3 run the delta recurrence, hand the deltas
-    //      over through shared memory, then build E and write the tape; warps 4-7 form y ----
+    // ---- solve: two threads per state row, both from r_t = beta_t v_t - beta_t G_t (S0 k_t).  Warps 0-3 form
+    //      delta = N r, build E and write the tape; warps 4-7 form y = G (S0 q) + Z r.  A step that does not run
+    //      has beta' = 0, hence r = 0, and is skipped: its delta and its y are exactly 0 ----
     if (!helper) {
       failed = !ptx::mbar_wait(&bars[3], par) || failed;
       failed = !ptx::mbar_wait(&bars[5 + buf], (uint32_t)(it >> 1) & 1u) || failed;
@@ -462,65 +517,55 @@ gdn_tc_kernel(const __grid_constant__ TcMaps maps, const GdnArgs a, int* status)
       ptx::tmem_ld_wait();
       PH(9);
       const uint32_t bits = reinterpret_cast<const uint32_t*>(sc)[32];
-      float* dx = reinterpret_cast<float*>(sm + kX);   // [t][row]: the operand tiles are idle until the next split
       const long long obase = ((long long)b_cur * T * a.Hv + hv_cur) * kD + row;
       const long long ostep = (long long)a.Hv * kD;
-      float d[kT];
-      if (w < 4) {
-        const __nv_bfloat16* vt = reinterpret_cast<const __nv_bfloat16*>(sm + kV + buf * 4096);
-        const float4* tkk = reinterpret_cast<const float4*>(tab + kTabKK);
-        // delta_t = r_t - sum_{s<t} c[t][s] delta_s  with  r_t = beta_t v_t - beta_t G_t (S0 k_t)  (beta folded into c).
-        // Steps are taken four at a time; a group in which no step runs costs nothing.
-        float r[kT];
+      const __nv_bfloat16* vt = reinterpret_cast<const __nv_bfloat16*>(sm + kV + buf * 4096);
+      float r[kT];
 #pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4) {
-          const float4 bg4 = reinterpret_cast<const float4*>(tab + kTabBG)[q4], be4 = reinterpret_cast<const float4*>(sc + 16)[q4];
-          const float bgv[4] = {bg4.x, bg4.y, bg4.z, bg4.w}, bev[4] = {be4.x, be4.y, be4.z, be4.w};
+      for (int q4 = 0; q4 < 4; ++q4) {
+        const float4 bg4 = reinterpret_cast<const float4*>(tab + kTabBG)[q4], be4 = reinterpret_cast<const float4*>(sc + 16)[q4];
+        const float bgv[4] = {bg4.x, bg4.y, bg4.z, bg4.w}, bev[4] = {be4.x, be4.y, be4.z, be4.w};
 #pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const int t = 4 * q4 + e;
-            r[t] = fmaf(-bgv[e], __uint_as_float(wr[t]), bev[e] * __bfloat162float(vt[t * kD + row]));
-          }
-        }
-#pragma unroll
-        for (int g4 = 0; g4 < 4; ++g4) {
-          if ((bits >> (4 * g4)) & 0xFu) {   // uniform over the CTA
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              const int t = 4 * g4 + e;
-              float ckk[kT];
-#pragma unroll
-              for (int q4 = 0; q4 < 4; ++q4)
-                if (4 * q4 < t) {
-                  const float4 c = tkk[t * 4 + q4];
-                  ckk[4 * q4] = c.x; ckk[4 * q4 + 1] = c.y; ckk[4 * q4 + 2] = c.z; ckk[4 * q4 + 3] = c.w;
-                }
-              // two partial sums keep the chain through the freshest delta short; a step that does not
-              // run has beta' = 0, hence r = 0 and a zero row of c: its delta is exactly 0
-              float acc0 = r[t], acc1 = 0.f;
-#pragma unroll
-              for (int s = 0; s < t; ++s) {
-                if (s & 1) acc1 = fmaf(-d[s], ckk[s], acc1);
-                else acc0 = fmaf(-d[s], ckk[s], acc0);
-              }
-              d[t] = acc0 + acc1;
-            }
-          } else {
-#pragma unroll
-            for (int e = 0; e < 4; ++e) d[4 * g4 + e] = 0.f;
-          }
-          // hand the group over to the y threads (named barriers 6-9: this side only signals)
-#pragma unroll
-          for (int e = 0; e < 4; ++e) dx[(4 * g4 + e) * kD + row] = d[4 * g4 + e];
-          __threadfence_block();
-          if (g4 == 0) asm volatile("bar.arrive 6, %0;" ::"n"(kComputeThreads) : "memory");
-          else if (g4 == 1) asm volatile("bar.arrive 7, %0;" ::"n"(kComputeThreads) : "memory");
-          else if (g4 == 2) asm volatile("bar.arrive 8, %0;" ::"n"(kComputeThreads) : "memory");
-          else asm volatile("bar.arrive 9, %0;" ::"n"(kComputeThreads) : "memory");
+        for (int e = 0; e < 4; ++e) {
+          const int t = 4 * q4 + e;
+          r[t] = fmaf(-bgv[e], __uint_as_float(wr[t]), bev[e] * __bfloat162float(vt[t * kD + row]));
         }
       }
-      PH(4);
+      // rows 4 g4 .. 4 g4 + 3 of a lower-triangular table against r: eight independent partial sums.  A group
+      // in which no step runs is skipped (uniform over the CTA); a step that does not run inside a running
+      // group has r = 0 and a unit row of N: its delta comes out as exactly 0, its y is forced to 0.
+      auto tri_rows = [&](const float4* table, int g4, const float (&first)[4], float (&out)[4]) {
+        float a0[4] = {first[0], first[1], first[2], first[3]}, a1[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4)
+          if (q4 <= g4) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const float4 c = table[(4 * g4 + e) * 4 + q4];
+              const float cv[4] = {c.x, c.y, c.z, c.w};
+#pragma unroll
+              for (int x = 0; x < 4; ++x)
+                if (4 * q4 + x <= 4 * g4 + e) {
+                  if (x & 1) a1[e] = fmaf(cv[x], r[4 * q4 + x], a1[e]);
+                  else a0[e] = fmaf(cv[x], r[4 * q4 + x], a0[e]);
+                }
+            }
+          }
+#pragma unroll
+        for (int e = 0; e < 4; ++e) out[e] = a0[e] + a1[e];
+      };
+      const float zero4[4] = {0.f, 0.f, 0.f, 0.f};
       if (w < 4) {
+        const float4* tn = reinterpret_cast<const float4*>(tab + kTabKK);
+        float d[kT];
+#pragma unroll
+        for (int g4 = 0; g4 < 4; ++g4) {
+          float o[4] = {0.f, 0.f, 0.f, 0.f};
+          if ((bits >> (4 * g4)) & 0xFu) tri_rows(tn, g4, zero4, o);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) d[4 * g4 + e] = o[e];
+        }
+        PH(4);
         // E = Gam[s,T] delta_s, split exactly into three bf16 terms, as the A operand (pairs of steps per column)
         const float* ge = reinterpret_cast<const float*>(tab + kTabGe);
         uint32_t er[32];
@@ -542,49 +587,25 @@ gdn_tc_kernel(const __grid_constant__ TcMaps maps, const GdnArgs a, int* status)
         ptx::tmem_st_wait();
         ptx::tc_fence_before();
       } else {
-        // y_t = G_t (S0 q_t) + sum_{s<=t} c'[t][s] delta_s
-        const float4* tkq = reinterpret_cast<const float4*>(tab + kTabKQ);
+        const float4* tz = reinterpret_cast<const float4*>(tab + kTabKQ);
         const float* gp = reinterpret_cast<const float*>(tab + kTabGp);
         __nv_bfloat16* yout = reinterpret_cast<__nv_bfloat16*>(a.y);
-        float gpv[kT];
-#pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4) {
-          const float4 g4 = reinterpret_cast<const float4*>(gp)[q4];
-          gpv[4 * q4] = g4.x; gpv[4 * q4 + 1] = g4.y; gpv[4 * q4 + 2] = g4.z; gpv[4 * q4 + 3] = g4.w;
-        }
 #pragma unroll
         for (int g4 = 0; g4 < 4; ++g4) {
-          if (g4 == 0) asm volatile("bar.sync 6, %0;" ::"n"(kComputeThreads) : "memory");
-          else if (g4 == 1) asm volatile("bar.sync 7, %0;" ::"n"(kComputeThreads) : "memory");
-          else if (g4 == 2) asm volatile("bar.sync 8, %0;" ::"n"(kComputeThreads) : "memory");
-          else asm volatile("bar.sync 9, %0;" ::"n"(kComputeThreads) : "memory");
-#pragma unroll
-          for (int e = 0; e < 4; ++e) d[4 * g4 + e] = dx[(4 * g4 + e) * kD + row];
-          float y[4] = {0.f, 0.f, 0.f, 0.f};
+          float o[4] = {0.f, 0.f, 0.f, 0.f};
           if ((bits >> (4 * g4)) & 0xFu) {
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              const int t = 4 * g4 + e;
-              float ckq[kT];
-#pragma unroll
-              for (int q4 = 0; q4 < 4; ++q4)
-                if (4 * q4 <= t) {
-                  const float4 c = tkq[t * 4 + q4];
-                  ckq[4 * q4] = c.x; ckq[4 * q4 + 1] = c.y; ckq[4 * q4 + 2] = c.z; ckq[4 * q4 + 3] = c.w;
-                }
-              float y0 = gpv[t] * __uint_as_float(wr[16 + t]), y1 = 0.f;
-#pragma unroll
-              for (int s = 0; s <= t; ++s) {
-                if (s & 1) y1 = fmaf(d[s], ckq[s], y1);
-                else y0 = fmaf(d[s], ckq[s], y0);
-              }
-              y[e] = ((bits >> t) & 1u) ? y0 + y1 : 0.f;
-            }
+            const float4 gp4 = reinterpret_cast<const float4*>(gp)[g4];
+            const float y0[4] = {gp4.x * __uint_as_float(wr[16 + 4 * g4]), gp4.y * __uint_as_float(wr[17 + 4 * g4]),
+                                 gp4.z * __uint_as_float(wr[18 + 4 * g4]), gp4.w * __uint_as_float(wr[19 + 4 * g4])};
+            tri_rows(tz, g4, y0, o);
           }
 #pragma unroll
-          for (int e = 0; e < 4; ++e)
-            if (4 * g4 + e < T) yout[obase + (4 * g4 + e) * ostep] = __float2bfloat16_rn(y[e]);
+          for (int e = 0; e < 4; ++e) {
+            const int t = 4 * g4 + e;
+            if (t < T) yout[obase + t * ostep] = __float2bfloat16_rn(((bits >> t) & 1u) ? o[e] : 0.f);
+          }
         }
+        PH(4);
       }
     }
     PH(5);
@@ -608,6 +629,14 @@ gdn_tc_kernel(const __grid_constant__ TcMaps maps, const GdnArgs a, int* status)
         failed = !ptx::mbar_wait(&bars[5 + (buf ^ 1)], (uint32_t)((it + 1) >> 1) & 1u);
         if (lane == 0) { ptx::tc_fence_after(); issue_gram(tmem, buf ^ 1); }
         __syncwarp();
+      }
+      // K, Q, V of the item after the next go into this item's buffers as soon as E K has read its K rows
+      // (every other reader of them finished before the barrier above): a whole iteration ahead of their use
+      if (nxt + G < n_items) {
+        failed = !ptx::mbar_wait(&bars[4], par) || failed;
+        int b2, hv2;
+        decode(nxt + G, b2, hv2);
+        issue_token_loads(b2, hv2, buf);
       }
     } else if (aux && has_next) {
       failed = !ptx::mbar_wait(&bars[2], gram_uses & 1u);
