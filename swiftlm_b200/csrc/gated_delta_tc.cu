@@ -26,21 +26,22 @@
 //
 // One persistent CTA per SM: eight compute warps, a scalar warp and an issuing warp.  Per work
 // item (sequence, v-head), with the phases of neighbouring items interleaved:
-//   load    issuing warp, TMA: the fp32 state tile (four 128-byte-swizzled boxes; one landing tile,
-//           refilled for the next item as soon as the split has read it), and K, Q rows of the block
-//           (swizzled, they are tensor-core operands as they land) and V rows on a barrier of their own
+//   load    issuing warp, TMA: the fp32 state tile (four 128-byte-swizzled boxes) into one of two landing tiles,
+//           issued two items ahead, as soon as the split has read the tile's previous contents: a state load is
+//           in flight at all times.  K, Q rows of the block (swizzled, they are tensor-core operands as they
+//           land) and V rows on a barrier of their own, also two items ahead
 //   split   compute warps, two threads per state row: S0 -> two bf16 operand tiles in the tensor
 //           cores' K-major layout, and G_T * S0 in fp32 -> the item's accumulator in tensor memory
-//   mma     issuing warp: [S0 K^T | S0 Q^T] into tensor memory; under it the compute warps move
-//           the PREVIOUS item's finished state from tensor memory to a staging tile, which a TMA
-//           store sends out
+//   mma     issuing warp: [S0 K^T | S0 Q^T] into tensor memory (first operand chunk while the split works
+//           on the second); behind each half of the products the compute warps move the PREVIOUS item's
+//           finished state from tensor memory into the operand tiles' memory, which a TMA store sends out
 //   solve   two threads per state row, both from r: warps 0-3 form delta = N r, write the tape and put
 //           E into tensor memory as the A operand of the last product; warps 4-7 form y = G (S0 q) + Z r
 //   mma     issuing warp: the accumulator += E K, then the next item's Gram products
 //   tables  scalar warp: gates and betas of the item after the next fetched into registers, those of
 //           the next item published; the next item's Gram rows out of tensor memory, scaled by the
-//           gate products (and beta) into C and Ckq, then N (lanes 0-15, a column each) and Z (lanes
-//           16-31, a row each) by one right-looking substitution into the other table slot
+//           gate products (and beta) into C and Ckq, then N (lanes 0-15, a row each) and Z (lanes
+//           16-31, a row each) by one right-looking substitution over shuffles into the other table slot
 // Hand-offs that only one side waits for use named barriers (bar.arrive on the other side).
 // Every wait is bounded; a wait that gives up sets the device status word and the CTA leaves.
 //
@@ -58,14 +59,14 @@ namespace {
 constexpr int kD = 128;
 constexpr int kT = 16;
 constexpr int kComputeThreads = 256;
-constexpr int kThreads = kComputeThreads + 64;   // + two helper warps: warp 8 scalars and tables, warp 9 TMA and tensor-core issue
+constexpr int kThreads = kComputeThreads + 96;   // + three helper warps: warp 8 scalars and tables, warp 9 tensor-core issue, warp 10 TMA loads
 constexpr int kPairThreads = kComputeThreads + 32;   // participants of the compute <-> one-helper named barriers
+constexpr int kTrioThreads = kComputeThreads + 64;   // compute <-> issuing and loading warps
 
 // shared memory map (bytes); every tensor-core / TMA tile starts on a 1024-byte boundary
-constexpr uint32_t kL = 0;                       // 64 KiB: landing tile of the fp32 state [4 boxes][128 rows][32 floats]
-constexpr uint32_t kY = 65536;                   // 64 KiB: staging tile of the outgoing state, same layout
-constexpr uint32_t kX = 2 * 65536;               // 2 x 32 KiB: bf16 operand tiles hi, lo: [2 chunks][128 rows][64]
-constexpr uint32_t kKQ = kX + 2 * 32768;         // 2 x 8 KiB: [2 chunks][32 rows: 16 k, 16 q][64]
+constexpr uint32_t kL = 0;                       // 2 x 64 KiB: landing tiles of the fp32 state [4 boxes][128 rows][32 floats]
+constexpr uint32_t kY = 2 * 65536;               // 64 KiB: staging tile of the outgoing state, same layout
+constexpr uint32_t kKQ = kY + 65536;             // 2 x 8 KiB: [2 chunks][32 rows: 16 k, 16 q][64]
 constexpr uint32_t kV = kKQ + 2 * 8192;          // 2 x 4 KiB: [16 steps][128] bf16
 constexpr uint32_t kTab = kV + 2 * 4096;         // 2 slots of coefficient tables
 constexpr uint32_t kTabSlot = 2304;
@@ -76,11 +77,10 @@ constexpr uint32_t kTabGe = 2048 + 64;           //   [s] Gam[s,T]
 constexpr uint32_t kTabBG = 2048 + 128;          //   [t] beta_t G_t
 constexpr uint32_t kScal = kTab + 2 * kTabSlot;  // 2 slots x { gate'[16], beta'[16], bits }
 constexpr uint32_t kScalSlot = 160;
-constexpr uint32_t kBars = kScal + 2 * kScalSlot;   // 7 mbarriers: state loads x 2, Gram, W, E K, K/Q/V loads x 2
+constexpr uint32_t kBars = kScal + 2 * kScalSlot;   // 8 mbarriers: state loads x 2, Gram, W, E K, K/Q/V loads x 2, first half of W
 constexpr uint32_t kMisc = kBars + 64;              // tensor-memory base
-constexpr uint32_t kScratch = kMisc + 16;           // 1 KiB: C reversed in both indices, the scalar warp's own
 constexpr uint32_t kSmemBytes = 226 * 1024;         // the Gram product reads 16 KiB past each K/Q chunk (rows it ignores)
-static_assert(kScratch % 16 == 0 && kScratch + 1024 <= kSmemBytes, "shared memory map");
+static_assert(kMisc + 16 <= kSmemBytes, "shared memory map");
 static_assert(kKQ + 8192 + 4096 + 16384 <= kSmemBytes, "Gram operand over-read stays inside the allocation");
 
 constexpr uint32_t kStateBytes = 65536, kTokenBytes = 8192 + 4096;
@@ -89,7 +89,8 @@ constexpr uint32_t kStateBytes = 65536, kTokenBytes = 8192 + 4096;
 constexpr uint32_t kColW = 0;      // [S0 K^T | S0 Q^T]: 32
 constexpr uint32_t kColGram = 32;  // 32
 constexpr uint32_t kColE = 64;     // E as bf16 pairs: 3 x 8
-constexpr uint32_t kColD = 128;    // 2 x 128: the items' accumulators G_T S0 + E K
+constexpr uint32_t kColA = 96;     // S0 as bf16 pairs, the A operand of [S0 K^T | S0 Q^T]: hi 64 columns, lo 64
+constexpr uint32_t kColD = 256;    // 2 x 128: the items' accumulators G_T S0 + E K
 constexpr uint32_t kTmemCols = 512;
 
 __device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
@@ -107,7 +108,7 @@ __device__ __forceinline__ uint32_t pack_trunc(float a, float b) {
 __device__ __forceinline__ float trunc16(float a) { return __uint_as_float(__float_as_uint(a) & 0xffff0000u); }
 
 struct TcMaps {
-  CUtensorMap state_in, state_out, k, q, v;
+  CUtensorMap state_in, state_out, k, q, v, y, tape;
 };
 
 __global__ void __launch_bounds__(kThreads, 1)
@@ -118,12 +119,12 @@ gdn_tc_kernel(const __grid_constant__ TcMaps maps, const GdnArgs a, int* status)
     return;
   }
   const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
-  const bool helper = w >= 8, aux = w == 8, mma = w == 9;
+  const bool helper = w >= 8, aux = w == 8, mma = w == 9, ldw = w == 10;
   const int T = a.T;
   const int rep = a.Hv / a.Hk;
   const uint32_t n_items = (uint32_t)a.B * (uint32_t)a.Hv;
   const uint32_t G = gridDim.x;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sm + kBars);   // 0,1: state loads; 2: Gram; 3: W; 4: E K; 5,6: K/Q/V loads
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sm + kBars);   // 0,1: state loads; 2: Gram; 3: W; 4: E K; 5,6: K/Q/V loads; 7: first half of W
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sm + kMisc);
   const __nv_bfloat16* gg = reinterpret_cast<const __nv_bfloat16*>(a.g);
   const __nv_bfloat16* gbeta = reinterpret_cast<const __nv_bfloat16*>(a.beta);
@@ -164,7 +165,7 @@ gdn_tc_kernel(const __grid_constant__ TcMaps maps, const GdnArgs a, int* status)
     void* bar = &bars[buf];
     if (lane == 0) ptx::mbar_arrive_expect_tx(bar, kStateBytes);
     __syncwarp();
-    if (lane < 4) ptx::tma_load_2d(sm + kL + lane * 16384, &maps.state_in, lane * 32, (b * a.Hv + hv) * kD, bar);
+    if (lane < 4) ptx::tma_load_2d(sm + kL + buf * 65536 + lane * 16384, &maps.state_in, lane * 32, (b * a.Hv + hv) * kD, bar);
     __syncwarp();
   };
   auto issue_token_loads = [&](int b, int hv, int buf) {   // a whole warp
@@ -185,100 +186,70 @@ gdn_tc_kernel(const __grid_constant__ TcMaps maps, const GdnArgs a, int* status)
   constexpr uint32_t kIdescW = (1u << 4) | (1u << 7) | (1u << 10) | ((32u >> 3) << 17) | ((128u >> 4) << 24);
   constexpr uint32_t kIdescD = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
   // Gram products of the item in buffer buf: rows of [K; Q] against [K; Q]; only rows 0-15 (the k rows) are read back
-  auto issue_gram = [&](uint32_t tmem, int buf) {   // one thread
+  PH_DECL();
+  auto issue_gram = [&](uint32_t tmem, int buf) {   // a whole warp, converged; lane 0 issues
     const uint32_t kq_addr = ptx::smem_u32(sm + kKQ + buf * 8192);
+    const uint32_t leader = lane == 0;
 #pragma unroll
     for (int kk = 0; kk < 8; ++kk) {
       const uint64_t d = make_desc(kq_addr + (kk >> 2) * 4096, 16, 1024) + 2 * (kk & 3);
-      if (kk == 0) ptx::umma_ss_first(tmem + kColGram, d, d, kIdescW);
-      else ptx::umma_ss_acc(tmem + kColGram, d, d, kIdescW);
+      ptx::umma_ss_if(leader, tmem + kColGram, d, d, kIdescW, kk != 0);
     }
-    ptx::umma_commit(&bars[2]);
+    ptx::umma_commit_if(leader, &bars[2]);
   };
   // the helper warp: Gram rows out of tensor memory, scaled by gate products (and beta), into table slot
+  // The scalar warp: lane t < 16 holds row t of the Gram block K K^T (symmetric, so also its column) and lane
+  // 16 + t row t of Q K^T.  Each lane scales its own row by gate products (and beta) into row t of C (lanes
+  // 0-15) or of Ckq (lanes 16-31), then one right-looking substitution, the same for both halves, gives row t
+  // of N = (I + C)^-1 (N (I + C) = I) and of Z = Ckq N (Z (I + C) = Ckq):
+  //     acc[u] -= acc[s] C[s][u]   for s = 15 .. 1, u < s,
+  // with row s of C broadcast from lane s by shuffles.  Nothing passes through shared memory but the results.
   auto build_tables = [&](uint32_t tmem, int slot) {
     uint32_t gr[32];
-    ptx::tmem_ld32(tmem + kColGram, gr);   // lane s < 16: k_s.k_t (t < 16), k_s.q_t
+    ptx::tmem_ld32(tmem + kColGram, gr);   // lane t < 16: k_t.k_s (s < 16); lane 16 + t: q_t.k_s
     ptx::tmem_ld_wait();
+    PH(9);
     const float* sc = reinterpret_cast<const float*>(sm + kScal + slot * kScalSlot);
     uint8_t* tab = sm + kTab + slot * kTabSlot;
-    float* tkk = reinterpret_cast<float*>(tab + kTabKK);
-    float* tkq = reinterpret_cast<float*>(tab + kTabKQ);
-    // lanes 0-15: column s of C and of Ckq (the scaled Gram blocks); lanes 16-31: the prefix products G_t.
-    // The scalars go to registers first: the table stores below could alias them for the compiler.
-    {
-      float gt[kT], bt[kT];
+    float gt[kT];
 #pragma unroll
-      for (int q4 = 0; q4 < 4; ++q4) {
-        const float4 g4 = reinterpret_cast<const float4*>(sc)[q4], b4 = reinterpret_cast<const float4*>(sc + 16)[q4];
-        gt[4 * q4] = g4.x; gt[4 * q4 + 1] = g4.y; gt[4 * q4 + 2] = g4.z; gt[4 * q4 + 3] = g4.w;
-        bt[4 * q4] = b4.x; bt[4 * q4 + 1] = b4.y; bt[4 * q4 + 2] = b4.z; bt[4 * q4 + 3] = b4.w;
-      }
-      const int s = lane & 15;
-      const bool pre = lane >= kT;
-      float gam = 1.f, bsel = 0.f;
-      float okk[kT], okq[kT];
-#pragma unroll
-      for (int t = 0; t < kT; ++t) {
-        if (pre ? t <= s : t > s) gam *= gt[t];
-        if (t == s) bsel = bt[t];
-        okk[t] = t > s ? bt[t] * gam * __uint_as_float(gr[t]) : 0.f;
-        okq[t] = t >= s ? gam * __uint_as_float(gr[16 + t]) : 0.f;
-      }
-      // C goes out in the two orders the substitution reads it in: by column into the N table's place
-      // (row j = column j of C) and reversed in both indices into the scratch tile; Ckq by row into Z's place.
-      float* crev = reinterpret_cast<float*>(sm + kScratch);
-      if (!pre) {
-#pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4)
-          reinterpret_cast<float4*>(tkk + s * 16)[q4] = make_float4(okk[4 * q4], okk[4 * q4 + 1], okk[4 * q4 + 2], okk[4 * q4 + 3]);
-#pragma unroll
-        for (int t = 0; t < kT; ++t) { crev[(15 - t) * 16 + 15 - s] = okk[t]; tkq[t * 16 + s] = okq[t]; }
-        reinterpret_cast<float*>(tab + kTabGe)[s] = gam;
-      } else {
-        reinterpret_cast<float*>(tab + kTabGp)[s] = gam;
-        reinterpret_cast<float*>(tab + kTabBG)[s] = bsel * gam;
-      }
-      __syncwarp();
-      // One right-looking substitution for both halves of the warp, acc[i] -= acc[j] vec_j[i] for i > j:
-      //   lanes 0-15, column u = s of N:  (I + C) N = I;  acc[t] = N[t][u], vec_j = column j of C
-      //   lanes 16-31, row t = s of Z:    Z (I + C) = Ckq;  acc[i] = Z[t][15-i], vec_j = row 15-j of C, reversed
-      // Once acc[j] is final only the first update of the next round waits for it.
-      float acc[kT];
-      if (!pre) {
-#pragma unroll
-        for (int i = 0; i < kT; ++i) acc[i] = i == s ? 1.f : 0.f;
-      } else {
-#pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4) {
-          const float4 c = reinterpret_cast<const float4*>(tkq + s * 16)[q4];
-          acc[15 - 4 * q4] = c.x; acc[14 - 4 * q4] = c.y; acc[13 - 4 * q4] = c.z; acc[12 - 4 * q4] = c.w;
-        }
-      }
-      __syncwarp();   // every row of Ckq has been read before Z overwrites it below
-      const float* vec = pre ? crev : tkk;
-#pragma unroll
-      for (int j = 0; j < kT - 1; ++j) {
-        const float piv = acc[j];
-#pragma unroll
-        for (int q4 = (j + 1) / 4; q4 < 4; ++q4) {
-          const float4 c = reinterpret_cast<const float4*>(vec + j * 16)[q4];
-          const float cv[4] = {c.x, c.y, c.z, c.w};
-#pragma unroll
-          for (int e = 0; e < 4; ++e)
-            if (4 * q4 + e > j) acc[4 * q4 + e] = fmaf(-piv, cv[e], acc[4 * q4 + e]);
-        }
-      }
-      __syncwarp();   // all of C has been read before N overwrites it
-      if (!pre) {
-#pragma unroll
-        for (int t = 0; t < kT; ++t) tkk[t * 16 + s] = acc[t];
-      } else {
-#pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4)
-          reinterpret_cast<float4*>(tkq + s * 16)[q4] = make_float4(acc[15 - 4 * q4], acc[14 - 4 * q4], acc[13 - 4 * q4], acc[12 - 4 * q4]);
-      }
+    for (int q4 = 0; q4 < 4; ++q4) {
+      const float4 g4 = reinterpret_cast<const float4*>(sc)[q4];
+      gt[4 * q4] = g4.x; gt[4 * q4 + 1] = g4.y; gt[4 * q4 + 2] = g4.z; gt[4 * q4 + 3] = g4.w;
     }
+    const int t = lane & 15;
+    const bool pre = lane >= kT;
+    const float beta_t = sc[16 + t];
+    // row t: Gam[s,t] = g_{s+1} .. g_t, built downwards from s = t; prefix and suffix products of the gates
+    float crow[kT], acc[kT];
+    float gam = 1.f, g_pre = 1.f, g_suf = 1.f;
+    const float scale = pre ? 1.f : beta_t;
+#pragma unroll
+    for (int s_ = kT - 1; s_ >= 0; --s_) {
+      if (s_ < t) gam *= gt[s_ + 1 < kT ? s_ + 1 : kT - 1];
+      const float wgt = s_ < t ? gam : (s_ == t && pre ? 1.f : 0.f);
+      const float val = wgt * scale * __uint_as_float(gr[s_]);
+      crow[s_] = val;
+      acc[s_] = pre ? val : (s_ == t ? 1.f : 0.f);
+      if (s_ <= t) g_pre *= gt[s_];
+      else g_suf *= gt[s_];
+    }
+    if (!pre) {
+      reinterpret_cast<float*>(tab + kTabGp)[t] = g_pre;
+      reinterpret_cast<float*>(tab + kTabBG)[t] = beta_t * g_pre;
+      reinterpret_cast<float*>(tab + kTabGe)[t] = g_suf;
+    }
+    PH(10);
+#pragma unroll
+    for (int s_ = kT - 1; s_ >= 1; --s_) {
+      const float piv = acc[s_];
+#pragma unroll
+      for (int u = 0; u < s_; ++u) acc[u] = fmaf(-piv, __shfl_sync(0xffffffffu, crow[u], s_), acc[u]);
+    }
+    PH(11);
+    float4* dst = reinterpret_cast<float4*>(tab + (pre ? kTabKQ : kTabKK)) + t * 4;
+#pragma unroll
+    for (int q4 = 0; q4 < 4; ++q4) dst[q4] = make_float4(acc[4 * q4], acc[4 * q4 + 1], acc[4 * q4 + 2], acc[4 * q4 + 3]);
     ptx::tc_fence_before();
     __syncwarp();
   };
@@ -286,7 +257,7 @@ gdn_tc_kernel(const __grid_constant__ TcMaps maps, const GdnArgs a, int* status)
   // ---- prologue ----
   uint32_t item = blockIdx.x;
   if (tid == 0) {
-    for (int i = 0; i < 7; ++i) ptx::mbar_init(&bars[i], 1);
+    for (int i = 0; i < 8; ++i) ptx::mbar_init(&bars[i], 1);
     ptx::fence_mbar_init();
   }
   if (mma && lane == 0) {
@@ -295,6 +266,8 @@ gdn_tc_kernel(const __grid_constant__ TcMaps maps, const GdnArgs a, int* status)
     ptx::prefetch_tensormap(&maps.q);
     ptx::prefetch_tensormap(&maps.v);
     ptx::prefetch_tensormap(&maps.state_out);
+    ptx::prefetch_tensormap(&maps.y);
+    if (a.tape) ptx::prefetch_tensormap(&maps.tape);
   }
   if (aux) {
     ptx::tmem_alloc(tmem_slot, kTmemCols);
@@ -311,16 +284,19 @@ gdn_tc_kernel(const __grid_constant__ TcMaps maps, const GdnArgs a, int* status)
   bool h_m = false;  // its mask bit
   if (item < n_items) {
     decode(item, b_cur, hv_cur);
-    if (mma) {
+    if (ldw) {
       issue_token_loads(b_cur, hv_cur, 0);
       issue_state_load(b_cur, hv_cur, 0);
       if (item + G < n_items) {
         int b1, hv1;
         decode(item + G, b1, hv1);
         issue_token_loads(b1, hv1, 1);
+        issue_state_load(b1, hv1, 1);
       }
+    } else if (mma) {
       failed = !ptx::mbar_wait(&bars[5], 0);
-      if (lane == 0) { ptx::tc_fence_after(); issue_gram(tmem, 0); }
+      ptx::tc_fence_after();
+      issue_gram(tmem, 0);
       __syncwarp();
     } else if (aux) {
       float g0, be0;
@@ -352,9 +328,12 @@ gdn_tc_kernel(const __grid_constant__ TcMaps maps, const GdnArgs a, int* status)
   // previous item's finished state: tensor memory -> staging tile -> TMA store (compute warps)
   auto flush_state = [&](int dbuf, int b, int hv, uint32_t ek_parity) -> bool {
     if (tid < 4) ptx::bulk_wait_read_all();           // the staging tile's previous store (this lane's box) has been read
+    PH(12);
     bool ok = ptx::mbar_wait(&bars[4], ek_parity);
     ptx::tc_fence_after();
+    PH(13);
     asm volatile("bar.sync 1, %0;" ::"n"(kComputeThreads) : "memory");
+    PH(10);
 #pragma unroll
     for (int bb = 0; bb < 2; ++bb) {
       uint32_t dr[32];
@@ -373,10 +352,10 @@ gdn_tc_kernel(const __grid_constant__ TcMaps maps, const GdnArgs a, int* status)
       ptx::tma_store_2d(&maps.state_out, tid * 32, row0, sm + kY + tid * 16384);
       ptx::bulk_commit_group();
     }
+    PH(11);
     return ok;
   };
 
-  PH_DECL();
   int b_prev = 0, hv_prev = 0, it = 0;
   for (; item < n_items; ++it, item += G) {
     const int buf = it & 1;
@@ -393,7 +372,7 @@ gdn_tc_kernel(const __grid_constant__ TcMaps maps, const GdnArgs a, int* status)
     if (!helper) failed = !ptx::mbar_wait(&bars[buf], (uint32_t)(it >> 1) & 1u);
     PH(0);
 
-    // ---- split: S0 = hi + lo + (dropped 2^-17), both bf16, K-major; G_T S0 -> this item's accumulator ----
+    // ---- split: S0 = hi + lo + (dropped 2^-17), both bf16, into tensor memory; G_T S0 -> this item's accumulator ----
     if (!helper) {
       float g_T = 1.f;
 #pragma unroll
@@ -404,7 +383,7 @@ gdn_tc_kernel(const __grid_constant__ TcMaps maps, const GdnArgs a, int* status)
         float4 x4[8];
 #pragma unroll
         for (int g = 0; g < 8; ++g)
-          x4[g] = *reinterpret_cast<const float4*>(sm + kL + box * 16384 + row * 128 + ((g ^ (row & 7)) << 4));
+          x4[g] = *reinterpret_cast<const float4*>(sm + kL + buf * 65536 + box * 16384 + row * 128 + ((g ^ (row & 7)) << 4));
         uint32_t acc[32];
 #pragma unroll
         for (int g = 0; g < 8; ++g) {
@@ -414,73 +393,80 @@ gdn_tc_kernel(const __grid_constant__ TcMaps maps, const GdnArgs a, int* status)
           acc[4 * g + 3] = __float_as_uint(g_T * x4[g].w);
         }
         ptx::tmem_st32(tmem + lane_addr + kColD + 128 * buf + 32 * box, acc);
-        // operand tiles: 16-byte granule = 8 columns
+        // the operand in tensor memory: a column holds two neighbouring state columns as a bf16 pair
+        uint32_t hi[16], lo[16];
 #pragma unroll
-        for (int gg8 = 0; gg8 < 4; ++gg8) {
-          const float x[8] = {x4[2 * gg8].x, x4[2 * gg8].y, x4[2 * gg8].z, x4[2 * gg8].w,
-                              x4[2 * gg8 + 1].x, x4[2 * gg8 + 1].y, x4[2 * gg8 + 1].z, x4[2 * gg8 + 1].w};
-          uint32_t hi[4], lo[4];
+        for (int g = 0; g < 8; ++g) {
+          const float x[4] = {x4[g].x, x4[g].y, x4[g].z, x4[g].w};
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            hi[i] = pack_trunc(x[2 * i], x[2 * i + 1]);
-            lo[i] = pack_rn(x[2 * i] - trunc16(x[2 * i]), x[2 * i + 1] - trunc16(x[2 * i + 1]));
+          for (int i = 0; i < 2; ++i) {
+            hi[2 * g + i] = pack_trunc(x[2 * i], x[2 * i + 1]);
+            lo[2 * g + i] = pack_rn(x[2 * i] - trunc16(x[2 * i]), x[2 * i + 1] - trunc16(x[2 * i + 1]));
           }
-          const int gran = half * 4 + gg8;
-          uint8_t* dst = sm + kX + pass * 16384 + row * 128 + ((gran ^ (row & 7)) << 4);
-          *reinterpret_cast<uint4*>(dst) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
-          *reinterpret_cast<uint4*>(dst + 32768) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
         }
+        ptx::tmem_st16(tmem + lane_addr + kColA + 16 * box, hi);
+        ptx::tmem_st16(tmem + lane_addr + kColA + 64 + 16 * box, lo);
         if (pass == 0) {
           // the first chunk is complete: its eight products can run under the second pass (named barrier 5)
-          ptx::fence_proxy_async();
+          ptx::tmem_st_wait();
+          ptx::tc_fence_before();
           asm volatile("bar.arrive 5, %0;" ::"n"(kPairThreads) : "memory");
         }
       }
-      ptx::fence_proxy_async();
       ptx::tmem_st_wait();
     } else if (mma) {
       asm volatile("bar.sync 5, %0;" ::"n"(kPairThreads) : "memory");
-      if (lane == 0) {
+      {
         ptx::tc_fence_after();
-        const uint32_t kq_addr = ptx::smem_u32(KQ), x_addr = ptx::smem_u32(sm + kX);
+        const uint32_t kq_addr = ptx::smem_u32(KQ), leader = lane == 0;
 #pragma unroll
         for (int sp = 0; sp < 2; ++sp)
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk) {
-            const uint64_t da = make_desc(x_addr + sp * 32768, 16, 1024) + 2 * kk;
             const uint64_t db = make_desc(kq_addr, 16, 1024) + 2 * kk;
-            if (sp == 0 && kk == 0) ptx::umma_ss_first(tmem + kColW, da, db, kIdescW);
-            else ptx::umma_ss_acc(tmem + kColW, da, db, kIdescW);
+            ptx::umma_ts_if(leader, tmem + kColW, tmem + kColA + 64 * sp + 8 * kk, db, kIdescW, (sp | kk) != 0);
           }
       }
       __syncwarp();
     }
     ptx::tc_fence_before();
     PH(1);
-    // split -> products and next loads: the compute warps only signal, the issuing warp waits (named barrier 3);
+    // split -> products and next loads: the compute warps only signal, the issuing and loading warps wait (named barrier 3);
     // the scalar warp has no part in it: it only ever writes the table and scalar slots of the NEXT item
-    if (mma) asm volatile("bar.sync 3, %0;" ::"n"(kPairThreads) : "memory");
-    else if (!helper) asm volatile("bar.arrive 3, %0;" ::"n"(kPairThreads) : "memory");
+    if (mma || ldw) asm volatile("bar.sync 3, %0;" ::"n"(kTrioThreads) : "memory");
+    else if (!helper) asm volatile("bar.arrive 3, %0;" ::"n"(kTrioThreads) : "memory");
     PH(2);
 
     if (mma) {
-      // ---- issuing warp: the second chunk's products, then the next item's state load (its landing
-      //      tile is free again) ----
-      if (lane == 0) {
+      // ---- issuing warp: the second chunk's products ----
+      {
         ptx::tc_fence_after();
-        const uint32_t kq_addr = ptx::smem_u32(KQ), x_addr = ptx::smem_u32(sm + kX);
+        const uint32_t kq_addr = ptx::smem_u32(KQ), leader = lane == 0;
 #pragma unroll
         for (int sp = 0; sp < 2; ++sp)
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk) {
-            const uint64_t da = make_desc(x_addr + sp * 32768 + 16384, 16, 1024) + 2 * kk;
             const uint64_t db = make_desc(kq_addr + 4096, 16, 1024) + 2 * kk;
-            ptx::umma_ss_acc(tmem + kColW, da, db, kIdescW);
+            ptx::umma_ts_if(leader, tmem + kColW, tmem + kColA + 64 * sp + 32 + 8 * kk, db, kIdescW, 1u);
           }
-        ptx::umma_commit(&bars[3]);
+        ptx::umma_commit_if(leader, &bars[3]);
       }
       __syncwarp();
-      if (has_next) issue_state_load(b_nxt, hv_nxt, buf ^ 1);
+      // the next item's Gram products: its K, Q rows landed an iteration ago, and the scalar warp read the
+      // previous Gram block before the barrier that ended the previous iteration
+      if (has_next) {
+        failed = !ptx::mbar_wait(&bars[5 + (buf ^ 1)], (uint32_t)((it + 1) >> 1) & 1u) || failed;
+        ptx::tc_fence_after();
+        issue_gram(tmem, buf ^ 1);
+        __syncwarp();
+      }
+    } else if (ldw) {
+      // ---- loading warp: the state of the item after the next into this item's landing tile (free again) ----
+      if (nxt + G < n_items) {
+        int b2, hv2;
+        decode(nxt + G, b2, hv2);
+        issue_state_load(b2, hv2, buf);
+      }
     } else if (aux) {
       // ---- scalar warp: the next item's gates, betas and step bits ----
       if (has_next) {
@@ -501,13 +487,17 @@ gdn_tc_kernel(const __grid_constant__ TcMaps maps, const GdnArgs a, int* status)
     } else {
       // ---- compute warps, under the helper's products: the previous item's state goes out ----
       if (it > 0 && !flush_state(buf ^ 1, b_prev, hv_prev, par ^ 1u)) failed = true;
-      asm volatile("bar.sync 4, %0;" ::"n"(kPairThreads) : "memory");   // this item's tables are in place
+      // this item's tables are in place (named barriers 4 and 6 alternate: the scalar warp signals the next
+      // item's tables before this item's have been waited for)
+      if (buf) asm volatile("bar.sync 6, %0;" ::"n"(kPairThreads) : "memory");
+      else asm volatile("bar.sync 4, %0;" ::"n"(kPairThreads) : "memory");
     }
     PH(3);
 
     // ---- solve: two threads per state row, both from r_t = beta_t v_t - beta_t G_t (S0 k_t).  Warps 0-3 form
     //      delta = N r, build E and write the tape; warps 4-7 form y = G (S0 q) + Z r.  A step that does not run
     //      has beta' = 0, hence r = 0, and is skipped: its delta and its y are exactly 0 ----
+    float outv[kT];
     if (!helper) {
       failed = !ptx::mbar_wait(&bars[3], par) || failed;
       failed = !ptx::mbar_wait(&bars[5 + buf], (uint32_t)(it >> 1) & 1u) || failed;
@@ -517,8 +507,6 @@ gdn_tc_kernel(const __grid_constant__ TcMaps maps, const GdnArgs a, int* status)
       ptx::tmem_ld_wait();
       PH(9);
       const uint32_t bits = reinterpret_cast<const uint32_t*>(sc)[32];
-      const long long obase = ((long long)b_cur * T * a.Hv + hv_cur) * kD + row;
-      const long long ostep = (long long)a.Hv * kD;
       const __nv_bfloat16* vt = reinterpret_cast<const __nv_bfloat16*>(sm + kV + buf * 4096);
       float r[kT];
 #pragma unroll
@@ -531,6 +519,8 @@ gdn_tc_kernel(const __grid_constant__ TcMaps maps, const GdnArgs a, int* status)
           r[t] = fmaf(-bgv[e], __uint_as_float(wr[t]), bev[e] * __bfloat162float(vt[t * kD + row]));
         }
       }
+      // every row's r is formed: nothing reads this item's V rows any more, the outputs are staged over them
+      asm volatile("bar.sync 7, %0;" ::"n"(kComputeThreads) : "memory");
       // rows 4 g4 .. 4 g4 + 3 of a lower-triangular table against r: eight independent partial sums.  A group
       // in which no step runs is skipped (uniform over the CTA); a step that does not run inside a running
       // group has r = 0 and a unit row of N: its delta comes out as exactly 0, its y is forced to 0.
@@ -557,7 +547,7 @@ gdn_tc_kernel(const __grid_constant__ TcMaps maps, const GdnArgs a, int* status)
       const float zero4[4] = {0.f, 0.f, 0.f, 0.f};
       if (w < 4) {
         const float4* tn = reinterpret_cast<const float4*>(tab + kTabKK);
-        float d[kT];
+        float (&d)[kT] = outv;
 #pragma unroll
         for (int g4 = 0; g4 < 4; ++g4) {
           float o[4] = {0.f, 0.f, 0.f, 0.f};
@@ -579,17 +569,23 @@ gdn_tc_kernel(const __grid_constant__ TcMaps maps, const GdnArgs a, int* status)
           er[24 + c] = 0u;
         }
         ptx::tmem_st32(tmem + lane_addr + kColE, er);
+        PH(14);
         if (a.tape) {
+          // the tape rows are staged at the head of the state's staging tile, once the previous state's
+          // store has read it (it was issued a whole flush ago), and leave with a TMA store after the barrier
+          if (tid < 4) ptx::bulk_wait_read_all();
+          asm volatile("bar.sync 8, 128;" ::: "memory");
+          float* stage = reinterpret_cast<float*>(sm + kY);
 #pragma unroll
-          for (int t = 0; t < kT; ++t)
-            if (t < T) a.tape[obase + t * ostep] = d[t];
+          for (int t = 0; t < kT; ++t) stage[t * kD + row] = d[t];
+          ptx::fence_proxy_async();
         }
         ptx::tmem_st_wait();
         ptx::tc_fence_before();
       } else {
         const float4* tz = reinterpret_cast<const float4*>(tab + kTabKQ);
         const float* gp = reinterpret_cast<const float*>(tab + kTabGp);
-        __nv_bfloat16* yout = reinterpret_cast<__nv_bfloat16*>(a.y);
+        float (&yv)[kT] = outv;
 #pragma unroll
         for (int g4 = 0; g4 < 4; ++g4) {
           float o[4] = {0.f, 0.f, 0.f, 0.f};
@@ -600,12 +596,13 @@ gdn_tc_kernel(const __grid_constant__ TcMaps maps, const GdnArgs a, int* status)
             tri_rows(tz, g4, y0, o);
           }
 #pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const int t = 4 * g4 + e;
-            if (t < T) yout[obase + t * ostep] = __float2bfloat16_rn(((bits >> t) & 1u) ? o[e] : 0.f);
-          }
+          for (int e = 0; e < 4; ++e) yv[4 * g4 + e] = ((bits >> (4 * g4 + e)) & 1u) ? o[e] : 0.f;
         }
-        PH(4);
+        PH(14);
+        __nv_bfloat16* stage = reinterpret_cast<__nv_bfloat16*>(sm + kV + buf * 4096);
+#pragma unroll
+        for (int t = 0; t < kT; ++t) stage[t * kD + row] = __float2bfloat16_rn(yv[t]);
+        ptx::fence_proxy_async();
       }
     }
     PH(5);
@@ -614,37 +611,50 @@ gdn_tc_kernel(const __grid_constant__ TcMaps maps, const GdnArgs a, int* status)
 
     // ---- issuing warp: accumulator += E K, then the next item's Gram products; scalar warp: its tables ----
     if (mma) {
-      if (lane == 0) {
+      {
         ptx::tc_fence_after();
         // k rows 0-15 of both chunks as an MN-major operand: 64-column atoms 4096 bytes apart, 8-step groups 1024 apart
         const uint64_t db = make_desc(ptx::smem_u32(KQ), 4096, 1024);
-        const uint32_t dcol = tmem + kColD + 128 * buf;
-        ptx::umma_ts_acc(dcol, tmem + kColE, db, kIdescD);
-        ptx::umma_ts_acc(dcol, tmem + kColE + 8, db, kIdescD);
-        ptx::umma_ts_acc(dcol, tmem + kColE + 16, db, kIdescD);
-        ptx::umma_commit(&bars[4]);
+        const uint32_t dcol = tmem + kColD + 128 * buf, leader = lane == 0;
+        ptx::umma_ts_if(leader, dcol, tmem + kColE, db, kIdescD, 1u);
+        ptx::umma_ts_if(leader, dcol, tmem + kColE + 8, db, kIdescD, 1u);
+        ptx::umma_ts_if(leader, dcol, tmem + kColE + 16, db, kIdescD, 1u);
+        ptx::umma_commit_if(leader, &bars[4]);
       }
       __syncwarp();
-      if (has_next) {
-        failed = !ptx::mbar_wait(&bars[5 + (buf ^ 1)], (uint32_t)((it + 1) >> 1) & 1u);
-        if (lane == 0) { ptx::tc_fence_after(); issue_gram(tmem, buf ^ 1); }
-        __syncwarp();
+    } else if (ldw) {
+      // this item's outputs leave from its V buffer
+      if (lane == 0) {
+        ptx::tma_store_4d(&maps.y, 0, hv_cur, 0, b_cur, sm + kV + buf * 4096);
+        ptx::bulk_commit_group();
       }
-      // K, Q, V of the item after the next go into this item's buffers as soon as E K has read its K rows
-      // (every other reader of them finished before the barrier above): a whole iteration ahead of their use
+      // K, Q, V of the item after the next go into this item's buffers as soon as E K has read its K rows and
+      // the store above its V buffer (every other reader of them finished before the barrier above): a whole
+      // iteration ahead of their use
       if (nxt + G < n_items) {
         failed = !ptx::mbar_wait(&bars[4], par) || failed;
+        if (lane == 0) ptx::bulk_wait_read_all();
+        __syncwarp();
         int b2, hv2;
         decode(nxt + G, b2, hv2);
         issue_token_loads(b2, hv2, buf);
       }
+    } else if (!helper) {
+      if (tid == 0 && a.tape) {   // steps past T fall outside the tensor and are dropped by the store
+        ptx::tma_store_4d(&maps.tape, 0, hv_cur, 0, b_cur, sm + kY);
+        ptx::bulk_commit_group();
+      }
     } else if (aux && has_next) {
+      // the next item's tables: its Gram products were issued behind this item's second chunk
       failed = !ptx::mbar_wait(&bars[2], gram_uses & 1u);
       ++gram_uses;
       ptx::tc_fence_after();
+      PH(12);
       build_tables(tmem, buf ^ 1);
+      PH(13);
       __threadfence_block();
-      asm volatile("bar.arrive 4, %0;" ::"n"(kPairThreads) : "memory");
+      if (buf) asm volatile("bar.arrive 4, %0;" ::"n"(kPairThreads) : "memory");
+      else asm volatile("bar.arrive 6, %0;" ::"n"(kPairThreads) : "memory");
     }
     PH(7);
     b_prev = b_cur;
@@ -659,7 +669,7 @@ gdn_tc_kernel(const __grid_constant__ TcMaps maps, const GdnArgs a, int* status)
 
   PH_FLUSH();
   if (failed && lane == 0) atomicExch(status, kStatusGdnWait);
-  if (tid < 4) ptx::bulk_wait_all();    // shared memory must outlive the last stores
+  if (tid < 4 || (ldw && lane == 0)) ptx::bulk_wait_all();    // shared memory must outlive the last stores
   ptx::tc_fence_before();
   __syncthreads();
   if (aux) {
@@ -676,7 +686,8 @@ bool gdn_tc_supported(const GdnArgs& a) {
   if ((long long)a.B * a.Hv > (1LL << 24) - 1024) return false;
   if (a.Hv % a.Hk != 0) return false;
   // TMA needs 16-byte aligned bases
-  const uintptr_t al = (uintptr_t)a.q | (uintptr_t)a.k | (uintptr_t)a.v | (uintptr_t)a.state_in | (uintptr_t)a.state_out;
+  const uintptr_t al = (uintptr_t)a.q | (uintptr_t)a.k | (uintptr_t)a.v | (uintptr_t)a.state_in | (uintptr_t)a.state_out |
+                       (uintptr_t)a.y | (uintptr_t)a.tape;
   return (al & 15u) == 0;
 }
 
@@ -708,6 +719,14 @@ int32_t launch_gdn_tc(const GdnArgs& a, cudaStream_t stream) {
   if (r == CUDA_SUCCESS) r = token_map(&maps.k, a.k, a.Hk, 64, CU_TENSOR_MAP_SWIZZLE_128B);
   if (r == CUDA_SUCCESS) r = token_map(&maps.q, a.q, a.Hk, 64, CU_TENSOR_MAP_SWIZZLE_128B);
   if (r == CUDA_SUCCESS) r = token_map(&maps.v, a.v, a.Hv, 128, CU_TENSOR_MAP_SWIZZLE_NONE);
+  if (r == CUDA_SUCCESS) r = token_map(&maps.y, a.y, a.Hv, 128, CU_TENSOR_MAP_SWIZZLE_NONE);
+  if (r == CUDA_SUCCESS && a.tape) {
+    const cuuint64_t dims[4] = {(cuuint64_t)kD, (cuuint64_t)a.Hv, (cuuint64_t)a.T, (cuuint64_t)a.B};
+    const cuuint64_t strides[3] = {(cuuint64_t)kD * 4, (cuuint64_t)a.Hv * kD * 4, (cuuint64_t)a.T * a.Hv * kD * 4};
+    const cuuint32_t box[4] = {(cuuint32_t)kD, 1, (cuuint32_t)kT, 1};
+    r = encode(&maps.tape, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, a.tape, dims, strides, box, ones, CU_TENSOR_MAP_INTERLEAVE_NONE,
+               CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  }
   if (r != CUDA_SUCCESS) { set_error("cuTensorMapEncodeTiled failed with CUresult %d", (int)r); return DFLASH_ERR_CUDA; }
   DFLASH_CUDA_CHECK(cudaFuncSetAttribute(gdn_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes));
   const long long items = (long long)a.B * a.Hv;

@@ -29,10 +29,10 @@ extern "C" int dflash_debug_trace(unsigned long long* out, int n, int clear) {
 
 // Optional phase timing (compile with -DDFLASH_GDN_TRACE; never part of the shipped library).
 #ifdef DFLASH_GDN_TRACE
-__device__ unsigned long long g_gdn_trace[256 * 10 * 16];
-#define PH_DECL() long long ph_[10] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0}; long long ph_t_ = clock64()
+__device__ unsigned long long g_gdn_trace[256 * 12 * 16];
+#define PH_DECL() long long ph_[16] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0}; long long ph_t_ = clock64()
 #define PH(i) do { const long long n_ = clock64(); ph_[i] += n_ - ph_t_; ph_t_ = n_; } while (0)
-#define PH_FLUSH() do { if ((threadIdx.x & 31) == 0) for (int i_ = 0; i_ < 10; ++i_) g_gdn_trace[(blockIdx.x * 10 + (threadIdx.x >> 5)) * 16 + i_] = (unsigned long long)ph_[i_]; } while (0)
+#define PH_FLUSH() do { if ((threadIdx.x & 31) == 0) for (int i_ = 0; i_ < 16; ++i_) g_gdn_trace[(blockIdx.x * 12 + (threadIdx.x >> 5)) * 16 + i_] = (unsigned long long)ph_[i_]; } while (0)
 extern "C" int dflash_gdn_trace(unsigned long long* out, int n) { return (int)cudaMemcpyFromSymbol(out, g_gdn_trace, sizeof(unsigned long long) * n); }
 #else
 #define PH_DECL() do {} while (0)
