@@ -51,10 +51,10 @@ def measured_peaks():
 
 # DRAM bytes moved per algorithmic byte, scaled from a smaller case: dram__bytes_read.sum +
 # dram__bytes_write.sum of one profiled launch of the same kernel on 16 of the 64 sequences
-# (2.6157 GB moved for 2.5627 GB algorithmic; traffic grows in proportion to the head-states
+# (2.6081 GB moved for 2.5627 GB algorithmic; traffic grows in proportion to the head-states
 # processed), and of one launch of configs[2] itself for the attention (279.0 MB moved for
 # 277.9 MB algorithmic, no merge kernel in that regime).
-TRAFFIC_PER_ALGORITHMIC_BYTE = {"gdn_tc_forward": 1.0207, "sdpa_tc": 1.0041}
+TRAFFIC_PER_ALGORITHMIC_BYTE = {"gdn_tc_forward": 1.0177, "sdpa_tc": 1.0041}
 
 
 class ClockSampler:
