@@ -60,7 +60,7 @@ constexpr int kBlockN = 128;            // keys per tile
 constexpr int kRowsM = 128;             // query rows per unit tile
 constexpr int kChunkBytes = 128 * 128;  // one TMA box: 128 rows x 64 16-bit elements
 constexpr int kThreads = 320;          // TMA warp, MMA warp, 8 softmax warps
-constexpr int kUnpackThreads = 128;    // compressed KV only: 4 more warps expand packed keys and values into the ring
+constexpr int kUnpackThreads = 256;    // compressed KV only: 8 more warps expand packed bytes into the rings: four the keys, four the values
 constexpr int kPvThreads = 32;         // one more warp whose lane 0 issues the P V products
 template <bool TURBO> struct ThreadsOf { static constexpr int value = kThreads + kPvThreads + (TURBO ? kUnpackThreads : 0); };
 constexpr float kRescaleThreshold = 8.f;   // in log2 units
@@ -451,8 +451,9 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     ptx::prefetch_tensormap(&map_v);
     for (int i = 0; i < SL::n_bars; ++i) {
       const bool eight = (i == SL::b_o_free) || (i == SL::b_p_full) || (i == SL::b_p_full + 1);
-      // compressed KV: a ring stage is filled either by the four unpack warps (one arrival each) or by a TMA load
-      // (the producer arrives four times); a landing area is released by the four unpack warps
+      // compressed KV: a ring stage is filled by the four warps of one unpack group (one arrival each; for a hot tile
+      // the group's first lane issues a TMA load and its arrival carries the byte count); a landing area is released
+      // by the four warps of the group that reads it
       const bool four = TURBO && ((i >= SL::b_kv_full && i < SL::b_kv_full + kStages) || (i >= SL::b_stg_empty && i < SL::b_stg_empty + 3));
       ptx::mbar_init(&bars[i], i == SL::b_peer_data ? 256 : (eight ? 8 : (four ? 4 : 1)));
     }
@@ -772,13 +773,16 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     }
   } else if (TURBO && warp > kThreads / 32) {
     // ====================================== unpack =======================================
-    // Compressed KV: thread t of these four warps owns key row t of every operand chunk of a cold tile.  Per tile it
+    // Compressed KV: two groups of four warps, one for the keys, one for the values; thread t of a group owns key row
+    // t of every operand chunk its group makes.  Per cold tile a group
     // expands, from the landing areas, the key's centroid indices into D / 64 chunks scaled by the key block's norm,
     // its residual sign bits into D / 64 chunks of +-(norm * QJL_C / 128 * rnorm), and (one tile behind, as the MMA
     // warp consumes them) the value's centroid indices scaled by the value block's norm - the operands the dense
     // path gets by TMA, in the same swizzled layout, so that no decoded key or value ever exists in global memory.
     if (begin < end) {
-      const int t = (int)threadIdx.x - kThreads - kPvThreads;   // key row of a chunk
+      const int u = (int)threadIdx.x - kThreads - kPvThreads;
+      const int t = u & 127;                                    // key row of a chunk
+      const bool v_group = u >= 128;                            // warps 0-3 expand keys (K ring), warps 4-7 values (V ring)
       constexpr int NB = D / 128;
       constexpr int kSK = SL::kStagesK, kSV = SL::kStagesV;
       SegmentIter it(p, begin, end, unit0, tile0);
@@ -871,18 +875,18 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         }
         return true;
       };
-      // Per step: the keys of tile j and, one tile behind, the values of tile j - 1.  The two rings are independent, so
-      // the value chunks are produced in two halves around the keys' centroid chunks: the P V issuer drains the first
-      // half while the keys are being expanded (the V ring holds half a tile at D = 256).
-      constexpr int kVHalf = kQChunks >= 4 ? kQChunks / 2 : kQChunks;
+      // The keys of tile j (K ring, landing areas A and B) and, one tile behind, the values of tile j - 1 (V ring, area C)
+      // are expanded by separate groups of four warps: neither waits for the other's ring.  (One group doing both spent
+      // most of a tile's time in the twelve per-chunk hand-offs, one after another.)
       while (ok && it.next(s)) {
         for (int j = s.tile_lo; ok && j <= s.tile_hi; ++j) {
           const bool has_k = j < s.tile_hi, has_v = j > s.tile_lo;
           const bool k_cold = j < p.tiles_cold, v_cold = j - 1 < p.tiles_cold;
-          if (has_v) ok = v_cold ? unpack_v(0, kVHalf) : load_hot(false, j - 1, 0, kVHalf);
-          if (ok && has_k) ok = k_cold ? unpack_kc() : load_hot(true, j, 0, kQChunks);
-          if (ok && has_v && kVHalf < kQChunks) ok = v_cold ? unpack_v(kVHalf, kQChunks) : load_hot(false, j - 1, kVHalf, kQChunks);
-          if (ok && has_k && k_cold) ok = unpack_ks();
+          if (v_group) {
+            if (has_v) ok = v_cold ? unpack_v(0, kQChunks) : load_hot(false, j - 1, 0, kQChunks);
+          } else if (has_k) {
+            ok = k_cold ? (unpack_kc() && unpack_ks()) : load_hot(true, j, 0, kQChunks);
+          }
         }
       }
     }
