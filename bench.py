@@ -655,7 +655,7 @@ def run_verify_step(torch, device, rank, world, peaks, max_over_ranks, barrier):
     from swiftlm_b200.verify_step import StepConfig, VerifyStep
     total = 64
     lo, hi = partition.plan(total, world)[rank]
-    cfg = StepConfig(batch=hi - lo)
+    cfg = StepConfig(batch=hi - lo, keep_state_verify=False)   # every sequence's result state is the rollback's
     step = VerifyStep(cfg, device)
     from swiftlm_b200 import kernels
     for _ in range(2):
@@ -680,7 +680,8 @@ def run_verify_step(torch, device, rank, world, peaks, max_over_ranks, barrier):
     byts = step.bytes_per_step() * world
     return {"config": f"configs[4]: 36 gated-delta + 12 attention layers, 64 sequences over {world} GPU(s), T=16, context 8192, "
                       "TurboQuant 3-bit KV, vocabulary 151936, per-sequence acceptance; one dflash_verify_step call per step "
-                      "(layers of a kind stacked into one launch), then the all-gather of acceptance and logits rows",
+                      "(layers of a kind stacked into one launch; the verify forward writes no final state, the rollback's state is the result "
+                      "for every sequence), then the all-gather of acceptance and logits rows",
             "ms_per_step": ms, "steps_per_s": 1e3 / ms, "sequences": total, "launches_per_step": launches,
             "committed_tokens_per_step_per_sequence": accepted,
             "ms_step_gather": parts[i],

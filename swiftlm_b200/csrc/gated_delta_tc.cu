@@ -123,6 +123,9 @@ gdn_tc_kernel(const __grid_constant__ TcMaps maps, const GdnArgs a, int* status)
   const int T = a.T;
   const int rep = a.Hv / a.Hk;
   const uint32_t n_items = (uint32_t)a.B * (uint32_t)a.Hv;
+  // No final state wanted (the verify step, whose result state is the rollback's): nothing is accumulated into the
+  // items' accumulators, no E K product, no state leaves the SM.
+  const bool want_state = a.state_out != nullptr;
   const uint32_t G = gridDim.x;
   uint64_t* bars = reinterpret_cast<uint64_t*>(sm + kBars);   // 0,1: state loads; 2: Gram; 3: W; 4: E K; 5,6: K/Q/V loads; 7: first half of W
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sm + kMisc);
@@ -384,15 +387,17 @@ gdn_tc_kernel(const __grid_constant__ TcMaps maps, const GdnArgs a, int* status)
 #pragma unroll
         for (int g = 0; g < 8; ++g)
           x4[g] = *reinterpret_cast<const float4*>(sm + kL + buf * 65536 + box * 16384 + row * 128 + ((g ^ (row & 7)) << 4));
-        uint32_t acc[32];
+        if (want_state) {
+          uint32_t acc[32];
 #pragma unroll
-        for (int g = 0; g < 8; ++g) {
-          acc[4 * g] = __float_as_uint(g_T * x4[g].x);
-          acc[4 * g + 1] = __float_as_uint(g_T * x4[g].y);
-          acc[4 * g + 2] = __float_as_uint(g_T * x4[g].z);
-          acc[4 * g + 3] = __float_as_uint(g_T * x4[g].w);
+          for (int g = 0; g < 8; ++g) {
+            acc[4 * g] = __float_as_uint(g_T * x4[g].x);
+            acc[4 * g + 1] = __float_as_uint(g_T * x4[g].y);
+            acc[4 * g + 2] = __float_as_uint(g_T * x4[g].z);
+            acc[4 * g + 3] = __float_as_uint(g_T * x4[g].w);
+          }
+          ptx::tmem_st32(tmem + lane_addr + kColD + 128 * buf + 32 * box, acc);
         }
-        ptx::tmem_st32(tmem + lane_addr + kColD + 128 * buf + 32 * box, acc);
         // the operand in tensor memory: a column holds two neighbouring state columns as a bf16 pair
         uint32_t hi[16], lo[16];
 #pragma unroll
@@ -486,7 +491,7 @@ gdn_tc_kernel(const __grid_constant__ TcMaps maps, const GdnArgs a, int* status)
       PH(8);
     } else {
       // ---- compute warps, under the helper's products: the previous item's state goes out ----
-      if (it > 0 && !flush_state(buf ^ 1, b_prev, hv_prev, par ^ 1u)) failed = true;
+      if (want_state && it > 0 && !flush_state(buf ^ 1, b_prev, hv_prev, par ^ 1u)) failed = true;
       // this item's tables are in place (named barriers 4 and 6 alternate: the scalar warp signals the next
       // item's tables before this item's have been waited for)
       if (buf) asm volatile("bar.sync 6, %0;" ::"n"(kPairThreads) : "memory");
@@ -557,18 +562,20 @@ gdn_tc_kernel(const __grid_constant__ TcMaps maps, const GdnArgs a, int* status)
         }
         PH(4);
         // E = Gam[s,T] delta_s, split exactly into three bf16 terms, as the A operand (pairs of steps per column)
-        const float* ge = reinterpret_cast<const float*>(tab + kTabGe);
-        uint32_t er[32];
+        if (want_state) {
+          const float* ge = reinterpret_cast<const float*>(tab + kTabGe);
+          uint32_t er[32];
 #pragma unroll
-        for (int c = 0; c < 8; ++c) {
-          const float e0 = ge[2 * c] * d[2 * c], e1 = ge[2 * c + 1] * d[2 * c + 1];
-          const float r0 = e0 - trunc16(e0), r1 = e1 - trunc16(e1);
-          er[c] = pack_trunc(e0, e1);
-          er[8 + c] = pack_trunc(r0, r1);
-          er[16 + c] = pack_rn(r0 - trunc16(r0), r1 - trunc16(r1));
-          er[24 + c] = 0u;
+          for (int c = 0; c < 8; ++c) {
+            const float e0 = ge[2 * c] * d[2 * c], e1 = ge[2 * c + 1] * d[2 * c + 1];
+            const float r0 = e0 - trunc16(e0), r1 = e1 - trunc16(e1);
+            er[c] = pack_trunc(e0, e1);
+            er[8 + c] = pack_trunc(r0, r1);
+            er[16 + c] = pack_rn(r0 - trunc16(r0), r1 - trunc16(r1));
+            er[24 + c] = 0u;
+          }
+          ptx::tmem_st32(tmem + lane_addr + kColE, er);
         }
-        ptx::tmem_st32(tmem + lane_addr + kColE, er);
         PH(14);
         if (a.tape) {
           // the tape rows are staged at the head of the state's staging tile, once the previous state's
@@ -611,7 +618,7 @@ gdn_tc_kernel(const __grid_constant__ TcMaps maps, const GdnArgs a, int* status)
 
     // ---- issuing warp: accumulator += E K, then the next item's Gram products; scalar warp: its tables ----
     if (mma) {
-      {
+      if (want_state) {
         ptx::tc_fence_after();
         // k rows 0-15 of both chunks as an MN-major operand: 64-column atoms 4096 bytes apart, 8-step groups 1024 apart
         const uint64_t db = make_desc(ptx::smem_u32(KQ), 4096, 1024);
@@ -632,7 +639,7 @@ gdn_tc_kernel(const __grid_constant__ TcMaps maps, const GdnArgs a, int* status)
       // the store above its V buffer (every other reader of them finished before the barrier above): a whole
       // iteration ahead of their use
       if (nxt + G < n_items) {
-        failed = !ptx::mbar_wait(&bars[4], par) || failed;
+        if (want_state) failed = !ptx::mbar_wait(&bars[4], par) || failed;
         if (lane == 0) ptx::bulk_wait_read_all();
         __syncwarp();
         int b2, hv2;
@@ -663,7 +670,7 @@ gdn_tc_kernel(const __grid_constant__ TcMaps maps, const GdnArgs a, int* status)
     hv_cur = hv_nxt;
   }
   // the last item's state
-  if (!failed && it > 0 && !helper) {
+  if (want_state && !failed && it > 0 && !helper) {
     if (!flush_state((it - 1) & 1, b_prev, hv_prev, (uint32_t)(it - 1) & 1u)) failed = true;
   }
 
@@ -686,6 +693,7 @@ bool gdn_tc_supported(const GdnArgs& a) {
   if ((long long)a.B * a.Hv > (1LL << 24) - 1024) return false;
   if (a.Hv % a.Hk != 0) return false;
   // TMA needs 16-byte aligned bases
+  // state_out may be null (internal callers only): no final state is produced
   const uintptr_t al = (uintptr_t)a.q | (uintptr_t)a.k | (uintptr_t)a.v | (uintptr_t)a.state_in | (uintptr_t)a.state_out |
                        (uintptr_t)a.y | (uintptr_t)a.tape;
   return (al & 15u) == 0;
@@ -715,7 +723,7 @@ int32_t launch_gdn_tc(const GdnArgs& a, cudaStream_t stream) {
                   CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   };
   CUresult r = state_map(&maps.state_in, a.state_in);
-  if (r == CUDA_SUCCESS) r = state_map(&maps.state_out, a.state_out);
+  if (r == CUDA_SUCCESS) r = state_map(&maps.state_out, a.state_out ? a.state_out : a.state_in);   // never used when there is no output
   if (r == CUDA_SUCCESS) r = token_map(&maps.k, a.k, a.Hk, 64, CU_TENSOR_MAP_SWIZZLE_128B);
   if (r == CUDA_SUCCESS) r = token_map(&maps.q, a.q, a.Hk, 64, CU_TENSOR_MAP_SWIZZLE_128B);
   if (r == CUDA_SUCCESS) r = token_map(&maps.v, a.v, a.Hv, 128, CU_TENSOR_MAP_SWIZZLE_NONE);

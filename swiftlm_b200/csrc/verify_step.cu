@@ -41,10 +41,20 @@ extern "C" int32_t dflash_verify_step(const dflash_verify_step_desc* d, void* wo
 
   // 1. verify forward of every gated-delta layer over the whole block, tape recorded
   if (d->gdn_layers > 0) {
-    if (!d->state_verify || !d->tape || !d->state_rolled) return bad_desc("null gated-delta output");
-    if (int32_t st = dflash_gated_delta_tape(d->q, d->k, d->v, d->g, d->beta, d->state, nullptr, nullptr, d->y, d->state_verify,
-                                             d->tape, items, d->T, d->Hk, d->Hv, d->Dk, d->Dv, d->g_is_vector, d->in_dtype, 0, stream))
-      return st;
+    if (!d->tape || !d->state_rolled) return bad_desc("null gated-delta output");
+    if (d->state_verify) {
+      if (int32_t st = dflash_gated_delta_tape(d->q, d->k, d->v, d->g, d->beta, d->state, nullptr, nullptr, d->y, d->state_verify,
+                                               d->tape, items, d->T, d->Hk, d->Hv, d->Dk, d->Dv, d->g_is_vector, d->in_dtype, 0, stream))
+        return st;
+    } else {
+      // The state after all T steps is not wanted: every sequence's result state is the rollback's (state_rolled; for a
+      // fully accepted block the two are the same state).  The tensor-core kernel then writes no state at all.
+      if (!d->q || !d->k || !d->v || !d->g || !d->beta || !d->state || !d->y) return bad_desc("null gated-delta input");
+      GdnArgs a{d->q, d->k, d->v, d->g, d->beta, d->state, nullptr, nullptr, d->y, nullptr, d->tape,
+                items, d->T, d->Hk, d->Hv, d->Dk, d->Dv, d->g_is_vector ? 1 : 0, d->in_dtype, 0, false};
+      if (!gdn_tc_supported(a)) return bad_desc("state_verify may be NULL only for bf16 inputs, Dk = Dv = 128, a scalar gate and T <= 16");
+      if (int32_t st = launch_gdn_tc(a, s)) return st;
+    }
   }
   // 2. block-verify attention of every attention layer
   if (d->attn_layers > 0) {

@@ -270,7 +270,9 @@ typedef struct {
   const void *q, *k, *v, *g, *beta;   /* as dflash_gated_delta_tape */
   const float* state;                 /* committed states [B*gdn_layers,Hv,Dv,Dk] */
   void* y;                            /* [B*gdn_layers,T,Hv,Dv] in_dtype: the verify forward's outputs */
-  float* state_verify;                /* state after all T steps (what a fully accepted block keeps) */
+  float* state_verify;                /* state after all T steps (what a fully accepted block keeps).  May be NULL
+                                         (bf16 inputs, Dk = Dv = 128, scalar gate, T <= 16): then it is not written and
+                                         state_rolled is the result for every sequence */
   float* tape;                        /* [B*gdn_layers,T,Hv,Dv] */
   float* state_rolled;                /* state replayed to replay_len[b] steps; may alias state */
   /* conv windows of the rollback cache (may all be NULL: skipped) */

@@ -40,6 +40,7 @@ class StepConfig:
     conv_kernel: int = 4
     seed: int = 20260330 + 4000
     turbo_kv: bool = True         # False: the same stack over dense bf16 KV
+    keep_state_verify: bool = True   # False: the verify forward writes no final state (state_rolled is the result)
 
 
 class VerifyStep:
@@ -61,7 +62,7 @@ class VerifyStep:
         self.conv = rn(I, c.conv_kernel - 1, c.conv_dim).to(bf)
         self.qkv = rn(I, T, c.conv_dim).to(bf)
         self.y = torch.empty_like(self.v)
-        self.state_verify = torch.empty_like(self.state)
+        self.state_verify = torch.empty_like(self.state) if c.keep_state_verify else None
         self.state_rolled = torch.empty_like(self.state)
         self.tape = torch.empty(I, T, c.Hv, c.Dk, device=device)
         self.conv_out = torch.empty_like(self.conv)
@@ -157,7 +158,8 @@ class VerifyStep:
         """Algorithmic HBM bytes of one step (what a fused implementation would have to move at least)."""
         c = self.cfg
         heads = c.batch * c.Hv
-        gdn = c.gdn_layers * (heads * (131072 + 772 * c.T) + heads * (131072 + 642 * 8))          # verify + mean rollback
+        verify_state = 131072 if c.keep_state_verify else 65536                                 # read, and written if kept
+        gdn = c.gdn_layers * (heads * (verify_state + 772 * c.T) + heads * (131072 + 642 * 8))    # verify + mean rollback
         blocks = c.batch * c.Hkv * c.context * (c.D // 128)
         per_block = (48 + 16 + 4 + 48 + 2) if c.turbo_kv else 2 * 256
         attn = c.attn_layers * (blocks * per_block + 2 * c.batch * c.Hkv * c.T * c.D * 2)

@@ -88,3 +88,18 @@ def test_config4_shape_on_a_sequence_sub_batch():
     from swiftlm_b200.verify_step import StepConfig
     cfg = StepConfig(batch=4)                                 # every other field at the benchmark definition's value
     check_step(cfg, attn_items=[0, 17, 47])
+
+
+def test_step_without_the_verify_forwards_final_state():
+    """state_verify = NULL: the forward writes no state; outputs, tape, rolled-back states and acceptance are the same
+    bits as with it."""
+    from swiftlm_b200.verify_step import StepConfig, VerifyStep
+    kw = dict(batch=3, gdn_layers=3, attn_layers=2, Hk=2, Hv=4, Hq=16, Hkv=2, D=256, context=384, vocab=4096, conv_dim=64)
+    dev = torch.device("cuda", 0)
+    a = VerifyStep(StepConfig(**kw), dev).run()
+    b = VerifyStep(StepConfig(keep_state_verify=False, **kw), dev).run()
+    torch.cuda.synchronize()
+    assert b["state_verify"] is None
+    for name in ("y", "tape", "states", "convs", "accept", "next_token", "replay_len", "attn_out"):
+        assert torch.equal(a[name], b[name]), name
+
