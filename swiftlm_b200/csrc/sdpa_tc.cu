@@ -366,11 +366,14 @@ __device__ __forceinline__ void unpack_centroid_row(uint8_t* chunk, int row, con
   for (int piece = 0; piece < 8; ++piece) {      // 8 indices = 24 bits -> 8 values = 16 bytes
     const int bit = piece * 24, word = bit >> 5, off = bit & 31;
     const uint32_t x = off ? __funnelshift_r(w[word], w[word + 1], off) : w[word];
+    // the eight 3-bit indices spread to one per nibble (a byte permute's selector spacing) in three halving steps
+    const uint32_t s12 = (x & 0x00000FFFu) | ((x << 4) & 0x0FFF0000u);
+    const uint32_t s6 = (s12 & 0x003F003Fu) | ((s12 << 2) & 0x3F003F00u);
+    const uint32_t s3 = (s6 & 0x07070707u) | ((s6 << 1) & 0x70707070u);
     uint32_t o[4];
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
-      const uint32_t y = x >> (12 * h);
-      const uint32_t sel = (y & 0x7u) | ((y << 1) & 0x70u) | ((y << 2) & 0x700u) | ((y << 3) & 0x7000u);
+      const uint32_t sel = h ? (s3 >> 16) : s3;   // a permute reads the low 16 bits of its selector
       const uint32_t lo4 = prmt(lo_a, lo_b, sel), hi4 = prmt(hi_a, hi_b, sel);
       o[2 * h] = prmt(lo4, hi4, 0x5140);
       o[2 * h + 1] = prmt(lo4, hi4, 0x7362);
