@@ -24,24 +24,29 @@
 // fp32: S_T = G_T * S0 + (E K) with S0 read from the fp32 tile, and E is split exactly (24 bits).
 // For a sequence with no running step the output state equals the input bit for bit.
 //
-// One persistent CTA per SM: eight compute warps, a scalar warp and an issuing warp.  Per work
-// item (sequence, v-head), with the phases of neighbouring items interleaved:
-//   load    issuing warp, TMA: the fp32 state tile (four 128-byte-swizzled boxes) into one of two landing tiles,
+// One persistent CTA per SM: eight compute warps, a scalar warp, a warp that issues the tensor-core products and a
+// warp that issues the TMA loads.  Per work item (sequence, v-head), with the phases of neighbouring items interleaved:
+//   load    loading warp, TMA: the fp32 state tile (four 128-byte-swizzled boxes) into one of two landing tiles,
 //           issued two items ahead, as soon as the split has read the tile's previous contents: a state load is
 //           in flight at all times.  K, Q rows of the block (swizzled, they are tensor-core operands as they
 //           land) and V rows on a barrier of their own, also two items ahead
-//   split   compute warps, two threads per state row: S0 -> two bf16 operand tiles in the tensor
-//           cores' K-major layout, and G_T * S0 in fp32 -> the item's accumulator in tensor memory
+//   split   compute warps, two threads per state row: S0 -> two bf16 terms written to tensor memory, where they are
+//           the A operand of TS-form products (nothing of the split passes through shared memory), and
+//           G_T * S0 in fp32 -> the item's accumulator in tensor memory
 //   mma     issuing warp: [S0 K^T | S0 Q^T] into tensor memory (first operand chunk while the split works
-//           on the second); behind each half of the products the compute warps move the PREVIOUS item's
-//           finished state from tensor memory into the operand tiles' memory, which a TMA store sends out
-//   solve   two threads per state row, both from r: warps 0-3 form delta = N r, write the tape and put
-//           E into tensor memory as the A operand of the last product; warps 4-7 form y = G (S0 q) + Z r
+//           on the second); under the products the compute warps move the PREVIOUS item's finished state from
+//           tensor memory to a staging tile, which a TMA store sends out
+//   solve   two threads per state row, both from r: warps 0-3 form delta = N r, stage the tape rows and put
+//           E into tensor memory as the A operand of the last product; warps 4-7 form y = G (S0 q) + Z r and
+//           stage it over the item's V rows.  Outputs and tape leave by TMA stores after the barrier that ends the
+//           solve (plain global stores from the SM are throttled while TMA traffic saturates the memory system)
 //   mma     issuing warp: the accumulator += E K, then the next item's Gram products
 //   tables  scalar warp: gates and betas of the item after the next fetched into registers, those of
 //           the next item published; the next item's Gram rows out of tensor memory, scaled by the
 //           gate products (and beta) into C and Ckq, then N (lanes 0-15, a row each) and Z (lanes
 //           16-31, a row each) by one right-looking substitution over shuffles into the other table slot
+// When no final state is wanted (state_out null: the verify step, whose result state is the rollback's) the
+// accumulator, the E K product and the state's way out are skipped.
 // Hand-offs that only one side waits for use named barriers (bar.arrive on the other side).
 // Every wait is bounded; a wait that gives up sets the device status word and the CTA leaves.
 //
