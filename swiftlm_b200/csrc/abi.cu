@@ -107,7 +107,7 @@ size_t align256(size_t x) { return (x + 255) / 256 * 256; }
 // The fused attention over compressed KV takes: a cold history of whole 128-key tiles, uniform lengths, no additive mask,
 // a positive scale.
 bool turbo_fused_applies(const dflash_turbo_kv* t, const int32_t* kv_len_per_seq, const void* mask, float scale) {
-  return t->n_cold > 0 && t->n_cold % 128 == 0 && !kv_len_per_seq && !mask && scale > 0.f;
+  return t->n_cold > 0 && t->n_cold % 128 == 0 && !kv_len_per_seq && !mask && scale > 0.f && sdpa_tc_turbo_available();
 }
 // rotated queries (two tiles) + rotated-domain output + the hot window in the rotated domain + the split-KV partials
 size_t turbo_fused_workspace_bytes(int B, int Hq, int Hkv, int D, int n_hot) {

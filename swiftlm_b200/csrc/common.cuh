@@ -136,6 +136,7 @@ struct TurboKvArgs {
   const void* q2;                     // Rq^T q, laid out as q
   int n_cold, n_hot;
 };
+bool sdpa_tc_turbo_available();   // the fused compressed-KV kernel's register pool matches this build
 int32_t launch_sdpa_tc_turbo(const SdpaArgs& a, const TurboKvArgs& t, cudaStream_t stream);
 size_t sdpa_tc_scratch_bytes(int D);
 int32_t launch_turbo_rotate_inputs(const void* q, void* q1, void* q2, long long q_blocks, const void* k_hot, void* k_rot,

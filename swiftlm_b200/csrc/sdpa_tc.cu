@@ -60,9 +60,22 @@ constexpr int kBlockN = 128;            // keys per tile
 constexpr int kRowsM = 128;             // query rows per unit tile
 constexpr int kChunkBytes = 128 * 128;  // one TMA box: 128 rows x 64 16-bit elements
 constexpr int kThreads = 320;          // TMA warp, MMA warp, 8 softmax warps
-constexpr int kUnpackThreads = 256;    // compressed KV only: 8 more warps expand packed bytes into the rings: four the keys, four the values
+constexpr int kUnpackThreads = 384;    // compressed KV only: 12 more warps expand packed bytes into the rings: eight the keys (two
+                                       // threads per key row), four the values
 constexpr int kPvThreads = 32;         // one more warp whose lane 0 issues the P V products
-template <bool TURBO> struct ThreadsOf { static constexpr int value = kThreads + kPvThreads + (TURBO ? kUnpackThreads : 0); };
+// Dense: warp 0 TMA, 1 Q K^T issuer, 2-9 softmax, 10 P V issuer.  Compressed KV: 24 warps laid out by warpgroup so that
+// registers can move between the roles (setmaxnreg works on whole warpgroups): warps 0-7 softmax, 8-15 key unpack,
+// 16-19 value unpack, 20 TMA, 21 Q K^T issuer, 22 P V issuer, 23 idle.  The code below speaks of roles by the dense
+// numbering.
+template <bool TURBO> struct ThreadsOf { static constexpr int value = TURBO ? 768 : kThreads + kPvThreads; };
+constexpr int kTurboIdleRole = 23;
+// Registers per thread of the compressed-KV kernel: 80 at launch; the softmax warps take 112, the unpack warps and the
+// last warpgroup keep 64 (256 x 112 + 384 x 64 + 128 x 64 = the launch's 61 440).
+constexpr int kTurboRegsLaunch = 80, kTurboRegsSoftmax = 112, kTurboRegsUnpack = 64, kTurboRegsHelper = 64;
+static_assert(256 * kTurboRegsSoftmax + 384 * kTurboRegsUnpack + 128 * kTurboRegsHelper <= 768 * kTurboRegsLaunch, "register pool");
+__device__ __forceinline__ int turbo_role(int pw) {   // physical warp -> the dense numbering (11-22 unpack, 23 idle)
+  return pw < 8 ? pw + 2 : (pw < 20 ? pw + 3 : (pw == 20 ? 0 : (pw == 21 ? 1 : (pw == 22 ? 10 : kTurboIdleRole))));
+}
 constexpr float kRescaleThreshold = 8.f;   // in log2 units
 constexpr int kFusedMax = 4;               // a unit cut into at most this many ranges is merged by its last finisher
 
@@ -353,18 +366,27 @@ template <> __device__ __forceinline__ uint32_t pack2_rn<__half>(float a, float 
 // 64 three-bit centroid indices (24 bytes at `src`, 8-byte aligned) -> 64 values scale * centroid in the attention
 // dtype.  The eight scaled centroids are split into a table of their low bytes and one of their high bytes; four
 // indices at a time select from both with byte permutes.
-template <typename InT>
-__device__ __forceinline__ void unpack_centroid_row(uint8_t* chunk, int row, const uint8_t* src, float scale) {
-  const uint2 a = *reinterpret_cast<const uint2*>(src), b = *reinterpret_cast<const uint2*>(src + 8), c = *reinterpret_cast<const uint2*>(src + 16);
-  const uint32_t w[7] = {a.x, a.y, b.x, b.y, c.x, c.y, 0u};
+// `kPieces` = 8: the whole row; 4: thread `hsel` (0 or 1) of a row's pair writes pieces 4 hsel .. 4 hsel + 3 (the 32
+// indices in bytes 12 hsel .. 12 hsel + 11).
+template <typename InT, int kPieces = 8>
+__device__ __forceinline__ void unpack_centroid_row(uint8_t* chunk, int row, const uint8_t* src, float scale, int hsel = 0) {
+  uint32_t w[7];
+  if (kPieces == 8) {
+    const uint2 a = *reinterpret_cast<const uint2*>(src), b = *reinterpret_cast<const uint2*>(src + 8), c = *reinterpret_cast<const uint2*>(src + 16);
+    w[0] = a.x; w[1] = a.y; w[2] = b.x; w[3] = b.y; w[4] = c.x; w[5] = c.y; w[6] = 0u;
+  } else {
+    const uint32_t* s32 = reinterpret_cast<const uint32_t*>(src + 12 * hsel);
+    w[0] = s32[0]; w[1] = s32[1]; w[2] = s32[2]; w[3] = 0u; w[4] = w[5] = w[6] = 0u;
+  }
   const uint32_t p0 = pack2_rn<InT>(TURBO_C3[0] * scale, TURBO_C3[1] * scale), p1 = pack2_rn<InT>(TURBO_C3[2] * scale, TURBO_C3[3] * scale);
   const uint32_t p2 = pack2_rn<InT>(TURBO_C3[4] * scale, TURBO_C3[5] * scale), p3 = pack2_rn<InT>(TURBO_C3[6] * scale, TURBO_C3[7] * scale);
   const uint32_t lo_a = prmt(p0, p1, 0x6420), lo_b = prmt(p2, p3, 0x6420), hi_a = prmt(p0, p1, 0x7531), hi_b = prmt(p2, p3, 0x7531);
   uint8_t* dst = chunk + row * 128;
   const int sw = row & 7;
 #pragma unroll
-  for (int piece = 0; piece < 8; ++piece) {      // 8 indices = 24 bits -> 8 values = 16 bytes
-    const int bit = piece * 24, word = bit >> 5, off = bit & 31;
+  for (int pp = 0; pp < kPieces; ++pp) {         // 8 indices = 24 bits -> 8 values = 16 bytes
+    const int piece = (kPieces == 8 ? 0 : 4 * hsel) + pp;
+    const int bit = pp * 24, word = bit >> 5, off = bit & 31;
     const uint32_t x = off ? __funnelshift_r(w[word], w[word + 1], off) : w[word];
     // the eight 3-bit indices spread to one per nibble (a byte permute's selector spacing) in three halving steps
     const uint32_t s12 = (x & 0x00000FFFu) | ((x << 4) & 0x0FFF0000u);
@@ -382,16 +404,17 @@ __device__ __forceinline__ void unpack_centroid_row(uint8_t* chunk, int row, con
   }
 }
 // 64 sign bits (8 bytes at `src`) -> 64 values +-mag: bit set = +mag (tests/test_turbo_quant.cpp:97 of the SwiftLM tree)
+// Thread `hsel` of a row's pair writes pieces 4 hsel .. 4 hsel + 3 (the 32 sign bits of word hsel).
 template <typename InT>
-__device__ __forceinline__ void unpack_sign_row(uint8_t* chunk, int row, const uint8_t* src, float mag) {
-  const uint2 a = *reinterpret_cast<const uint2*>(src);
-  const uint32_t nw[2] = {~a.x, ~a.y};          // set bit = negative
+__device__ __forceinline__ void unpack_sign_half_row(uint8_t* chunk, int row, const uint8_t* src, float mag, int hsel) {
+  const uint32_t nw = ~reinterpret_cast<const uint32_t*>(src)[hsel];   // set bit = negative
   const uint32_t m2 = pack2_rn<InT>(mag, mag);
   uint8_t* dst = chunk + row * 128;
   const int sw = row & 7;
 #pragma unroll
-  for (int piece = 0; piece < 8; ++piece) {      // 8 bits -> 8 values = 16 bytes
-    const uint32_t t = nw[piece >> 2] >> ((piece & 3) * 8);
+  for (int pp = 0; pp < 4; ++pp) {               // 8 bits -> 8 values = 16 bytes
+    const int piece = 4 * hsel + pp;
+    const uint32_t t = nw >> (pp * 8);
     uint32_t o[4];
 #pragma unroll
     for (int k = 0; k < 4; ++k) o[k] = m2 ^ ((t << (15 - 2 * k)) & 0x8000u) ^ ((t << (30 - 2 * k)) & 0x80000000u);
@@ -425,7 +448,8 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
   volatile int* abort_flag = reinterpret_cast<volatile int*>(sm + SL::misc + 4);
   int* range_info = reinterpret_cast<int*>(sm + SL::misc + 8);   // unit0, tile0
 
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int pw = threadIdx.x >> 5, lane = threadIdx.x & 31;   // physical warp
+  const int warp = TURBO ? turbo_role(pw) : pw;                // role, in the dense numbering
   const SdpaArgs& a = p.a;
   if (threadIdx.x == 0) TR_STAMP(0);
   TR_DECL();
@@ -447,7 +471,7 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
   long long begin, end;
   cta_range(p, total, blockIdx.x, begin, end);
 
-  if (threadIdx.x == 0) {
+  if (warp == 0 && lane == 0) {
     ptx::prefetch_tensormap(&map_q);
     if (TURBO) ptx::prefetch_tensormap(&map_q2);
     ptx::prefetch_tensormap(&map_k);
@@ -457,8 +481,10 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       // compressed KV: a ring stage is filled by the four warps of one unpack group (one arrival each; for a hot tile
       // the group's first lane issues a TMA load and its arrival carries the byte count); a landing area is released
       // by the four warps of the group that reads it
-      const bool four = TURBO && ((i >= SL::b_kv_full && i < SL::b_kv_full + kStages) || (i >= SL::b_stg_empty && i < SL::b_stg_empty + 3));
-      ptx::mbar_init(&bars[i], i == SL::b_peer_data ? 256 : (eight ? 8 : (four ? 4 : 1)));
+      // (the keys' group has eight warps, the values' four)
+      const bool k_side = TURBO && ((i >= SL::b_kv_full && i < SL::b_kv_full + SL::kStagesK) || i == SL::b_stg_empty || i == SL::b_stg_empty + 1);
+      const bool v_side = TURBO && ((i >= SL::b_kv_full + SL::kStagesK && i < SL::b_kv_full + kStages) || i == SL::b_stg_empty + 2);
+      ptx::mbar_init(&bars[i], i == SL::b_peer_data ? 256 : ((eight || k_side) ? 8 : (v_side ? 4 : 1)));
     }
     *abort_flag = 0;
     reinterpret_cast<volatile uint32_t*>(sm + SL::misc)[4] = 0;   // group counter
@@ -510,6 +536,10 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
   const int unit0 = range_info[0], tile0 = range_info[1];
   if (threadIdx.x == 0) TR_STAMP(1);
 
+  // Compressed KV: each warpgroup sets its register budget as the first thing in its own branch - code that paths
+  // with different budgets share is compiled for the smallest of them, so the branches meet again only at the very end.
+  if (warp == 0 || warp == 1 || warp == kThreads / 32 || warp == kTurboIdleRole) {
+  if constexpr (TURBO) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kTurboRegsHelper));
   if (warp == 0) {
     // =================================== TMA producer ===================================
     if (lane == 0 && begin < end) {
@@ -774,18 +804,21 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         ++seg_idx;
       }
     }
-  } else if (TURBO && warp > kThreads / 32) {
+  }
+  } else if (TURBO && warp > kThreads / 32 && warp < kThreads / 32 + 1 + kUnpackThreads / 32) {
+    if constexpr (TURBO) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kTurboRegsUnpack));
     // ====================================== unpack =======================================
-    // Compressed KV: two groups of four warps, one for the keys, one for the values; thread t of a group owns key row
-    // t of every operand chunk its group makes.  Per cold tile a group
+    // Compressed KV: a group of eight warps for the keys (two threads per key row, half a row of every chunk each: the
+    // keys' eight chunks per tile are the longest chain in the kernel) and a group of four for the values (one thread
+    // per row).  Per cold tile a group
     // expands, from the landing areas, the key's centroid indices into D / 64 chunks scaled by the key block's norm,
     // its residual sign bits into D / 64 chunks of +-(norm * QJL_C / 128 * rnorm), and (one tile behind, as the MMA
     // warp consumes them) the value's centroid indices scaled by the value block's norm - the operands the dense
     // path gets by TMA, in the same swizzled layout, so that no decoded key or value ever exists in global memory.
     if (begin < end) {
-      const int u = (int)threadIdx.x - kThreads - kPvThreads;
-      const int t = u & 127;                                    // key row of a chunk
-      const bool v_group = u >= 128;                            // warps 0-3 expand keys (K ring), warps 4-7 values (V ring)
+      const int u = (int)threadIdx.x - 8 * 32;                  // physical warps 8-19
+      const int t = u & 127, hsel = (u >> 7) & 1;               // key row of a chunk; which half of the row (key group)
+      const bool v_group = u >= 256;                            // warps 0-7 expand keys (K ring), warps 8-11 values (V ring)
       constexpr int NB = D / 128;
       constexpr int kSK = SL::kStagesK, kSV = SL::kStagesV;
       SegmentIter it(p, begin, end, unit0, tile0);
@@ -826,7 +859,7 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         for (int c = 0; c < kQChunks; ++c) {
           uint32_t stage;
           if (!ring_slot(true, stage)) return false;
-          unpack_centroid_row<InT>(sm + SL::ring + stage * kChunkBytes, t, sm + SL::stg_a + (t * NB + (c >> 1)) * 48 + (c & 1) * 24, nrm[c >> 1]);
+          unpack_centroid_row<InT, 4>(sm + SL::ring + stage * kChunkBytes, t, sm + SL::stg_a + (t * NB + (c >> 1)) * 48 + (c & 1) * 24, nrm[c >> 1], hsel);
           publish(true, stage);
         }
         release(0);
@@ -838,7 +871,7 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         for (int c = 0; c < kQChunks; ++c) {
           uint32_t stage;
           if (!ring_slot(true, stage)) return false;
-          unpack_sign_row<InT>(sm + SL::ring + stage * kChunkBytes, t, sm + SL::stg_b + (t * NB + (c >> 1)) * 16 + (c & 1) * 8, mag[c >> 1]);
+          unpack_sign_half_row<InT>(sm + SL::ring + stage * kChunkBytes, t, sm + SL::stg_b + (t * NB + (c >> 1)) * 16 + (c & 1) * 8, mag[c >> 1], hsel);
           publish(true, stage);
         }
         release(1);
@@ -867,7 +900,7 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
           if (!ring_slot(is_k, stage)) return false;
           if (lane == 0) {
             void* bar = &bars[SL::b_kv_full + stage];
-            if (t == 0) {
+            if (t == 0 && hsel == 0) {   // the group's first lane
               ptx::mbar_arrive_expect_tx(bar, kChunkBytes);
               ptx::tma_load_4d(sm + SL::ring + stage * kChunkBytes, is_k ? &map_k : &map_v, c * 64, (tile - p.tiles_cold) * kBlockN, s.kvh, s.b, bar);
             } else {
@@ -893,13 +926,14 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         }
       }
     }
-  } else {
+  } else if (warp >= 2 && warp < 2 + 8) {
+    if constexpr (TURBO) asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kTurboRegsSoftmax));
     // ====================================== softmax ======================================
     // Two threads per query row: warps 2-5 take key columns 0-63 of every tile (and the lower
     // half of O's columns), warps 6-9 columns 64-127 (upper half).  Both warps of a pair touch
     // the same tensor-memory lane quarter.  The two partial row maxima of a tile (and the two
     // partial sums at the end of a segment) are exchanged through shared memory.
-    const int wq = warp & 3;                       // tensor-memory lane quarter this warp may touch
+    const int wq = pw & 3;                         // tensor-memory lane quarter this (physical) warp may touch
     const int half = (warp - 2) >> 2;              // which 64 key columns / which half of O
     const int row = wq * 32 + lane;                // query row of the unit tile = tensor-memory lane
     const uint32_t lane_addr = (uint32_t)(wq * 32) << 16;
@@ -1675,6 +1709,21 @@ static int32_t launch_dims(const SdpaArgs& a, cudaStream_t stream) {
 
 // Attention over KV in the TurboQuant 3-bit format without decoding it to global memory: a.q = Q1 = R q, t.q2 = Rq^T q,
 // a.k / a.v = the hot window in the rotated domain (or null), a.out = the output in the rotated domain.
+// The compressed-KV kernel moves registers between its warpgroups; that arithmetic holds only if the launch gives every
+// thread kTurboRegsLaunch registers (a request for more than the pool holds would wait forever).  Checked once; if it
+// does not hold, the caller takes the route through a decoded copy.
+template <typename InT, int D>
+static bool turbo_pool_ok_one() {
+  cudaFuncAttributes attr;
+  if (cudaFuncGetAttributes(&attr, sdpa_tc_kernel<InT, D, false, true>) != cudaSuccess) { (void)cudaGetLastError(); return false; }
+  return attr.numRegs > kTurboRegsLaunch - 8 && attr.numRegs <= kTurboRegsLaunch;
+}
+bool sdpa_tc_turbo_available() {
+  static const bool ok = turbo_pool_ok_one<__nv_bfloat16, 256>() && turbo_pool_ok_one<__nv_bfloat16, 128>() &&
+                         turbo_pool_ok_one<__half, 256>() && turbo_pool_ok_one<__half, 128>();
+  return ok;
+}
+
 int32_t launch_sdpa_tc_turbo(const SdpaArgs& a, const TurboKvArgs& t, cudaStream_t stream) {
   if (a.dtype == DFLASH_BF16)
     return a.D == 256 ? launch_typed<__nv_bfloat16, 256, false, true>(a, &t, stream) : launch_typed<__nv_bfloat16, 128, false, true>(a, &t, stream);
