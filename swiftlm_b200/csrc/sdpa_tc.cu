@@ -1372,10 +1372,10 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
   // No CTA of a pair may leave while its partner can still write into its shared memory.  Every
   // wait above is bounded, so both always get here.
   if (p.pair) cluster_sync_all();
-  if (threadIdx.x == 0) TR_FLUSH(16, 16);
-  if (threadIdx.x == 32) { TR_FLUSH(17, 17); TR_FLUSH(22, 22); }
-  if (threadIdx.x == kThreads) { TR_FLUSH(18, 19); TR_FLUSH(23, 23); }
-  if (threadIdx.x == 64) TR_FLUSH(20, 21);
+  if (warp == 0 && lane == 0) TR_FLUSH(16, 16);
+  if (warp == 1 && lane == 0) { TR_FLUSH(17, 17); TR_FLUSH(22, 22); }
+  if (warp == kThreads / 32 && lane == 0) { TR_FLUSH(18, 19); TR_FLUSH(23, 23); }
+  if (warp == 2 && lane == 0) TR_FLUSH(20, 21);
   ptx::tc_fence_before();
   __syncthreads();
   if (threadIdx.x == 0) TR_STAMP(12);
