@@ -49,6 +49,26 @@ class _Staging:
 _pipes = {}
 
 
+def _chunk_schedule(B: int, chunk: int):
+    """Row ranges of the pipeline's chunks: full chunks in the middle, a quarter and a half chunk at either end.  The
+    first copy in and the last copy out overlap with nothing, so they are kept short; small chunks everywhere would
+    pay the per-copy overheads on the whole batch."""
+    edges = [chunk // 4, chunk // 2] if chunk >= 8 and B >= 4 * chunk else []
+    head = [e for e in edges if e > 0]
+    tail = head[::-1]
+    sizes, left = list(head), B - sum(head) - sum(tail)
+    while left > 0:
+        sizes.append(min(chunk, left))
+        left -= sizes[-1]
+    sizes += tail
+    out, lo = [], 0
+    for n in sizes:
+        out.append((lo, lo + n))
+        lo += n
+    assert lo == B
+    return out
+
+
 def gated_delta_from_host(hx: Dict[str, torch.Tensor], hout: Dict[str, torch.Tensor], chunk: int = 144) -> Tuple[int, int]:
     """Gated-delta replay with every tensor in pinned host memory.
 
@@ -72,8 +92,7 @@ def gated_delta_from_host(hx: Dict[str, torch.Tensor], hout: Dict[str, torch.Ten
     for s in (s_in, s_run, s_out):
         s.wait_event(start)
     h2d = d2h = 0
-    for ci, lo in enumerate(range(0, B, chunk)):
-        hi = min(B, lo + chunk)
+    for ci, (lo, hi) in enumerate(_chunk_schedule(B, chunk)):
         rows = hi - lo
         st = pipe["stage"][ci % 2]
         with torch.cuda.stream(s_in):

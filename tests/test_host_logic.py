@@ -124,3 +124,11 @@ def test_oracle_trimmable_cache_follows_the_restore_rule():
     assert ref.offset(0) == 6 and ref.offset(1) == 25
     np.testing.assert_array_equal(ref.k[0][0, 5], blk[0, 0, 0])       # the new block starts right behind the kept prefix
     np.testing.assert_array_equal(ref.v[1][0, 24], -blk[1, 0, 8])
+
+
+def test_chunk_schedule_covers_the_batch():
+    from swiftlm_b200.host_api import _chunk_schedule
+    for B, chunk in ((2304, 144), (100, 144), (576, 144), (7, 3), (1, 1), (33, 8)):
+        r = _chunk_schedule(B, chunk)
+        assert r[0][0] == 0 and r[-1][1] == B and all(a[1] == b[0] for a, b in zip(r, r[1:]))
+        assert all(0 < hi - lo <= chunk for lo, hi in r)
