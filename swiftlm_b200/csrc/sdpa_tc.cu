@@ -448,9 +448,18 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
   volatile int* abort_flag = reinterpret_cast<volatile int*>(sm + SL::misc + 4);
   int* range_info = reinterpret_cast<int*>(sm + SL::misc + 8);   // unit0, tile0
 
+  // Back-to-back calls (the attention of one layer after another): a launch made with programmatic stream
+  // serialization may bring its CTAs onto SMs as the previous grid's CTAs leave, so that its set-up (barriers, tensor
+  // memory, tensor maps) runs beside the previous grid's tail.  Nothing of the previous grid's results, of this call's
+  // inputs or of the workspace is touched before griddepcontrol.wait, which returns when every earlier grid has
+  // completed and its memory is visible: with per-sequence lengths (read right below) every thread waits here; else
+  // the one thread that sets the CTA up waits before its first global store, and every other thread meets it at the
+  // barrier that ends the set-up.  Without the launch attribute both instructions do nothing.
   const int pw = threadIdx.x >> 5, lane = threadIdx.x & 31;   // physical warp
   const int warp = TURBO ? turbo_role(pw) : pw;                // role, in the dense numbering
   const SdpaArgs& a = p.a;
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  if (a.kv_len) asm volatile("griddepcontrol.wait;" ::: "memory");
   if (threadIdx.x == 0) TR_STAMP(0);
   TR_DECL();
 
@@ -512,6 +521,7 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     range_info[0] = unit;
     range_info[1] = tile;
     ptx::fence_mbar_init();
+    if (!a.kv_len) asm volatile("griddepcontrol.wait;" ::: "memory");
     // slot table: rewritten below by the softmax warps for the slots this CTA uses
     p.slot_unit[2 * blockIdx.x] = -1;
     p.slot_unit[2 * blockIdx.x + 1] = -1;
@@ -1652,16 +1662,28 @@ int32_t launch_typed(const SdpaArgs& a, const TurboKvArgs* turbo, cudaStream_t s
     cfg.blockDim = dim3(kNumThreads);
     cfg.dynamicSmemBytes = SL::alloc;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 2;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;   // see the top of the kernel
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 2;
+    DFLASH_CUDA_CHECK(cudaLaunchKernelEx(&cfg, kernel, mq, mq2, mk, mv, p));
+  } else {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3(kNumThreads);
+    cfg.dynamicSmemBytes = SL::alloc;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;   // see the top of the kernel
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     DFLASH_CUDA_CHECK(cudaLaunchKernelEx(&cfg, kernel, mq, mq2, mk, mv, p));
-  } else {
-    kernel<<<(unsigned)grid, kNumThreads, SL::alloc, stream>>>(mq, mq2, mk, mv, p);
   }
   DFLASH_LAUNCH_CHECK();
   count_launch();
