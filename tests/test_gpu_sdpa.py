@@ -257,3 +257,31 @@ def test_long_context_paged_matches_oracle_and_dense():
     want = CO.verify_sdpa(x["q"], x["k"], x["v"], float(x["scale"]))
     assert np.abs(dense.float().cpu().numpy() - want).max() < ATOL
     assert np.abs(paged.float().cpu().numpy() - want).max() < ATOL
+
+
+@pytest.mark.parametrize("shape", [(8, 16, 2, 256, 2064), (1, 16, 2, 256, 20016), (40, 16, 2, 256, 528), (3, 32, 8, 128, 4112)],
+                         ids=["cuts", "stream_k_merge", "many_units", "d128"])
+def test_back_to_back_calls_share_the_workspace(shape):
+    """Calls issued one after another with no synchronisation in between (each may start its set-up beside the previous
+    call's tail) through the one cached workspace give the bits of calls made one at a time."""
+    B, Hq, Hkv, D, N = shape
+    g = torch.Generator(device="cuda").manual_seed(sum(shape))
+    sets = []
+    for _ in range(3):
+        q = torch.randn(B, Hq, 16, D, device="cuda", generator=g).bfloat16()
+        k = torch.randn(B, Hkv, N, D, device="cuda", generator=g).bfloat16()
+        v = torch.randn(B, Hkv, N, D, device="cuda", generator=g).bfloat16()
+        sets.append((q, k, v))
+    scale = 1.0 / float(D) ** 0.5
+    alone = []
+    for q, k, v in sets:
+        alone.append(K().batched_sdpa_2pass(q, k, v, scale).clone())
+        torch.cuda.synchronize()
+    outs = [torch.empty_like(sets[0][0]) for _ in range(9)]
+    for i in range(9):
+        q, k, v = sets[i % 3]
+        K().batched_sdpa_2pass(q, k, v, scale, out=outs[i])
+    torch.cuda.synchronize()
+    K().device_status()
+    for i in range(9):
+        assert torch.equal(outs[i], alone[i % 3]), i
