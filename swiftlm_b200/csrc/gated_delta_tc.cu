@@ -334,23 +334,26 @@ gdn_tc_kernel(const __grid_constant__ TcMaps maps, const GdnArgs a, int* status)
   uint32_t gram_uses = 1;                             // phases of the Gram barrier consumed so far (helper warp)
 
   // previous item's finished state: tensor memory -> staging tile -> TMA store (compute warps)
+  // The staging tile is free when this starts: the lanes that issued its previous store waited for that store's read
+  // just before the barrier that ended the previous iteration.  With a tape, the previous item's tape rows left from
+  // the head of the tile by a store issued AFTER that barrier: it is waited for here, and everyone is told.
   auto flush_state = [&](int dbuf, int b, int hv, uint32_t ek_parity) -> bool {
-    if (tid < 4) ptx::bulk_wait_read_all();           // the staging tile's previous store (this lane's box) has been read
-    PH(12);
+    if (a.tape && tid < 4) ptx::bulk_wait_read_all();
     bool ok = ptx::mbar_wait(&bars[4], ek_parity);
     ptx::tc_fence_after();
-    PH(13);
-    asm volatile("bar.sync 1, %0;" ::"n"(kComputeThreads) : "memory");
+    if (a.tape) asm volatile("bar.sync 1, %0;" ::"n"(kComputeThreads) : "memory");
     PH(10);
-#pragma unroll
-    for (int bb = 0; bb < 2; ++bb) {
-      uint32_t dr[32];
-      ptx::tmem_ld32(tmem + lane_addr + kColD + 128 * dbuf + 64 * half + 32 * bb, dr);
+    {   // both 32-column reads in flight before either is waited for
+      uint32_t dr[2][32];
+      ptx::tmem_ld32(tmem + lane_addr + kColD + 128 * dbuf + 64 * half, dr[0]);
+      ptx::tmem_ld32(tmem + lane_addr + kColD + 128 * dbuf + 64 * half + 32, dr[1]);
       ptx::tmem_ld_wait();
 #pragma unroll
-      for (int g = 0; g < 8; ++g)
-        *reinterpret_cast<uint4*>(sm + kY + (2 * half + bb) * 16384 + row * 128 + ((g ^ (row & 7)) << 4)) =
-            make_uint4(dr[4 * g], dr[4 * g + 1], dr[4 * g + 2], dr[4 * g + 3]);
+      for (int bb = 0; bb < 2; ++bb)
+#pragma unroll
+        for (int g = 0; g < 8; ++g)
+          *reinterpret_cast<uint4*>(sm + kY + (2 * half + bb) * 16384 + row * 128 + ((g ^ (row & 7)) << 4)) =
+              make_uint4(dr[bb][4 * g], dr[bb][4 * g + 1], dr[bb][4 * g + 2], dr[bb][4 * g + 3]);
     }
     ptx::fence_proxy_async();
     ptx::tc_fence_before();
@@ -618,6 +621,9 @@ gdn_tc_kernel(const __grid_constant__ TcMaps maps, const GdnArgs a, int* status)
       }
     }
     PH(5);
+    // the previous state's store, issued in this iteration, has read the staging tile by now; after the barrier every
+    // thread may write there again (one barrier fewer at the start of the next flush)
+    if (tid < 4) ptx::bulk_wait_read_all();
     if (__syncthreads_or(failed)) { failed = true; break; }
     PH(6);
 
