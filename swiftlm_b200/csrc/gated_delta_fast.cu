@@ -15,9 +15,12 @@
 //   * the state is carried as S = G * U with a running scalar G (product of the gates so far):
 //       kv = G <U_row, k>,  delta = (v - kv) beta,  U_row += (delta / G) k,  y = G <U_row, q>
 //     i.e. 3 packed fp32x2 fused multiply-adds per state element per step instead of 4; G is
-//     folded back into U when it gets small (or a gate is exactly 0); with a per-channel gate
-//     (a [Dk] vector per step, kept in its input type in shared memory and widened as it is read)
-//     the state is decayed column by column in the reference's own order, 4 operations per element;
+//     folded back into U when it gets small (or a gate is exactly 0);
+//   * with a per-channel gate (a [Dk] vector per step) the forward does the same with a vector of running products:
+//     S = U diag(G_t), the products folded into the per-token vectors once per item (G_t k_t, k_t / G_t, G_t q_t), so the
+//     recurrence keeps its 3 operations per element; an item whose product leaves [1e-12, 1e12] in any channel decays
+//     its state column by column in the reference's own order instead (4 operations), as the replay always does, with
+//     the gate rows kept in their input type in shared memory and widened as they are read;
 //   * the new state leaves as full 128-byte lines; y and the tape are staged per warp and written
 //     as 16-byte pieces.
 // Work items are ordered so that consecutive items come from different sequences: accepted
@@ -46,20 +49,27 @@ struct Layout {
   static constexpr uint32_t raw_k = kStateBytes;
   static constexpr uint32_t raw_q = raw_k + kTmax * in_row;                       // forward only
   static constexpr uint32_t raw_v = REPLAY ? raw_q : raw_q + kTmax * in_row;      // v (InT) or recorded delta (fp32)
-  // per-channel gate only: two buffers, because the gate is read during the recurrence while the next item's inputs land
+  // per-channel gate only.  The replay reads the gate during the recurrence while the next item's inputs land: two
+  // buffers.  The forward folds it into k and q before the recurrence starts: one.
+  static constexpr bool kFolded = VEC && !REPLAY;
   static constexpr uint32_t raw_g = raw_v + kTmax * (REPLAY ? kD * 4 : in_row);
-  static constexpr uint32_t raw_end = raw_g + (VEC ? 2 * kTmax * in_row : 0);
+  static constexpr uint32_t raw_end = raw_g + (VEC ? (REPLAY ? 2 : 1) * kTmax * in_row : 0);
   static constexpr uint32_t k32 = raw_end;                                        // [16][128] fp32
   static constexpr uint32_t q32 = k32 + f32_tile;                                 // forward only
   static constexpr uint32_t d32 = REPLAY ? q32 : q32 + f32_tile;                  // [8 warps][16 steps][16 rows]: v / delta in; y out
-  static constexpr uint32_t dout = d32 + f32_tile;                                // forward with a scalar gate only: delta out
-  static constexpr uint32_t scal = (REPLAY || VEC) ? dout : dout + f32_tile;
+  static constexpr uint32_t dout = d32 + f32_tile;                                // forward with a scalar gate: delta out; folded gate: k / G
+  static constexpr uint32_t scal = REPLAY ? dout : dout + f32_tile;
   static constexpr uint32_t s_beta = scal;               // [3][16]
   static constexpr uint32_t s_g = s_beta + 3 * 16 * 4;   // [3][16]
   static constexpr uint32_t s_bits = s_g + 3 * 16 * 4;   // [4]
   static constexpr uint32_t s_bar = s_bits + 16;         // 8 bytes
-  static constexpr uint32_t total = s_bar + 16;
-  static constexpr uint32_t alloc = total + 1024;        // room to align the base to 1024 bytes
+  static constexpr uint32_t s_gt = s_bar + 16;           // folded gate only: [128] gate products of the whole block
+  static constexpr uint32_t total = s_gt + (kFolded ? kD * 4 : 0);
+  // Room to align the base to 1024 bytes, except where two CTAs of 16-bit inputs would no longer fit one SM with it:
+  // there the kernel checks the alignment of the dynamic shared memory (it is the only shared memory of the kernel).
+  static constexpr uint32_t slack = (kFolded && in_row == kD * 2) ? 0 : 1024;
+  static constexpr uint32_t alloc = total + slack;
+  static_assert(in_row != kD * 2 || 2 * (alloc + 1024) <= 233472, "two CTAs of 16-bit inputs per SM");
 };
 
 __device__ __forceinline__ float2 f2(float a, float b) { return make_float2(a, b); }
@@ -142,6 +152,11 @@ gdn_fast_kernel(const __grid_constant__ CUtensorMap state_map, const GdnArgs a, 
   using L = Layout<InT, REPLAY, VEC>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* sm = smem_raw + ((1024u - (ptx::smem_u32(smem_raw) & 1023u)) & 1023u);
+  if (L::slack == 0 && sm != smem_raw) {   // no room to move the base: report and leave
+    if (threadIdx.x == 0) atomicExch(status, kStatusSmemAlign);
+    return;
+  }
+  constexpr bool kFolded = L::kFolded;
 
   const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
   const int c_sub = lane & 7, r_sub = lane >> 3;   // 8 lanes share a state row; 4 row slots per warp
@@ -158,6 +173,8 @@ gdn_fast_kernel(const __grid_constant__ CUtensorMap state_map, const GdnArgs a, 
   float* q32 = reinterpret_cast<float*>(sm + L::q32);
   float* d32 = reinterpret_cast<float*>(sm + L::d32) + w * (kTmax * 16);   // this warp's [16 steps][16 rows]
   float* dout = reinterpret_cast<float*>(sm + L::dout) + w * (kTmax * 16);
+  float* kh32 = reinterpret_cast<float*>(sm + L::dout);    // folded gate: [16][128] k / G
+  float* s_gt = reinterpret_cast<float*>(sm + L::s_gt);
 
   const InT* gq = reinterpret_cast<const InT*>(a.q);
   const InT* gk = reinterpret_cast<const InT*>(a.k);
@@ -190,7 +207,7 @@ gdn_fast_kernel(const __grid_constant__ CUtensorMap state_map, const GdnArgs a, 
         const long long bt = (long long)b * T + t;
         ptx::cp_async16(sm + L::raw_k + t * L::in_row + off, reinterpret_cast<const uint8_t*>(gk + (bt * a.Hk + hk) * kD) + off);
         if (VEC)
-          ptx::cp_async16(sm + L::raw_g + (gbuf * kTmax + t) * L::in_row + off, reinterpret_cast<const uint8_t*>(gg + (bt * a.Hv + hv) * kD) + off);
+          ptx::cp_async16(sm + L::raw_g + ((kFolded ? 0 : gbuf) * kTmax + t) * L::in_row + off, reinterpret_cast<const uint8_t*>(gg + (bt * a.Hv + hv) * kD) + off);
         if (!REPLAY) {
           ptx::cp_async16(sm + L::raw_q + t * L::in_row + off, reinterpret_cast<const uint8_t*>(gq + (bt * a.Hk + hk) * kD) + off);
           ptx::cp_async16(sm + L::raw_v + t * L::in_row + off, reinterpret_cast<const uint8_t*>(gv + (bt * a.Hv + hv) * kD) + off);
@@ -289,12 +306,16 @@ gdn_fast_kernel(const __grid_constant__ CUtensorMap state_map, const GdnArgs a, 
       const int t = tid >> 4, seg = (tid & 15) * 8;
       if (t < T && ((bits >> t) & 1u)) {
         float x[8];
-        load8_as_f32<InT>(reinterpret_cast<const InT*>(sm + L::raw_k) + t * kD + seg, x);
-        store8<float>(k32 + t * kD + seg, x);
+        if (!kFolded) {
+          load8_as_f32<InT>(reinterpret_cast<const InT*>(sm + L::raw_k) + t * kD + seg, x);
+          store8<float>(k32 + t * kD + seg, x);
+        }
         float* dstage = reinterpret_cast<float*>(sm + L::d32) + (seg >> 4) * (kTmax * 16) + t * 16 + (seg & 15);
         if (!REPLAY) {
-          load8_as_f32<InT>(reinterpret_cast<const InT*>(sm + L::raw_q) + t * kD + seg, x);
-          store8<float>(q32 + t * kD + seg, x);
+          if (!kFolded) {
+            load8_as_f32<InT>(reinterpret_cast<const InT*>(sm + L::raw_q) + t * kD + seg, x);
+            store8<float>(q32 + t * kD + seg, x);
+          }
           load8_as_f32<InT>(reinterpret_cast<const InT*>(sm + L::raw_v) + t * kD + seg, x);
           store8<float>(dstage, x);
         } else {
@@ -302,6 +323,43 @@ gdn_fast_kernel(const __grid_constant__ CUtensorMap state_map, const GdnArgs a, 
           store8<float>(dstage, x);
         }
       }
+    }
+    // Per-channel gate, forward: the gates are folded into the per-token vectors once per item, so that the recurrence
+    // is the scalar-gate one with G = 1.  With G_t the product of the gate rows of the running steps up to t and the
+    // state carried as S = U diag(G_t):  kv = U (G_t k_t),  U += delta (k_t / G_t)^T,  y = U (G_t q_t),  and
+    // S_T = U diag(G_T) at the end.  One thread per channel walks the steps (both halves of the CTA compute the products;
+    // the lower half writes the two k tiles, the upper half q).  A product outside [1e-12, 1e12] in any channel (a gate
+    // of zero, a long run of tiny gates) sends the item down the explicit route below.
+    bool bad = false;
+    if (kFolded) {
+      const int c = tid & (kD - 1), hsel = tid >> 7;
+      const InT* rg = reinterpret_cast<const InT*>(sm + L::raw_g) + c;
+      const InT* rx = reinterpret_cast<const InT*>(sm + (hsel ? L::raw_q : L::raw_k)) + c;
+      // all the loads first (bits has no step at or beyond T), then the chain of products
+      float gv[kTmax], xv[kTmax];
+#pragma unroll
+      for (int t = 0; t < kTmax; ++t) {
+        const bool on = (bits >> t) & 1u;
+        gv[t] = on ? to_f32(rg[t * kD]) : 1.f;
+        xv[t] = on ? to_f32(rx[t * kD]) : 0.f;
+      }
+      float Gc = 1.f, lo = 1.f, hi = 1.f;
+#pragma unroll
+      for (int t = 0; t < kTmax; ++t) {
+        Gc *= gv[t];
+        lo = fminf(lo, Gc);
+        hi = fmaxf(hi, Gc);
+        if ((bits >> t) & 1u) {
+          if (hsel) {
+            q32[t * kD + c] = xv[t] * Gc;
+          } else {
+            k32[t * kD + c] = xv[t] * Gc;
+            kh32[t * kD + c] = __fdividef(xv[t], Gc);
+          }
+        }
+      }
+      bad = !(lo >= 1e-12f && hi <= 1e12f) || Gc != Gc;   // a product that is not a number stays one to the end
+      if (!hsel) s_gt[c] = Gc;
     }
     // thread (r_sub, c_sub) owns rows 16w + r_sub + 4i (i < 4) and, in each 32-column box, the
     // 4 columns of 16-byte chunk c_sub: 64 floats.  A quarter warp reads 8 distinct chunks of
@@ -318,7 +376,26 @@ gdn_fast_kernel(const __grid_constant__ CUtensorMap state_map, const GdnArgs a, 
         S[i][box][1] = f2(v4.z, v4.w);
       }
     }
-    __syncthreads();  // state tile and raw inputs are consumed: both may be refilled
+    // state tile and raw inputs are consumed: both may be refilled
+    bool explicit_gate = false;
+    if (kFolded) {
+      explicit_gate = __syncthreads_or(bad);
+      if (explicit_gate) {   // uniform: every step decays the state column by column; k and q as they are, the gate rows in the k / G tile
+        const int c = tid & (kD - 1), hsel = tid >> 7;
+        for (int t = 0; t < T; ++t) {
+          if (!((bits >> t) & 1u)) continue;
+          if (hsel) {
+            q32[t * kD + c] = to_f32(reinterpret_cast<const InT*>(sm + L::raw_q)[t * kD + c]);
+          } else {
+            k32[t * kD + c] = to_f32(reinterpret_cast<const InT*>(sm + L::raw_k)[t * kD + c]);
+            kh32[t * kD + c] = to_f32(reinterpret_cast<const InT*>(sm + L::raw_g)[t * kD + c]);
+          }
+        }
+        __syncthreads();
+      }
+    } else {
+      __syncthreads();
+    }
 
     if (has_next) {
       if (tid == 0) issue_state(b_nxt, hv_nxt);
@@ -338,7 +415,7 @@ gdn_fast_kernel(const __grid_constant__ CUtensorMap state_map, const GdnArgs a, 
         kk[box][1] = f2(k4.z, k4.w);
       }
       // per-channel gate: this thread's 16 columns of the step's gate row, read box by box where they are used
-      const InT* grow = VEC ? reinterpret_cast<const InT*>(sm + L::raw_g) + ((it & 1) * kTmax + t) * kD + col : nullptr;
+      const InT* grow = (VEC && REPLAY) ? reinterpret_cast<const InT*>(sm + L::raw_g) + ((it & 1) * kTmax + t) * kD + col : nullptr;
       if (!VEC) Gd *= s_g[slot * 16 + t];
       if (!VEC && Gd < 1e-12f) {  // uniform per work item: U <- Gd * U, Gd <- 1
         const float2 G2 = f2(Gd, Gd);
@@ -370,11 +447,11 @@ gdn_fast_kernel(const __grid_constant__ CUtensorMap state_map, const GdnArgs a, 
       } else {
         const float beta = s_beta[slot * 16 + t];
         float part[4];
-        if (VEC) {   // decay column by column first, as the reference does
+        if (kFolded && explicit_gate) {   // decay column by column first, as the reference does
 #pragma unroll
           for (int box = 0; box < 4; ++box) {
-            float2 gb[2];
-            load4_as_f32x2<InT>(grow + 32 * box, gb);
+            const float4 g4 = *reinterpret_cast<const float4*>(kh32 + t * kD + 32 * box + col);
+            const float2 gb[2] = {f2(g4.x, g4.y), f2(g4.z, g4.w)};
 #pragma unroll
             for (int i = 0; i < 4; ++i)
 #pragma unroll
@@ -402,12 +479,18 @@ gdn_fast_kernel(const __grid_constant__ CUtensorMap state_map, const GdnArgs a, 
         for (int box = 0; box < 4; ++box) {
           const float4 q4 = *reinterpret_cast<const float4*>(q32 + t * kD + 32 * box + col);
           const float2 qq[2] = {f2(q4.x, q4.y), f2(q4.z, q4.w)};
+          float2 ku[2] = {kk[box][0], kk[box][1]};   // the update's k: k itself, or k / G where the gate is folded
+          if (kFolded && !explicit_gate) {
+            const float4 h4 = *reinterpret_cast<const float4*>(kh32 + t * kD + 32 * box + col);
+            ku[0] = f2(h4.x, h4.y);
+            ku[1] = f2(h4.z, h4.w);
+          }
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
             const float2 dd = f2(d[i], d[i]);
 #pragma unroll
             for (int j = 0; j < 2; ++j) {
-              S[i][box][j] = __ffma2_rn(dd, kk[box][j], S[i][box][j]);
+              S[i][box][j] = __ffma2_rn(dd, ku[j], S[i][box][j]);
               acc[i][j] = box == 0 ? __fmul2_rn(S[i][box][j], qq[j]) : __ffma2_rn(S[i][box][j], qq[j], acc[i][j]);
             }
           }
@@ -422,6 +505,17 @@ gdn_fast_kernel(const __grid_constant__ CUtensorMap state_map, const GdnArgs a, 
           else if (a.tape)   // no staging tile in this variant: 16 lanes write the warp's 64 contiguous bytes of the step
             a.tape[(((long long)b_cur * T + t) * a.Hv + hv_cur) * kD + 16 * w + my_r] = d_mine;
         }
+      }
+    }
+    if (kFolded && !explicit_gate) {   // S_T = U diag(G_T)
+#pragma unroll
+      for (int box = 0; box < 4; ++box) {
+        const float4 g4 = *reinterpret_cast<const float4*>(s_gt + 32 * box + col);
+        const float2 gb[2] = {f2(g4.x, g4.y), f2(g4.z, g4.w)};
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+          for (int j = 0; j < 2; ++j) S[i][box][j] = __fmul2_rn(S[i][box][j], gb[j]);
       }
     }
     if (Gd != 1.f) {

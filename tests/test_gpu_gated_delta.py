@@ -149,6 +149,39 @@ def test_edge_lengths_and_determinism(vec):
     np.testing.assert_array_equal(s, s3)
 
 
+@pytest.mark.parametrize("dtype", ["bf16", "fp32"])
+@pytest.mark.parametrize("regime", ["zero_gates", "tiny_gates", "small_gates", "mixed_items"])
+def test_vector_gate_extreme_gates(regime, dtype):
+    """Per-channel gates at the edges of the forward kernel's two routes: it folds the running gate products into k
+    and q (state carried divided by the product), and takes the column-by-column route for an item whose product
+    leaves [1e-12, 1e12] in any channel."""
+    B, T, Hk, Hv, D = 6, 16, 2, 4, 128
+    x = O.make_gdn_inputs(B, T, Hk, Hv, D, D, 930, True, dtype)
+    x["n"] = np.array([16, 16, 9, 16, 1, 13], np.int32)
+    g = x["g"]
+    if regime == "zero_gates":            # exact zeros in some channels of some steps: those columns are cleared
+        rng = np.random.default_rng(5)
+        g[rng.random(g.shape) < 0.02] = 0.0
+    elif regime == "tiny_gates":          # products far below the smallest normal number
+        g[:] = (g * 1e-4).astype(np.float32)
+    elif regime == "small_gates":         # products down to ~1e-11: still the folded route, 1 / G large
+        g[:] = np.clip(g, 0.21, 1.0)
+    else:                                 # one sequence on the explicit route between sequences on the folded one
+        g[2, 3, :, 17] = 0.0
+        g[4, 0, 1, :] = 1e-20
+    if dtype != "fp32":
+        x["g"] = g = O._round_to(g, dtype)
+    y, s, tape = run_fwd(x, dtype)
+    yo, so, to = CO.gated_delta(x["q"], x["k"], x["v"], g, x["beta"], x["state"], n=x["n"])
+    assert np.isfinite(s).all() and np.isfinite(y).all()
+    assert rel(s, so) < STATE_RTOL
+    assert rel(tape, to) < 1e-4
+    assert rel(y, yo) < y_tol(dtype)
+    # column by column too: a column the gates cleared holds what the later steps wrote, nothing of the old state
+    col_scale = np.maximum(np.abs(so).max(axis=(0, 2), keepdims=True), 1e-30)
+    assert float((np.abs(s - so) / col_scale).max()) < 1e-3
+
+
 def test_in_place_state_through_c_abi():
     from swiftlm_b200 import _lib
     x = O.make_gdn_inputs(3, 16, 2, 4, 128, 128, 901, False, "bf16")
