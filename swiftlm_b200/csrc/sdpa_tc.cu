@@ -1408,6 +1408,10 @@ __global__ void __launch_bounds__(128) sdpa_tc_merge_kernel(const TcParams p, in
   __shared__ float s_f[kMaxRanges][32];    // per range and row: the range's maximum, then exp2(m - max over the ranges)
   __shared__ float s_red[4][32];           // per warp and row: partial maximum, then partial denominator
   __shared__ int s_count;
+  // Launched with programmatic stream serialization behind the main kernel (which lets its dependents go as soon as all
+  // of its CTAs are placed): the CTAs of this grid are resident when the main kernel ends; nothing is read before the wait.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   const int unit = blockIdx.x, rgrp = blockIdx.y, cgrp = blockIdx.z;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   // Every global load of the set-up below is issued together with its neighbours (a chain of dependent loads, one
@@ -1688,7 +1692,17 @@ int32_t launch_typed(const SdpaArgs& a, const TurboKvArgs* turbo, cudaStream_t s
   DFLASH_LAUNCH_CHECK();
   count_launch();
   if (need_merge_kernel) {
-    sdpa_tc_merge_kernel<InT, D><<<dim3(p.units, kRowsM / 32, D / 16), 128, 0, stream>>>(p, (int)(2 * grid));
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(p.units, kRowsM / 32, D / 16);
+    cfg.blockDim = dim3(128);
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;   // see the top of the merge kernel
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    DFLASH_CUDA_CHECK(cudaLaunchKernelEx(&cfg, sdpa_tc_merge_kernel<InT, D>, p, (int)(2 * grid)));
     DFLASH_LAUNCH_CHECK();
     count_launch();
   }
