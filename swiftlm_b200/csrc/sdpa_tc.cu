@@ -1268,6 +1268,12 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                   const int sl = (i == cta_first) ? 2 * i + 1 : 2 * i;
                   if (sl != s.slot) all = all && (ld_acquire_u64(p.flags + sl) == p.epoch);
                 }
+                // The CTA that sees every range of the unit arrived merges, and clears the unit's flags: a launch
+                // replayed from a CUDA graph carries the same epoch every time and must not find the flags of its
+                // previous run.  (A range's owner sets its flag once per launch, before anybody can see it set, so a
+                // clear never overtakes a set; a CTA that reads cleared flags leaves the merge to the one that cleared.)
+                if (all)
+                  for (int i = cta_first; i <= cta_last; ++i) st_release_u64(p.flags + ((i == cta_first) ? 2 * i + 1 : 2 * i), 0ull);
                 *merge_go = all ? 1 : 0;
               }
               ok = group_sync();

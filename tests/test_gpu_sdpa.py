@@ -285,3 +285,40 @@ def test_back_to_back_calls_share_the_workspace(shape):
     K().device_status()
     for i in range(9):
         assert torch.equal(outs[i], alone[i % 3]), i
+
+
+@pytest.mark.parametrize("shape", [(20, 16, 2, 256, 2064), (50, 16, 2, 256, 1040), (1, 16, 2, 256, 20016), (32, 16, 2, 256, 1040)],
+                         ids=["equal_cuts_fused_merge", "stream_k_fused_merge", "stream_k_merge_kernel", "cluster_pairs"])
+def test_replay_from_a_cuda_graph_with_new_inputs(shape):
+    """One call captured into a CUDA graph and replayed over inputs that change between replays gives the bits of a
+    direct call on the same inputs: nothing a replay leaves in the workspace (arrival flags, partials, the slot table)
+    may look current to the next replay, which carries the same launch parameters."""
+    B, Hq, Hkv, D, N = shape
+    g = torch.Generator(device="cuda").manual_seed(sum(shape) + 1)
+    q = torch.empty(B, Hq, 16, D, device="cuda", dtype=torch.bfloat16)
+    k = torch.empty(B, Hkv, N, D, device="cuda", dtype=torch.bfloat16)
+    v = torch.empty_like(k)
+    out = torch.empty_like(q)
+    scale = 1.0 / float(D) ** 0.5
+
+    def fill():
+        q.copy_(torch.randn(q.shape, device="cuda", generator=g))
+        k.copy_(torch.randn(k.shape, device="cuda", generator=g))
+        v.copy_(torch.randn(v.shape, device="cuda", generator=g))
+
+    fill()
+    K().batched_sdpa_2pass(q, k, v, scale, out=out)      # the cached workspace exists before the capture
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        K().batched_sdpa_2pass(q, k, v, scale, out=out)
+    for _ in range(4):
+        fill()
+        out.zero_()
+        graph.replay()
+        torch.cuda.synchronize()
+        got = out.clone()
+        want = K().batched_sdpa_2pass(q, k, v, scale)
+        torch.cuda.synchronize()
+        assert torch.equal(got, want)
+    K().device_status()
