@@ -103,3 +103,45 @@ def test_step_without_the_verify_forwards_final_state():
     for name in ("y", "tape", "states", "convs", "accept", "next_token", "replay_len", "attn_out"):
         assert torch.equal(a[name], b[name]), name
 
+
+
+def test_step_replayed_from_a_cuda_graph():
+    """The step captured once into a CUDA graph and replayed over new activations, states and logits gives the bits of a
+    direct call on the same inputs (the accepted lengths change from replay to replay and never leave the device)."""
+    from swiftlm_b200 import kernels
+    from swiftlm_b200.verify_step import StepConfig, VerifyStep
+    cfg = StepConfig(batch=5, gdn_layers=3, attn_layers=2, Hk=2, Hv=4, Hq=16, Hkv=2, D=256, context=1024, vocab=4096, conv_dim=64)
+    step = VerifyStep(cfg, torch.device("cuda", 0))
+    step.run()                                                # attributes set, nothing left to allocate
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        step.run()
+    names = ("y", "tape", "states", "convs", "accept", "next_token", "replay_len", "attn_out", "logits_rows")
+    g = torch.Generator(device="cuda").manual_seed(77)
+    seen = set()
+    for _ in range(3):
+        for t in (step.q, step.k, step.v, step.attn_q, step.qkv, step.logits):
+            t.copy_(torch.randn(t.shape, device="cuda", generator=g))
+        step.state.copy_(0.02 * torch.randn(step.state.shape, device="cuda", generator=g))
+        post = kernels.greedy_tokens_with_mask(step.logits).to(torch.int32)
+        agree = torch.randint(0, cfg.T, (cfg.batch,), device="cuda", generator=g)
+        ids = torch.zeros(cfg.batch, cfg.T, dtype=torch.int32, device="cuda")
+        ids[:, 1:] = post[:, :-1]
+        wrong = torch.arange(cfg.T - 1, device="cuda").view(1, -1) >= agree.view(-1, 1)
+        ids[:, 1:][wrong] = (ids[:, 1:][wrong] + 1) % cfg.vocab
+        step.verify_ids.copy_(ids)
+        graph.replay()
+        torch.cuda.synchronize()
+        got = {n: getattr_out(step, n).clone() for n in names}
+        step.run()
+        torch.cuda.synchronize()
+        for n in names:
+            assert torch.equal(got[n], getattr_out(step, n)), n
+        seen.add(tuple(step.accept.cpu().tolist()))
+    kernels.device_status()
+    assert len(seen) > 1                                      # the replays really ran on different acceptance patterns
+
+
+def getattr_out(step, name):
+    return {"states": step.state_rolled, "convs": step.conv_out}.get(name, getattr(step, name, None))
