@@ -1404,14 +1404,19 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
 // ---- merge of the split-KV partials ----------------------------------------------------------
 // One block per (unit, 32 rows, 16 columns); the ranges of a unit are summed in slot order.
 template <typename InT, int D>
-__global__ void __launch_bounds__(128) sdpa_tc_merge_kernel(const TcParams p, int n_slots) {
+__global__ void __launch_bounds__(128) sdpa_tc_merge_kernel(const TcParams p, int n_slots, int max_ranges) {
   // One CTA (4 warps) combines 32 rows x 4 float4 columns of one unit: lane = row (the partials keep the 128 rows of a float4
   // column contiguous, so a warp reads 512 contiguous bytes per range), warp = column.  A unit has at most one range
-  // per CTA of the main kernel, so kMaxRanges covers every GPU with up to 320 SMs; more is reported, not dropped.
-  constexpr int kMaxRanges = 320;
-  __shared__ int s_slots[kMaxRanges];
-  __shared__ int s_raw[2 * kMaxRanges];    // copy of the slot table (two slots per CTA of the main kernel)
-  __shared__ float s_f[kMaxRanges][32];    // per range and row: the range's maximum, then exp2(m - max over the ranges)
+  // per CTA of the main kernel, so the limit of 320 covers every GPU with up to 320 SMs; more is reported, not dropped.
+  // The per-range weights live in dynamic shared memory sized by the launcher for the most ranges a unit of this
+  // launch can have (`max_ranges`, at most one per CTA of the main kernel): a fixed array for 320 ranges would be 40 KB
+  // and leave room for five of these small CTAs per SM, two waves for a grid of a thousand.
+  constexpr int kMaxRangesLimit = 320;
+  const int kMaxRanges = max_ranges < kMaxRangesLimit ? max_ranges : kMaxRangesLimit;
+  __shared__ int s_slots[kMaxRangesLimit];
+  __shared__ int s_raw[2 * kMaxRangesLimit];    // copy of the slot table (two slots per CTA of the main kernel)
+  extern __shared__ float s_f_raw[];
+  float (*s_f)[32] = reinterpret_cast<float (*)[32]>(s_f_raw);   // per range and row: the range's maximum, then exp2(m - max over the ranges)
   __shared__ float s_red[4][32];           // per warp and row: partial maximum, then partial denominator
   __shared__ int s_count;
   // Launched with programmatic stream serialization behind the main kernel (which lets its dependents go as soon as all
@@ -1422,7 +1427,7 @@ __global__ void __launch_bounds__(128) sdpa_tc_merge_kernel(const TcParams p, in
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   // Every global load of the set-up below is issued together with its neighbours (a chain of dependent loads, one
   // L2 round trip each, used to take most of this kernel's time): the slot table first, then the maxima, then the sums.
-  const int n_scan = n_slots < 2 * kMaxRanges ? n_slots : 2 * kMaxRanges;
+  const int n_scan = n_slots < 2 * kMaxRangesLimit ? n_slots : 2 * kMaxRangesLimit;
   for (int i = threadIdx.x; i < n_scan; i += 128) s_raw[i] = p.slot_unit[i];
   __syncthreads();
   // slots of this unit, in slot order (a fixed summation order keeps results bit-reproducible)
@@ -1701,14 +1706,15 @@ int32_t launch_typed(const SdpaArgs& a, const TurboKvArgs* turbo, cudaStream_t s
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(p.units, kRowsM / 32, D / 16);
     cfg.blockDim = dim3(128);
-    cfg.dynamicSmemBytes = 0;
+    const int max_ranges = (int)grid;                       // a unit has at most one range per CTA of the main kernel
+    cfg.dynamicSmemBytes = (size_t)(max_ranges < 320 ? max_ranges : 320) * 32 * sizeof(float);
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;   // see the top of the merge kernel
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    DFLASH_CUDA_CHECK(cudaLaunchKernelEx(&cfg, sdpa_tc_merge_kernel<InT, D>, p, (int)(2 * grid)));
+    DFLASH_CUDA_CHECK(cudaLaunchKernelEx(&cfg, sdpa_tc_merge_kernel<InT, D>, p, (int)(2 * grid), max_ranges));
     DFLASH_LAUNCH_CHECK();
     count_launch();
   }
