@@ -150,7 +150,7 @@ def test_edge_lengths_and_determinism(vec):
 
 
 @pytest.mark.parametrize("dtype", ["bf16", "fp32"])
-@pytest.mark.parametrize("regime", ["zero_gates", "tiny_gates", "small_gates", "mixed_items"])
+@pytest.mark.parametrize("regime", ["zero_gates", "tiny_gates", "small_gates", "gates_above_one", "mixed_items"])
 def test_vector_gate_extreme_gates(regime, dtype):
     """Per-channel gates at the edges of the forward kernel's two routes: it folds the running gate products into k
     and q (state carried divided by the product), and takes the column-by-column route for an item whose product
@@ -166,6 +166,8 @@ def test_vector_gate_extreme_gates(regime, dtype):
         g[:] = (g * 1e-4).astype(np.float32)
     elif regime == "small_gates":         # products down to ~1e-11: still the folded route, 1 / G large
         g[:] = np.clip(g, 0.21, 1.0)
+    elif regime == "gates_above_one":     # not a decay any more, but nothing in the interface forbids it
+        g[:] = (g * 1.8).astype(np.float32)
     else:                                 # one sequence on the explicit route between sequences on the folded one
         g[2, 3, :, 17] = 0.0
         g[4, 0, 1, :] = 1e-20
